@@ -37,7 +37,7 @@ int check_cuda(cudaError_t e, const char* what);
 
 // Device-side status word: kernels OR a bit in when a bounded wait gives up.
 // The host reads it with ab_device_status().
-extern __device__ unsigned int g_device_status;
+static __device__ unsigned int g_device_status = 0;
 constexpr unsigned int DEV_WAIT_GEMV = 1u;
 constexpr unsigned int DEV_WAIT_GEMM = 2u;
 constexpr unsigned int DEV_WAIT_HEAD = 4u;

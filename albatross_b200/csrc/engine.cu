@@ -1,0 +1,319 @@
+// Host-side engine: the layer loop of RWKV_x070.forward / forward_batch as kernel launches,
+// and the extern "C" surface declared in include/albatross_b200.h.
+//
+// Two launch programs share the weights:
+//   * batch 1, one token (reference/rwkv7.py:128-157): five launches per block —
+//       [LN1 + shift-lerps + r/k/v + adapter-down rows] -> [per-head fused WKV] -> [output proj + residual]
+//       -> [LN2 + shift-lerp + ffn key + relu^2] -> [ffn value + residual], then [LN_out + head].
+//   * any other (B, T) (reference/rwkv7.py:159-221): row-wise LN / lerp kernels, batched matrix
+//     products, the same per-head kernel reading precomputed adapter outputs.
+#include <stdarg.h>
+#include <string.h>
+
+#include <new>
+#include <vector>
+
+#include "../../include/albatross_b200.h"
+#include "gemm.cuh"
+#include "gemv.cuh"
+#include "head.cuh"
+#include "rows.cuh"
+
+namespace ab {
+
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+int check_cuda(cudaError_t e, const char* what) {
+    if (e == cudaSuccess) return OK;
+    set_error("CUDA error %d (%s) in %s", (int)e, cudaGetErrorString(e), what);
+    return ERR_CUDA;
+}
+
+static GemvSeg seg_of(const ab_mat& m, const void* mix, int epi, void* out, const void* resid = nullptr) {
+    GemvSeg g = {};
+    g.w = m.w; g.scale = m.scale; g.col_scale = m.col_scale; g.tscale = m.tscale;
+    g.mix = (const __half*)mix; g.resid = (const __half*)resid; g.out = (__half*)out;
+    g.fmt = m.fmt; g.epi = epi; g.n_rows = m.n_out;
+    return g;
+}
+
+}  // namespace ab
+
+using namespace ab;
+
+struct ab_model {
+    ab_model_desc d;
+    std::vector<ab_layer> layers;
+    int stages = 4;
+    int use_pdl = 1;
+};
+
+namespace {
+
+inline size_t al(size_t v) { return (v + 255) & ~(size_t)255; }
+
+// Workspace carve-up shared by both programs. M = B*T rows.
+struct Workspace {
+    __half *x, *xn, *xn2, *r, *k, *v, *vfirst, *att, *kf, *hw, *ha, *hv, *hg;
+    __half *mix[6], *w_raw, *a_raw, *vg_raw, *g, *xlast;
+    void* gemm_scratch;
+    size_t total;
+};
+
+Workspace carve(const ab_model* m, int B, int T, unsigned char* base) {
+    const size_t M = (size_t)B * T, D = m->d.n_embd, F = 4 * D;
+    const ab_layer& l0 = m->layers[0];
+    size_t rmax[4] = {0, 0, 0, 0};
+    for (const ab_layer& l : m->layers) {
+        rmax[0] = std::max(rmax[0], (size_t)l.w1t.n_out); rmax[1] = std::max(rmax[1], (size_t)l.a1t.n_out);
+        rmax[2] = std::max(rmax[2], (size_t)l.v1t.n_out); rmax[3] = std::max(rmax[3], (size_t)l.g1t.n_out);
+    }
+    (void)l0;
+    Workspace w;
+    size_t off = 0;
+    auto take = [&](size_t elems) { __half* p = (__half*)(base + off); off += al(elems * 2); return p; };
+    w.x = take(M * D); w.xn = take(M * D); w.xn2 = take(M * D);
+    w.r = take(M * D); w.k = take(M * D); w.v = take(M * D); w.vfirst = take(M * D); w.att = take(M * D);
+    w.kf = take(M * F);
+    w.hw = take(M * rmax[0]); w.ha = take(M * rmax[1]); w.hv = take(M * rmax[2]); w.hg = take(M * rmax[3]);
+    const bool batched = !(B == 1 && T == 1);
+    for (int j = 0; j < 6; ++j) w.mix[j] = batched ? take(M * D) : nullptr;
+    w.w_raw = batched ? take(M * D) : nullptr; w.a_raw = batched ? take(M * D) : nullptr;
+    w.vg_raw = batched ? take(M * D) : nullptr; w.g = batched ? take(M * D) : nullptr;
+    w.xlast = batched ? take((size_t)B * D) : nullptr;
+    w.gemm_scratch = base + off;
+    off += al(batched ? gemm_scratch_bytes(m->d.head, (int)M) : 0);
+    w.total = off;
+    return w;
+}
+
+#define AB_TRY(call)                \
+    do {                            \
+        int _s = (call);            \
+        if (_s != OK) return _s;    \
+    } while (0)
+
+int forward_one(ab_model* m, const int32_t* token, void* const* state, const Workspace& ws, __half* logits,
+                cudaStream_t st) {
+    const int D = m->d.n_embd, H = D / HEAD;
+    for (int i = 0; i < m->d.n_layer; ++i) {
+        const ab_layer& L = m->layers[i];
+        __half* att_prev = (__half*)state[3 * i];
+        float* kv = (float*)state[3 * i + 1];
+        __half* ffn_prev = (__half*)state[3 * i + 2];
+        {   // LN1 + shift-lerps + r/k/v + adapter-down rows
+            GemvParams p = {};
+            p.K = D; p.stages = m->stages; p.use_pdl = m->use_pdl;
+            if (i == 0) { p.emb = (const __half*)m->d.emb; p.token = token; p.x_copy = ws.x; }
+            else p.x = ws.x;
+            p.x_prev = att_prev; p.ln_w = (const __half*)L.ln1_w; p.ln_b = (const __half*)L.ln1_b; p.ln_out = ws.xn;
+            int n = 0;
+            p.seg[n++] = seg_of(L.receptance, L.x_r, EPI_NONE, ws.r);
+            p.seg[n++] = seg_of(L.key, L.x_k, EPI_NONE, ws.k);
+            p.seg[n++] = seg_of(L.value, L.x_v, EPI_NONE, ws.v);
+            p.seg[n++] = seg_of(L.w1t, L.x_w, EPI_TANH, ws.hw);
+            p.seg[n++] = seg_of(L.a1t, L.x_a, EPI_NONE, ws.ha);
+            if (i > 0) p.seg[n++] = seg_of(L.v1t, L.x_v, EPI_NONE, ws.hv);
+            p.seg[n++] = seg_of(L.g1t, L.x_g, EPI_SIGMOID, ws.hg);
+            p.nseg = n;
+            AB_TRY(gemv_launch(p, st));
+        }
+        {   // per-head: adapter up-projections, glue, WKV state update, group norm, bonus, gate
+            HeadParams h = {};
+            h.B = 1; h.T = 1; h.D = D; h.H = H; h.layer0 = (i == 0);
+            h.state = kv; h.r = ws.r; h.k = ws.k; h.v = ws.v; h.v_first = ws.vfirst;
+            h.hw = ws.hw; h.ha = ws.ha; h.hv = ws.hv; h.hg = ws.hg;
+            h.w2 = (const __half*)L.w2; h.a2 = (const __half*)L.a2; h.v2 = (const __half*)L.v2; h.g2 = (const __half*)L.g2;
+            h.rw = L.w1t.n_out; h.ra = L.a1t.n_out; h.rv = (i == 0) ? 0 : L.v1t.n_out; h.rg = L.g1t.n_out;
+            h.w0 = (const __half*)L.w0; h.a0 = (const __half*)L.a0; h.v0 = (const __half*)L.v0;
+            h.k_k = (const __half*)L.k_k; h.k_a = (const __half*)L.k_a; h.r_k = (const __half*)L.r_k;
+            h.lnx_w = (const __half*)L.lnx_w; h.lnx_b = (const __half*)L.lnx_b;
+            h.out = ws.att; h.copy_src = ws.xn; h.copy_dst = att_prev; h.use_pdl = m->use_pdl;
+            AB_TRY(head_launch(h, st));
+        }
+        {   // output projection + residual
+            GemvParams p = {};
+            p.K = D; p.stages = m->stages; p.use_pdl = m->use_pdl; p.x = ws.att; p.nseg = 1;
+            p.seg[0] = seg_of(L.output, nullptr, EPI_RESID, ws.x, ws.x);
+            AB_TRY(gemv_launch(p, st));
+        }
+        {   // LN2 + shift-lerp + ffn key + relu^2
+            GemvParams p = {};
+            p.K = D; p.stages = m->stages; p.use_pdl = m->use_pdl; p.x = ws.x; p.nseg = 1;
+            p.x_prev = ffn_prev; p.ln_w = (const __half*)L.ln2_w; p.ln_b = (const __half*)L.ln2_b; p.ln_out = ws.xn2;
+            p.seg[0] = seg_of(L.ffn_key, L.ffn_x_k, EPI_RELU2, ws.kf);
+            AB_TRY(gemv_launch(p, st));
+        }
+        {   // ffn value + residual; hands the new channel-mix token-shift state over
+            GemvParams p = {};
+            p.K = 4 * D; p.stages = m->stages; p.use_pdl = m->use_pdl; p.x = ws.kf; p.nseg = 1;
+            p.seg[0] = seg_of(L.ffn_value, nullptr, EPI_RESID, ws.x, ws.x);
+            p.copy_src = ws.xn2; p.copy_dst = ffn_prev; p.copy_n = D;
+            AB_TRY(gemv_launch(p, st));
+        }
+    }
+    GemvParams p = {};
+    p.K = D; p.stages = m->stages; p.use_pdl = m->use_pdl; p.x = ws.x; p.nseg = 1;
+    p.ln_w = (const __half*)m->d.lnout_w; p.ln_b = (const __half*)m->d.lnout_b;
+    p.seg[0] = seg_of(m->d.head, nullptr, EPI_NONE, logits);
+    return gemv_launch(p, st);
+}
+
+int forward_rows(ab_model* m, int B, int T, const int32_t* tokens, void* const* state, const Workspace& ws,
+                 __half* logits, int full_output, cudaStream_t st) {
+    const int D = m->d.n_embd, H = D / HEAD, M = B * T;
+    AB_TRY(gather_rows((const __half*)m->d.emb, tokens, M, D, ws.x, st));
+    for (int i = 0; i < m->d.n_layer; ++i) {
+        const ab_layer& L = m->layers[i];
+        AB_TRY(ln_rows(ws.x, (const __half*)L.ln1_w, (const __half*)L.ln1_b, M, D, 1, 0, ws.xn, st));
+        MixParams mp = {};
+        mp.xn = ws.xn; mp.x_prev = (__half*)state[3 * i]; mp.B = B; mp.T = T; mp.D = D; mp.n_mix = 6;
+        const void* mv[6] = {L.x_r, L.x_k, L.x_v, L.x_w, L.x_a, L.x_g};
+        for (int j = 0; j < 6; ++j) { mp.mix[j] = (const __half*)mv[j]; mp.out[j] = ws.mix[j]; }
+        AB_TRY(mix_rows(mp, st));
+        void* sc = ws.gemm_scratch;
+        AB_TRY(gemm_launch(L.receptance, M, ws.mix[0], ws.r, EPI_NONE, nullptr, sc, st));
+        AB_TRY(gemm_launch(L.key, M, ws.mix[1], ws.k, EPI_NONE, nullptr, sc, st));
+        AB_TRY(gemm_launch(L.value, M, ws.mix[2], ws.v, EPI_NONE, nullptr, sc, st));
+        AB_TRY(gemm_launch(L.w1t, M, ws.mix[3], ws.hw, EPI_TANH, nullptr, sc, st));
+        AB_TRY(gemm_launch(L.a1t, M, ws.mix[4], ws.ha, EPI_NONE, nullptr, sc, st));
+        AB_TRY(gemm_launch(L.g1t, M, ws.mix[5], ws.hg, EPI_SIGMOID, nullptr, sc, st));
+        AB_TRY(gemm_launch(L.w2t, M, ws.hw, ws.w_raw, EPI_NONE, nullptr, sc, st));
+        AB_TRY(gemm_launch(L.a2t, M, ws.ha, ws.a_raw, EPI_NONE, nullptr, sc, st));
+        AB_TRY(gemm_launch(L.g2t, M, ws.hg, ws.g, EPI_NONE, nullptr, sc, st));
+        if (i > 0) {
+            AB_TRY(gemm_launch(L.v1t, M, ws.mix[2], ws.hv, EPI_NONE, nullptr, sc, st));
+            AB_TRY(gemm_launch(L.v2t, M, ws.hv, ws.vg_raw, EPI_NONE, nullptr, sc, st));
+        }
+        HeadParams h = {};
+        h.B = B; h.T = T; h.D = D; h.H = H; h.layer0 = (i == 0);
+        h.state = (float*)state[3 * i + 1]; h.r = ws.r; h.k = ws.k; h.v = ws.v; h.v_first = ws.vfirst;
+        h.w_raw = ws.w_raw; h.a_raw = ws.a_raw; h.vg_raw = ws.vg_raw; h.g = ws.g;
+        h.w0 = (const __half*)L.w0; h.a0 = (const __half*)L.a0; h.v0 = (const __half*)L.v0;
+        h.k_k = (const __half*)L.k_k; h.k_a = (const __half*)L.k_a; h.r_k = (const __half*)L.r_k;
+        h.lnx_w = (const __half*)L.lnx_w; h.lnx_b = (const __half*)L.lnx_b;
+        h.out = ws.att;
+        AB_TRY(head_launch(h, st));
+        AB_TRY(gemm_launch(L.output, M, ws.att, ws.x, EPI_RESID, ws.x, sc, st));
+
+        AB_TRY(ln_rows(ws.x, (const __half*)L.ln2_w, (const __half*)L.ln2_b, M, D, 1, 0, ws.xn, st));
+        MixParams fp = {};
+        fp.xn = ws.xn; fp.x_prev = (__half*)state[3 * i + 2]; fp.B = B; fp.T = T; fp.D = D; fp.n_mix = 1;
+        fp.mix[0] = (const __half*)L.ffn_x_k; fp.out[0] = ws.mix[0];
+        AB_TRY(mix_rows(fp, st));
+        AB_TRY(gemm_launch(L.ffn_key, M, ws.mix[0], ws.kf, EPI_RELU2, nullptr, sc, st));
+        AB_TRY(gemm_launch(L.ffn_value, M, ws.kf, ws.x, EPI_RESID, ws.x, sc, st));
+    }
+    if (full_output || T == 1) {
+        AB_TRY(ln_rows(ws.x, (const __half*)m->d.lnout_w, (const __half*)m->d.lnout_b, M, D, 1, 0, ws.xn, st));
+        return gemm_launch(m->d.head, M, ws.xn, logits, EPI_NONE, nullptr, ws.gemm_scratch, st);
+    }
+    AB_TRY(ln_rows(ws.x, (const __half*)m->d.lnout_w, (const __half*)m->d.lnout_b, B, D, T, T - 1, ws.xlast, st));
+    return gemm_launch(m->d.head, B, ws.xlast, logits, EPI_NONE, nullptr, ws.gemm_scratch, st);
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* ab_last_error(void) { return g_err; }
+int ab_version(void) { return 1; }
+
+int ab_device_status(uint32_t* status_host) {
+    AB_CHECK_ARG(status_host, "ab_device_status: null pointer");
+    AB_CUDA(cudaDeviceSynchronize());
+    unsigned int v = 0, zero = 0;
+    AB_CUDA(cudaMemcpyFromSymbol(&v, g_device_status, sizeof(v)));
+    AB_CUDA(cudaMemcpyToSymbol(g_device_status, &zero, sizeof(zero)));
+    *status_host = v;
+    return OK;
+}
+
+int ab_wkv7_fwd(int B, int T, int C, int H, float* state, const void* r, const void* w, const void* k, const void* v,
+                const void* a, const void* b, void* y, void* stream) {
+    return wkv7_launch(B, T, C, H, state, (const __half*)r, (const __half*)w, (const __half*)k, (const __half*)v,
+                       (const __half*)a, (const __half*)b, (__half*)y, (cudaStream_t)stream);
+}
+
+int ab_gemv(const ab_mat* m, const void* x, void* y, void* stream) {
+    AB_CHECK_ARG(m && x && y, "ab_gemv: null pointer");
+    AB_TRY(check_mat(*m, "ab_gemv"));
+    GemvParams p = {};
+    p.nseg = 1; p.K = m->k; p.x = (const __half*)x;
+    p.seg[0] = seg_of(*m, nullptr, EPI_NONE, y);
+    return gemv_launch(p, (cudaStream_t)stream);
+}
+
+size_t ab_gemm_scratch_bytes(const ab_mat* m, int rows) { return m ? gemm_scratch_bytes(*m, rows) : 0; }
+
+int ab_gemm(const ab_mat* m, int rows, const void* x, void* y, int epi, const void* resid, void* scratch, void* stream) {
+    AB_CHECK_ARG(m && x && y, "ab_gemm: null pointer");
+    AB_CHECK_ARG(epi >= EPI_NONE && epi <= EPI_RESID && (epi != EPI_RESID || resid), "ab_gemm: bad epilogue");
+    return gemm_launch(*m, rows, (const __half*)x, (__half*)y, epi, (const __half*)resid, scratch, (cudaStream_t)stream);
+}
+
+int ab_dequant(const ab_mat* m, float* out, void* stream) {
+    AB_CHECK_ARG(m, "ab_dequant: null pointer");
+    return dequant_launch(*m, out, (cudaStream_t)stream);
+}
+
+int ab_model_create(const ab_model_desc* desc, ab_model** out) {
+    AB_CHECK_ARG(desc && out && desc->layers, "ab_model_create: null pointer");
+    AB_CHECK_ARG(desc->n_layer > 0 && desc->n_embd > 0 && desc->n_embd % 64 == 0 && desc->vocab > 0,
+                 "ab_model_create: bad shape (n_layer=%d n_embd=%d vocab=%d)", desc->n_layer, desc->n_embd, desc->vocab);
+    AB_CHECK_ARG(desc->emb && desc->lnout_w && desc->lnout_b, "ab_model_create: null top-level tensor");
+    AB_TRY(check_mat(desc->head, "head.weight"));
+    for (int i = 0; i < desc->n_layer; ++i) {
+        const ab_layer& l = desc->layers[i];
+        const ab_mat* big[6] = {&l.receptance, &l.key, &l.value, &l.output, &l.ffn_key, &l.ffn_value};
+        for (const ab_mat* mm : big) AB_TRY(check_mat(*mm, "block matrix"));
+        AB_TRY(check_mat(l.w1t, "w1")); AB_TRY(check_mat(l.a1t, "a1")); AB_TRY(check_mat(l.g1t, "g1"));
+        if (i > 0) AB_TRY(check_mat(l.v1t, "v1"));
+        AB_CHECK_ARG(l.w2 && l.a2 && l.g2 && (i == 0 || l.v2), "ab_model_create: layer %d adapter up-projection missing", i);
+        AB_CHECK_ARG(l.ln1_w && l.ln1_b && l.ln2_w && l.ln2_b && l.x_r && l.x_w && l.x_k && l.x_v && l.x_a && l.x_g &&
+                         l.w0 && l.a0 && l.k_k && l.k_a && l.r_k && l.lnx_w && l.lnx_b && l.ffn_x_k,
+                     "ab_model_create: layer %d has a null vector", i);
+    }
+    ab_model* m = new (std::nothrow) ab_model();
+    AB_CHECK_ARG(m, "ab_model_create: out of host memory");
+    m->d = *desc;
+    m->layers.assign(desc->layers, desc->layers + desc->n_layer);
+    m->d.layers = m->layers.data();
+    *out = m;
+    return OK;
+}
+
+void ab_model_destroy(ab_model* m) { delete m; }
+
+size_t ab_workspace_bytes(const ab_model* m, int B, int T) {
+    if (!m || B <= 0 || T <= 0) return 0;
+    return carve(m, B, T, nullptr).total;
+}
+
+int ab_model_set_option(ab_model* m, const char* name, int value) {
+    AB_CHECK_ARG(m && name, "ab_model_set_option: null pointer");
+    if (!strcmp(name, "stages")) { AB_CHECK_ARG(value >= 2 && value <= 8, "stages must be in [2,8]"); m->stages = value; }
+    else if (!strcmp(name, "pdl")) m->use_pdl = value != 0;
+    else { set_error("unknown option %s", name); return ERR_BAD_ARG; }
+    return OK;
+}
+
+int ab_forward(ab_model* m, int B, int T, const int32_t* tokens, void* const* state, void* workspace, void* logits,
+               int full_output, void* stream) {
+    AB_CHECK_ARG(m && tokens && state && workspace && logits, "ab_forward: null pointer");
+    AB_CHECK_ARG(B > 0 && T > 0, "ab_forward: bad batch shape B=%d T=%d", B, T);
+    AB_CHECK_ARG(((uintptr_t)workspace & 255) == 0, "ab_forward: workspace must be 256-byte aligned");
+    for (int i = 0; i < 3 * m->d.n_layer; ++i) AB_CHECK_ARG(state[i], "ab_forward: state[%d] is null", i);
+    const Workspace ws = carve(m, B, T, (unsigned char*)workspace);
+    if (B == 1 && T == 1) return forward_one(m, tokens, state, ws, (__half*)logits, (cudaStream_t)stream);
+    return forward_rows(m, B, T, tokens, state, ws, (__half*)logits, full_output, (cudaStream_t)stream);
+}
+
+}  // extern "C"

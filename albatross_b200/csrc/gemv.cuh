@@ -1,0 +1,54 @@
+// Parameter blocks of the batch-1 streaming matrix-vector kernel (see gemv.cu).
+#pragma once
+#include "common.cuh"
+
+namespace ab {
+
+enum Fmt : int { FMT_F16 = 0, FMT_I8 = 1, FMT_FP4 = 2 };
+enum Epi : int { EPI_NONE = 0, EPI_TANH = 1, EPI_SIGMOID = 2, EPI_RELU2 = 3, EPI_RESID = 4 };
+
+constexpr int GEMV_MAX_SEG = 7;
+constexpr int GEMV_WARPS = 8;
+constexpr int GEMV_THREADS = GEMV_WARPS * 32;
+constexpr int GEMV_TILE_K = 1024;     // K elements covered by one pipeline stage
+constexpr int GEMV_TILE_BYTES = 4096; // weight bytes of one stage (rows_per_group * row bytes of 1024 k)
+constexpr int GEMV_SCALE_BYTES = 512; // NVFP4 block scales of one stage (8 rows * 64)
+constexpr int GEMV_STAGE_BYTES = GEMV_TILE_BYTES + GEMV_SCALE_BYTES;
+
+// One matrix (a contiguous run of output rows) inside a fused launch.
+struct GemvSeg {
+    const void* w;           // int8 [n,K] | fp16 [n,K] | e2m1 pairs [n,K/2]; rows K-contiguous
+    const void* scale;       // int8: float[n] row scales | NVFP4: e4m3 [n,K/16] | fp16: unused
+    const __half* mix;       // token-shift lerp vector [K], or null: take the (normalised) input as is
+    const float* col_scale;  // optional per-input-column scale folded into x (int8 only)
+    const __half* resid;     // EPI_RESID: vector added to the result (may alias out)
+    __half* out;             // [n]
+    float tscale;            // NVFP4 per-tensor scale, 1 otherwise
+    int fmt, epi, n_rows;
+};
+
+struct GemvParams {
+    GemvSeg seg[GEMV_MAX_SEG];
+    int nseg, K;
+    const __half* x;        // input vector [K] (ignored when emb != null)
+    const __half* emb;      // optional embedding table [V,K]: x = emb[token[0]]
+    const int* token;
+    const __half* x_prev;   // token-shift state [K] (needed when any seg has mix)
+    const __half* ln_w;     // layer-norm weight/bias [K], or null: no normalisation
+    const __half* ln_b;
+    __half* ln_out;         // optional: block 0 stores the normalised input here
+    __half* x_copy;         // optional: block 0 stores the raw input here (embedding row -> residual stream)
+    const __half* copy_src; // optional: block 0 copies copy_n halves to copy_dst (token-shift state hand-over)
+    __half* copy_dst;
+    int copy_n;
+    int stages;             // pipeline depth per warp
+    int use_pdl;            // kernel was launched with programmatic stream serialization
+};
+
+__host__ __device__ inline int gemv_rows_per_group(int fmt) { return fmt == FMT_I8 ? 4 : (fmt == FMT_F16 ? 2 : 8); }
+__host__ __device__ inline int gemv_row_bytes(int fmt, int K) { return fmt == FMT_I8 ? K : (fmt == FMT_F16 ? 2 * K : K / 2); }
+
+size_t gemv_smem_bytes(const GemvParams& p);
+int gemv_launch(const GemvParams& p, cudaStream_t stream);
+
+}  // namespace ab

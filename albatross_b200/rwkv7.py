@@ -1,0 +1,301 @@
+"""Drop-in `RWKV_x070` for the reference model class (reference/rwkv7.py:71-221).
+
+Same constructor argument (`args.MODEL_NAME` without ".pth", `n_layer`, `n_embd`, `head_size`,
+`vocab_size`), same `forward(idx, state, full_output=False)` / `forward_batch(idxs, state,
+full_output=False)` signatures, same state-list layout (3 tensors per layer, reference/rwkv7.py:102-105
+and :122-125) and the same checkpoint key schema. Differences a caller can observe:
+
+  * the big matrices (`att.{receptance,key,value,output}.weight`, `ffn.{key,value}.weight`,
+    `head.weight`) are quantised at load (`quant="int8" | "nvfp4"`, or kept fp16 with `quant=None`);
+    `model.z[...]` holds `PackedMatrix` objects for them (their `numel()` still counts parameters,
+    which is what reference benchmark.py:49-51 reads);
+  * every state tensor is updated IN PLACE (the reference replaces the two x_prev entries and, on
+    the single-token path, the kv entry); the returned list is a new list of the same tensors;
+  * kernels run on the current torch stream (the reference kernel uses the legacy default stream).
+
+All arithmetic runs in the CUDA library bound by `_lib`; there is no PyTorch fallback.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Dict, Iterable, List, Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+
+from . import _lib
+from .quant import PackedMatrix, pack_fp16, quantize
+
+HEAD_SIZE = 64
+DTYPE = torch.half
+_BIG = ("att.receptance.weight", "att.key.weight", "att.value.weight", "att.output.weight",
+        "ffn.key.weight", "ffn.value.weight", "head.weight")
+
+
+def _is_big(name: str) -> bool:
+    return any(name.endswith(s) for s in _BIG)
+
+
+# --------------------------------------------------------------------------------------------
+# Operator-level wrappers (reference/rwkv7.py:37-67)
+# --------------------------------------------------------------------------------------------
+def _wkv(B, T, C_, state, r, w, k, v, a, b):
+    H = C_ // HEAD_SIZE
+    assert HEAD_SIZE == C_ // H
+    assert all(x.dtype == DTYPE for x in [r, w, k, v, a, b])
+    assert all(x.is_contiguous() for x in [r, w, k, v, a, b])
+    assert state.dtype == torch.float32 and state.is_contiguous() and state.is_cuda
+    y = torch.empty_like(r)
+    _lib.check(_lib.lib.ab_wkv7_fwd(B, T, C_, H, state.data_ptr(), r.data_ptr(), w.data_ptr(), k.data_ptr(),
+                                    v.data_ptr(), a.data_ptr(), b.data_ptr(), y.data_ptr(),
+                                    torch.cuda.current_stream().cuda_stream), "ab_wkv7_fwd")
+    return y
+
+
+def RWKV7_OP(state, r, w, k, v, a, b):
+    """WKV-7 over a [T, C] sequence; `state` [H,64,64] fp32 is updated in place (reference/rwkv7.py:37-50)."""
+    T, C_ = r.size()
+    return _wkv(1, T, C_, state, r, w, k, v, a, b)
+
+
+def RWKV7_BATCH_OP(state, r, w, k, v, a, b):
+    """WKV-7 over [B, T, C]; `state` [B,H,64,64] fp32 is updated in place (reference/rwkv7.py:52-67)."""
+    B, T, C_ = r.size()
+    return _wkv(B, T, C_, state, r, w, k, v, a, b)
+
+
+# --------------------------------------------------------------------------------------------
+# Model
+# --------------------------------------------------------------------------------------------
+class RWKV_x070:
+    def __init__(self, args, quant: Optional[str] = "int8", state_dict: Optional[Iterable[Tuple[str, torch.Tensor]]] = None,
+                 device: str = "cuda", use_graph: bool = True):
+        if not torch.cuda.is_available():
+            raise RuntimeError("albatross_b200 needs a CUDA device (sm_100a); there is no CPU path")
+        self.args = args
+        self.n_embd = args.n_embd
+        self.n_layer = args.n_layer
+        self.quant = quant
+        self.device = torch.device(device)
+        self.use_graph = use_graph and os.environ.get("ALBATROSS_NO_GRAPH", "0") != "1"
+
+        items = state_dict
+        if items is None:
+            items = torch.load(args.MODEL_NAME + ".pth", map_location="cpu", mmap=True).items()
+        elif isinstance(items, dict):
+            items = items.items()
+        self.z: Dict[str, object] = {}
+        self._extra: Dict[str, object] = {}
+        ln0 = {}
+        for name, t in items:
+            self._ingest(name, t, ln0)
+        z = self.z
+        self.n_head, self.head_size = self._r_k_shape
+        assert HEAD_SIZE == self.head_size
+        assert self.head_size == args.head_size
+        # ln0 is folded into the embedding table once (reference/rwkv7.py:93)
+        z["emb.weight"] = F.layer_norm(z["emb.weight"], (args.n_embd,), weight=z["blocks.0.ln0.weight"],
+                                       bias=z["blocks.0.ln0.bias"]).contiguous()
+        for s in ("0", "1", "2"):  # layer 0 never uses its v adapter (reference/rwkv7.py:94-96, :239)
+            z["blocks.0.att.v" + s] = z["blocks.0.att.a" + s]
+        self.vocab = z["emb.weight"].shape[0]
+        self._build_native()
+        self._ws: Dict[Tuple[int, int], torch.Tensor] = {}
+        self._graphs: Dict[tuple, tuple] = {}
+        self._tok_pinned = torch.empty(1, dtype=torch.int32).pin_memory()
+
+    # ---- load-time preparation (reference/rwkv7.py:86-96) -----------------------------------
+    def _ingest(self, name: str, t: torch.Tensor, ln0: dict) -> None:
+        dev = self.device
+        if _is_big(name):
+            # storage is [out, in] row-major; the reference views it as [in, out]. Quantise per output row.
+            w = t.to(dev, non_blocking=True)
+            self.z[name] = quantize(w, self.quant)
+            return
+        t = t.to(dev).squeeze().to(DTYPE)
+        if name.endswith("att.r_k"):
+            self._r_k_shape = tuple(t.shape)
+            t = t.flatten()
+        self.z[name] = t.contiguous()
+        # adapter matrices in kernel layout
+        leaf = name.rsplit(".", 1)[-1]
+        if leaf in ("w1", "a1", "v1", "g1"):   # [D, rank] -> rows of [rank, D]
+            self._extra[name + "t"] = pack_fp16(self.z[name].t().contiguous())
+        elif leaf in ("w2", "a2", "v2", "g2"):  # [rank, D] -> rows of [D, rank] for the batched path
+            self._extra[name + "t"] = pack_fp16(self.z[name].t().contiguous())
+
+    def _build_native(self) -> None:
+        z, ex = self.z, self._extra
+        L = self.n_layer
+        self._layers = (_lib.Layer * L)()
+        empty = _lib.Mat()
+        for i in range(L):
+            b, a, f = f"blocks.{i}.", f"blocks.{i}.att.", f"blocks.{i}.ffn."
+            ly = self._layers[i]
+            ptr = lambda key: z[key].data_ptr()
+            ly.ln1_w, ly.ln1_b, ly.ln2_w, ly.ln2_b = ptr(b + "ln1.weight"), ptr(b + "ln1.bias"), ptr(b + "ln2.weight"), ptr(b + "ln2.bias")
+            for c in "rwkvag":
+                setattr(ly, "x_" + c, ptr(a + "x_" + c))
+            for n in ("w0", "a0", "v0", "k_k", "k_a", "r_k"):
+                setattr(ly, n, ptr(a + n))
+            ly.lnx_w, ly.lnx_b, ly.ffn_x_k = ptr(a + "ln_x.weight"), ptr(a + "ln_x.bias"), ptr(f + "x_k")
+            ly.receptance, ly.key = z[a + "receptance.weight"].as_mat(), z[a + "key.weight"].as_mat()
+            ly.value, ly.output = z[a + "value.weight"].as_mat(), z[a + "output.weight"].as_mat()
+            ly.ffn_key, ly.ffn_value = z[f + "key.weight"].as_mat(), z[f + "value.weight"].as_mat()
+            for n in ("w", "a", "v", "g"):
+                if n == "v" and i == 0:
+                    setattr(ly, "v1t", empty)
+                    setattr(ly, "v2t", empty)
+                    ly.v2 = None
+                    continue
+                setattr(ly, n + "1t", ex[a + n + "1t"].as_mat())
+                setattr(ly, n + "2t", ex[a + n + "2t"].as_mat())
+                setattr(ly, n + "2", ptr(a + n + "2"))
+        d = _lib.ModelDesc()
+        d.n_layer, d.n_embd, d.vocab = L, self.n_embd, self.vocab
+        d.emb, d.lnout_w, d.lnout_b = z["emb.weight"].data_ptr(), z["ln_out.weight"].data_ptr(), z["ln_out.bias"].data_ptr()
+        d.head = z["head.weight"].as_mat()
+        d.layers = C.cast(self._layers, C.POINTER(_lib.Layer))
+        self._desc = d
+        h = C.c_void_p()
+        _lib.check(_lib.lib.ab_model_create(C.byref(d), C.byref(h)), "ab_model_create")
+        self._handle = h
+
+    def __del__(self):
+        h = getattr(self, "_handle", None)
+        if h:
+            _lib.lib.ab_model_destroy(h)
+            self._handle = None
+
+    def set_option(self, name: str, value: int) -> None:
+        _lib.check(_lib.lib.ab_model_set_option(self._handle, name.encode(), int(value)), "ab_model_set_option")
+        self._graphs.clear()
+
+    # ---- state ------------------------------------------------------------------------------
+    def new_state(self, batch: Optional[int] = None) -> List[torch.Tensor]:
+        """Zero state in the reference's layout (reference/rwkv7.py:100-105, :120-125)."""
+        args, lead = self.args, (() if batch is None else (batch,))
+        st: List[torch.Tensor] = []
+        for _ in range(args.n_layer):  # state: 0=att_x_prev 1=att_kv 2=ffn_x_prev
+            st.append(torch.zeros(lead + (args.n_embd,), dtype=DTYPE, device=self.device))
+            st.append(torch.zeros(lead + (args.n_embd // args.head_size, args.head_size, args.head_size),
+                                  dtype=torch.float, device=self.device))
+            st.append(torch.zeros(lead + (args.n_embd,), dtype=DTYPE, device=self.device))
+        return st
+
+    def _check_state(self, state: List[torch.Tensor], batch: Optional[int]) -> None:
+        D, H = self.n_embd, self.n_embd // HEAD_SIZE
+        lead = () if batch is None else (batch,)
+        assert len(state) == 3 * self.n_layer, "state must hold 3 tensors per layer"
+        for i, t in enumerate(state):
+            want = lead + ((H, HEAD_SIZE, HEAD_SIZE) if i % 3 == 1 else (D,))
+            dt = torch.float32 if i % 3 == 1 else DTYPE
+            assert tuple(t.shape) == want and t.dtype == dt and t.is_cuda and t.is_contiguous(), \
+                f"state[{i}]: expected {want} {dt} contiguous on CUDA, got {tuple(t.shape)} {t.dtype}"
+
+    def _workspace(self, B: int, T: int) -> torch.Tensor:
+        key = (B, T)
+        ws = self._ws.get(key)
+        if ws is None:
+            n = _lib.lib.ab_workspace_bytes(self._handle, B, T)
+            ws = torch.empty(n + 256, dtype=torch.uint8, device=self.device)
+            self._ws = {k: v for k, v in self._ws.items() if k == (1, 1)}  # keep the decode workspace only
+            self._ws[key] = ws
+        return ws
+
+    def _run(self, B: int, T: int, tokens_dev: torch.Tensor, state: List[torch.Tensor], logits: torch.Tensor,
+             full_output: bool) -> None:
+        ws = self._workspace(B, T)
+        base = (ws.data_ptr() + 255) & ~255
+        ptrs = (C.c_void_p * len(state))(*[t.data_ptr() for t in state])
+        _lib.check(_lib.lib.ab_forward(self._handle, B, T, tokens_dev.data_ptr(), ptrs, base, logits.data_ptr(),
+                                       int(full_output), torch.cuda.current_stream().cuda_stream), "ab_forward")
+
+    # ---- the reference's public entry points ------------------------------------------------
+    def forward(self, idx, state, full_output=False):
+        if state is None:
+            state = self.new_state()
+        if type(idx) is list:
+            if len(idx) > 1:
+                return self.forward_seq(idx, state, full_output)
+            return self.forward_one(idx[0], state)
+        return self.forward_one(idx, state)
+
+    def forward_batch(self, idxs, state, full_output=False):
+        assert type(idxs) is list
+        assert len(set([len(x) for x in idxs])) == 1, 'currently all token inputs in a batch must have the same length'
+        if state is None:
+            state = self.new_state(len(idxs))
+        return self.forward_seq_batch(idxs, state, full_output)
+
+    @torch.no_grad()
+    def forward_one(self, idx: int, state: List[torch.Tensor]):
+        self._check_state(state, None)
+        if not self.use_graph:
+            tok = torch.tensor([int(idx)], dtype=torch.int32, device=self.device)
+            logits = torch.empty(self.vocab, dtype=DTYPE, device=self.device)
+            self._run(1, 1, tok, state, logits, False)
+            return logits, list(state)
+        key = tuple(t.data_ptr() for t in state)
+        entry = self._graphs.get(key)
+        if entry is None:
+            entry = self._capture(state)
+            if len(self._graphs) >= 4:
+                self._graphs.pop(next(iter(self._graphs)))
+            self._graphs[key] = entry
+        graph, tok_dev, logits_buf = entry
+        self._tok_pinned[0] = int(idx)
+        tok_dev.copy_(self._tok_pinned, non_blocking=True)
+        graph.replay()
+        return logits_buf.clone(), list(state)
+
+    def _capture(self, state: List[torch.Tensor]):
+        """Record one decode step (all launches of ab_forward at B=T=1) into a CUDA graph.
+
+        Capture replays nothing: the state is not touched until the first replay. A warm-up step on
+        a scratch copy of the state runs first so that lazy one-time set-up inside the library
+        (function attributes) happens outside the capture."""
+        tok_dev = torch.zeros(1, dtype=torch.int32, device=self.device)
+        logits_buf = torch.empty(self.vocab, dtype=DTYPE, device=self.device)
+        scratch = [t.clone() for t in state]
+        self._run(1, 1, tok_dev, scratch, logits_buf, False)
+        torch.cuda.synchronize()
+        del scratch
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self._run(1, 1, tok_dev, state, logits_buf, False)
+        return graph, tok_dev, logits_buf
+
+    @torch.no_grad()
+    def forward_seq(self, idx: List[int], state: List[torch.Tensor], full_output: bool = False):
+        self._check_state(state, None)
+        T = len(idx)
+        tok = torch.tensor(idx, dtype=torch.int32, device=self.device)
+        logits = torch.empty((T, self.vocab) if full_output else (self.vocab,), dtype=DTYPE, device=self.device)
+        self._run(1, T, tok, state, logits, full_output)
+        return logits, list(state)
+
+    @torch.no_grad()
+    def forward_seq_batch(self, idxs: List[List[int]], state: List[torch.Tensor], full_output: bool = False):
+        B, T = len(idxs), len(idxs[0])
+        self._check_state(state, B)
+        tok = torch.tensor(idxs, dtype=torch.int32, device=self.device)
+        shape = (B, T, self.vocab) if full_output else (B, self.vocab)
+        logits = torch.empty(shape, dtype=DTYPE, device=self.device)
+        self._run(B, T, tok, state, logits, full_output)
+        return logits, list(state)
+
+    # ---- bookkeeping for benchmarks ---------------------------------------------------------
+    def weight_bytes(self, include_emb: bool = False) -> int:
+        """Bytes a decode step streams: every tensor except the embedding table (cf. benchmark.py:47-52)."""
+        n = 0
+        for k, v in self.z.items():
+            if "emb" in k and not include_emb:
+                continue
+            if k.startswith("blocks.0.att.v") and k[-2:] in ("v0", "v1", "v2"):
+                continue
+            if "ln0" in k:
+                continue
+            n += v.nbytes() if isinstance(v, PackedMatrix) else v.numel() * v.element_size()
+        return n

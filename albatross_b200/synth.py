@@ -19,7 +19,7 @@ HEAD = 64
 
 CONFIGS = {
     # name: (n_layer, n_embd, vocab, (rank_w, rank_a, rank_v, rank_g))
-    "tiny": (2, 128, 256, (32, 32, 16, 32)),
+    "tiny": (2, 256, 512, (32, 32, 16, 48)),
     "0.1b": (12, 768, 65536, (64, 64, 32, 128)),
     "7.2b": (32, 4096, 65536, (128, 128, 96, 480)),
 }

@@ -1,0 +1,297 @@
+#!/usr/bin/env python
+"""Decode benchmark for the RWKV-7 quantised-weight hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload decode_bsz1_int8|decode_bsz320_nvfp4] [--model 7.2b|0.1b|tiny]
+
+One "step" is one decode step of the whole model (every matrix product of the 32 blocks, the WKV-7
+state update between them and the vocabulary head) for the workload's batch. Weights are random
+(seeded, reference checkpoint schema), since trained checkpoints are not available offline.
+
+Prints ONE JSON line. `value` is device-timed (CUDA events, inputs resident in HBM, CUDA-graph
+replay of the library's launches); `e2e` goes through the public `RWKV_x070.forward[_batch]` call with
+host token ids (pinned host -> device) and reads the logits back to the host every step.
+`--impl reference` times the CPU restatement of the reference's PyTorch path (oracle/) on the host
+cores on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    "decode_bsz1_int8": dict(batch=1, quant="int8"),
+    "decode_bsz320_nvfp4": dict(batch=320, quant="nvfp4"),
+}
+METRIC = "rwkv7_decode_tokens_per_s"
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), float(d.get("bf16_tflops_sustained", d.get("bf16_tflops", 1590.0))), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.idx)], stdout=subprocess.PIPE, text=True)
+            self.t = threading.Thread(target=lambda: [self.lines.append(l) for l in self.proc.stdout], daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        self.t.join(timeout=2)
+        sm, mx, reasons = [], [], set()
+        for l in self.lines:
+            f = [x.strip() for x in l.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def algorithmic_bytes(model, batch: int) -> dict:
+    """Bytes one decode step must move: every weight once, the kv state read + written, the WKV vectors."""
+    L, D = model.n_layer, model.n_embd
+    H = D // 64
+    weights = model.weight_bytes()
+    kv = batch * L * H * (2 * 64 * 64 * 4 + 7 * 64 * 2)
+    return {"weights": weights, "kv_state": kv, "total": weights + kv}
+
+
+# ----------------------------------------------------------------------------------------------
+# our arm
+# ----------------------------------------------------------------------------------------------
+def run_ours(a, rank, world, dev):
+    from albatross_b200 import RWKV_x070, synth
+    wl = WORKLOADS[a.workload]
+    B = a.batch or wl["batch"]
+    args = synth.make_args(a.model)
+    torch.cuda.set_device(dev)
+    model = RWKV_x070(args, quant=wl["quant"], state_dict=synth.iter_checkpoint(a.model, seed=0, device=f"cuda:{dev}"),
+                      device=f"cuda:{dev}")
+    if a.stages:
+        model.set_option("stages", a.stages)
+    if a.no_pdl:
+        model.set_option("pdl", 0)
+    V = args.vocab_size
+    g = torch.Generator().manual_seed(1000 + rank)
+    n_tok = a.warmup + a.steps + 8
+    toks = torch.randint(0, V, (n_tok, B), generator=g)
+    launches_per_step = 5 * args.n_layer + 1
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], device=f"cuda:{dev}")
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- e2e: the public call, host token ids in, logits back on the host, every step
+    pinned_logits = torch.empty((B, V) if B > 1 else (V,), dtype=torch.float16).pin_memory()
+    state = model.new_state(B if B > 1 else None)
+
+    def e2e_step(i):
+        nonlocal state
+        if B == 1:
+            logits, state = model.forward(int(toks[i, 0]), state)
+        else:
+            logits, state = model.forward_batch([[int(t)] for t in toks[i]], state)
+        pinned_logits.copy_(logits, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for i in range(a.warmup):
+        e2e_step(i)
+    sync_all()
+    t0 = time.perf_counter()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(a.warmup, a.warmup + a.steps):
+        e2e_step(i)
+    e1.record()
+    sync_all()
+    e2e_ms = max_over_ranks(max(e0.elapsed_time(e1), (time.perf_counter() - t0) * 1e3 * 0.0))
+    e2e_val = world * B * a.steps / (e2e_ms * 1e-3)
+
+    # ---- device-timed: token ids resident, one CUDA graph replay per step, events on the launch stream
+    state = model.new_state(B if B > 1 else None)
+    tok_dev = toks.to(torch.int32).to(f"cuda:{dev}")
+    if B == 1:
+        model.forward(0, state)                     # captures the graph for this state
+        graph, tok_buf, logits_buf = next(iter(model._graphs.values()))
+        step_fn = lambda i: (tok_buf.copy_(tok_dev[i]), graph.replay())
+    else:
+        cur = torch.zeros(B, dtype=torch.int32, device=f"cuda:{dev}")
+        logits_buf = torch.empty(B, V, dtype=torch.float16, device=f"cuda:{dev}")
+        step_fn = lambda i: (cur.copy_(tok_dev[i]), model._run(B, 1, cur, state, logits_buf, False))
+    for i in range(a.warmup):
+        step_fn(i)
+    sync_all()
+    sampler = ClockSampler(dev)
+    sampler.start()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(a.steps + 1)]
+    ev[0].record()
+    for i in range(a.steps):
+        step_fn(a.warmup + i)
+        ev[i + 1].record()
+    sync_all()
+    clocks = sampler.stop()
+    per_step = np.array([ev[i].elapsed_time(ev[i + 1]) for i in range(a.steps)])
+    total_ms = max_over_ranks(ev[0].elapsed_time(ev[-1]))
+    value = world * B * a.steps / (total_ms * 1e-3)
+
+    from albatross_b200 import _lib
+    status = _lib.device_status()
+    hbm, tf, which = measured_peaks()
+    ab = algorithmic_bytes(model, B)
+    ms_step = total_ms / a.steps
+    achieved = ab["total"] / (ms_step * 1e-3) / 1e9
+    out = {
+        "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
+        "ms_per_step": ms_step, "ms_per_step_p10": float(np.percentile(per_step, 10)),
+        "ms_per_step_p50": float(np.percentile(per_step, 50)),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int8 weights (dp4a, exact int32 sums), fp16 activations, fp32 WKV state" if wl["quant"] == "int8"
+        else "nvfp4 weights, fp16 activations, fp32 accumulate and WKV state",
+        "data": "synthetic (seeded random weights in the reference checkpoint schema, random token ids)",
+        "config": {"workload": a.workload, "model": a.model, "batch_per_gpu": B, "n_layer": args.n_layer,
+                   "n_embd": args.n_embd, "vocab": V, "sharding": "independent sequences per GPU, no collective in the step",
+                   "l2": "inputs larger than L2: %.2f GB of weights streamed per step" % (ab["weights"] / 1e9)},
+        "e2e": {"value": e2e_val, "unit": "tokens/s", "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 2 * B * V,
+                "ms_per_step": e2e_ms / a.steps},
+        "gpu_launches": launches_per_step * a.steps,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s", "frac": achieved / hbm,
+                     "traffic": None, "peak_source": which,
+                     "kernel": "gemv_stream_kernel (%d of the %d launches of a step; achieved = all algorithmic bytes "
+                               "of the step / step time, so the other launches' time is charged to it)" %
+                               (4 * args.n_layer + 1, launches_per_step),
+                     "algorithmic_bytes_per_step": ab},
+        "clocks": clocks, "device_status": status,
+    }
+    return out
+
+
+# ----------------------------------------------------------------------------------------------
+# CPU arm: the oracle's restatement of the reference's PyTorch path on the host cores
+# ----------------------------------------------------------------------------------------------
+def run_cpu(a, n_layers_sample: int = 2, steps: int = 6):
+    """Times the single-token path (the only one that is pure torch in the reference) in fp32.
+
+    A 7.2B fp32 checkpoint is 28 GB, so the sample is `n_layers_sample` blocks plus the vocabulary head
+    at the workload's shapes; per-block time is extrapolated to the full depth."""
+    from albatross_b200 import synth
+    from oracle.rwkv7_oracle import Oracle, new_state, prepare
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    L, D, V, ranks = synth.CONFIGS[a.model]
+    Ls = min(L, n_layers_sample)
+    raw = synth.make_checkpoint((Ls, D, V, ranks), seed=0)
+    z = prepare(raw, D, torch.float32)
+    o = Oracle(z, Ls, D)
+    st = new_state(Ls, D)
+    toks = torch.randint(0, V, (steps + 2,), generator=torch.Generator().manual_seed(0)).tolist()
+    # head-only time: a zero-block model
+    o0 = Oracle(z, 0, D)
+    ts_full, ts_head = [], []
+    for i, t in enumerate(toks):
+        t0 = time.perf_counter(); o.step(t, st); t1 = time.perf_counter()
+        o0.step(t, []); t2 = time.perf_counter()
+        if i >= 2:
+            ts_full.append(t1 - t0); ts_head.append(t2 - t1)
+    t_head = float(np.percentile(ts_head, 10))
+    t_block = (float(np.percentile(ts_full, 10)) - t_head) / Ls
+    t_token = t_block * L + t_head
+    B = a.batch or WORKLOADS[a.workload]["batch"]
+    return {"value": 1.0 / t_token, "unit": "tokens/s", "cores": cores, "kind": "port",
+            "sample": f"{Ls} of {L} blocks + head at {a.model} shapes, fp32 torch single-token path, {steps} steps, p10, "
+                      f"extrapolated to {L} blocks; bsz {B} on the CPU = this rate (sequences run one after another)"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="decode_bsz1_int8", choices=sorted(WORKLOADS))
+    ap.add_argument("--model", default="7.2b")
+    ap.add_argument("--batch", type=int, default=0)
+    ap.add_argument("--stages", type=int, default=0)
+    ap.add_argument("--no-pdl", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    a = ap.parse_args()
+    a.warmup = max(a.warmup, 3)
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if a.impl == "reference":
+        if rank != 0:
+            return
+        cb = run_cpu(a)
+        B = a.batch or WORKLOADS[a.workload]["batch"]
+        print(json.dumps({
+            "impl": "reference", "metric": METRIC, "value": cb["value"], "unit": "tokens/s", "n_gpus": a.gpus,
+            "steps": a.steps, "warmup": a.warmup, "ms_per_step": 1e3 / cb["value"], "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "fp32 (CPU)", "data": "synthetic",
+            "config": {"workload": a.workload, "model": a.model, "batch_per_gpu": B},
+            "cpu_baseline": cb,
+            "e2e": {"value": cb["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+        return
+
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local)
+        torch.distributed.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
+    out = run_ours(a, rank, world, local)
+    if rank == 0:
+        if world == 1 and not a.no_cpu_baseline:
+            out["cpu_baseline"] = run_cpu(a)
+        print(json.dumps(out))
+    if world > 1:
+        torch.distributed.barrier()
+        torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,124 @@
+/*
+ * albatross_b200 — C ABI of the sm_100a kernels for the RWKV-7 decode hot path.
+ *
+ * Plain pointers and sizes only; every pointer is a DEVICE pointer unless said otherwise; `stream`
+ * is a cudaStream_t passed as void*. Every function returns 0 on success and a negative code
+ * otherwise (AB_ERR_*); ab_last_error() gives the message of the calling thread's last failure.
+ * Kernels are asynchronous on `stream`; nothing here allocates device memory.
+ *
+ * Each entry point names the reference interface it replaces (paths inside the reference project).
+ */
+#ifndef ALBATROSS_B200_H
+#define ALBATROSS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define AB_OK 0
+#define AB_ERR_BAD_ARG (-1)
+#define AB_ERR_CUDA (-2)
+#define AB_ERR_TOO_LARGE (-3)
+#define AB_ERR_DEVICE_WAIT (-4)
+
+/* weight formats */
+#define AB_FMT_F16 0   /* fp16 rows                                                        */
+#define AB_FMT_I8 1    /* int8 rows + fp32 scale per output row (+ optional per-input scale) */
+#define AB_FMT_FP4 2   /* NVFP4: e2m1 pairs, e4m3 scale per 16 inputs, fp32 tensor scale     */
+
+/* A weight matrix in the reference's storage order: [n_out, k] row-major, i.e. nn.Linear's
+ * [out, in] storage that reference/rwkv7.py:88-90 views transposed. */
+typedef struct ab_mat {
+    int32_t fmt, n_out, k, _pad;
+    const void* w;          /* int8 [n_out,k] | fp16 [n_out,k] | uint8 [n_out,k/2] (even k in the low nibble) */
+    const void* scale;      /* I8: float [n_out] | FP4: uint8 e4m3 [n_out,k/16] | F16: NULL */
+    const float* col_scale; /* I8 only, optional float [k]: W ~= q * row_scale * col_scale */
+    float tscale;           /* FP4 tensor scale (1.0f otherwise) */
+    float _pad2;
+} ab_mat;
+
+/* One RWKV-7 block. Vectors are fp16 [n_embd]; names follow the checkpoint keys read at
+ * reference/rwkv7.py:142-152. Adapter down-projections are stored TRANSPOSED ([rank, n_embd],
+ * fp16, AB_FMT_F16 mats) so that they stream like any other output row; up-projections keep the
+ * checkpoint layout [rank, n_embd]. */
+typedef struct ab_layer {
+    const void *ln1_w, *ln1_b, *ln2_w, *ln2_b;
+    const void *x_r, *x_w, *x_k, *x_v, *x_a, *x_g;
+    const void *w0, *a0, *v0, *k_k, *k_a, *r_k, *lnx_w, *lnx_b;
+    const void* ffn_x_k;
+    ab_mat receptance, key, value, output, ffn_key, ffn_value;
+    ab_mat w1t, a1t, v1t, g1t;
+    const void *w2, *a2, *v2, *g2;
+    /* batched path: the four up-projections as [n_embd, rank] fp16 AB_FMT_F16 mats (may be empty at batch 1) */
+    ab_mat w2t, a2t, v2t, g2t;
+} ab_layer;
+
+typedef struct ab_model_desc {
+    int32_t n_layer, n_embd, vocab, _pad;
+    const void* emb;              /* fp16 [vocab, n_embd], ln0 already folded in (reference/rwkv7.py:93) */
+    const void *lnout_w, *lnout_b;
+    ab_mat head;
+    const ab_layer* layers;       /* HOST array of n_layer entries; copied by ab_model_create */
+} ab_model_desc;
+
+typedef struct ab_model ab_model;
+
+/* ---- diagnostics ------------------------------------------------------------------------- */
+const char* ab_last_error(void);
+int ab_version(void);
+/* Reads and clears the device-side status word (non-zero: a bounded device wait gave up).
+ * Synchronises the device. Host pointer. */
+int ab_device_status(uint32_t* status_host);
+
+/* ---- WKV-7 state update -------------------------------------------------------------------
+ * Replaces torch.ops.rwkv7_state_fwd_fp16.forward(B,T,C,H,state,r,w,k,v,a,b,y)
+ * (reference/cuda/rwkv7_state_fwd_fp16.cpp:8-14; kernel reference/cuda/rwkv7_state_fwd_fp16.cu:7-62).
+ * state fp32 [B,H,64,64] updated in place; r,w,k,v,a,b,y fp16 [B,T,C]; w is the pre-transform decay
+ * (the kernel applies exp(-exp(w))). Unlike the reference it launches on `stream`, not the legacy stream. */
+int ab_wkv7_fwd(int B, int T, int C, int H, float* state, const void* r, const void* w, const void* k,
+                const void* v, const void* a, const void* b, void* y, void* stream);
+
+/* ---- batch-1 matrix-vector products -------------------------------------------------------
+ * Replace the fp16 `x @ W` call sites at batch 1 (reference/rwkv7.py:230,232,233,250,308,309,156)
+ * with de-quantisation fused into the product. x fp16 [k], y fp16 [n_out]. */
+int ab_gemv(const ab_mat* m, const void* x, void* y, void* stream);
+
+/* ---- batched matrix products (tensor cores) -----------------------------------------------
+ * Replace the `[B,T,D] @ W` call sites of the batch path (reference/rwkv7.py:283,285,286,300,322,323,220).
+ * x fp16 [rows, k] row-major, y fp16 [rows, n_out]; epi is one of AB_EPI_*; resid (fp16 [rows,n_out])
+ * is added when epi == AB_EPI_RESID and may alias y. `scratch` holds at least
+ * ab_gemm_scratch_bytes(m, rows) bytes. */
+#define AB_EPI_NONE 0
+#define AB_EPI_TANH 1
+#define AB_EPI_SIGMOID 2
+#define AB_EPI_RELU2 3
+#define AB_EPI_RESID 4
+size_t ab_gemm_scratch_bytes(const ab_mat* m, int rows);
+int ab_gemm(const ab_mat* m, int rows, const void* x, void* y, int epi, const void* resid, void* scratch,
+            void* stream);
+
+/* ---- de-quantisation dump (parity checks) ---------------------------------------------------
+ * Writes the kernels' in-register de-quantised weights as fp32 [n_out,k] (tensor/row/column scales applied). */
+int ab_dequant(const ab_mat* m, float* out, void* stream);
+
+/* ---- whole-model forward -------------------------------------------------------------------
+ * ab_forward replaces RWKV_x070.forward / forward_batch (reference/rwkv7.py:98-126, :128-221):
+ * tokens int32 [B,T] on the device; state = HOST array of 3*n_layer device pointers laid out as
+ * reference/rwkv7.py:102-105 / :122-125 ([3i] fp16 [B,D], [3i+1] fp32 [B,H,64,64], [3i+2] fp16 [B,D]),
+ * all updated in place; logits fp16 [B,V] (or [B,T,V] when full_output). `workspace` holds at
+ * least ab_workspace_bytes(model, B, T) bytes and is scratch. */
+int ab_model_create(const ab_model_desc* desc, ab_model** out);
+void ab_model_destroy(ab_model* m);
+size_t ab_workspace_bytes(const ab_model* m, int B, int T);
+int ab_forward(ab_model* m, int B, int T, const int32_t* tokens, void* const* state, void* workspace,
+               void* logits, int full_output, void* stream);
+/* Tuning knobs: pipeline depth of the streaming kernels and programmatic dependent launch (default on). */
+int ab_model_set_option(ab_model* m, const char* name, int value);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ALBATROSS_B200_H */

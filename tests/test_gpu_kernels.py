@@ -1,0 +1,129 @@
+"""GPU: each kernel through the C ABI against the CPU oracle on the same seeded inputs."""
+import ctypes as C
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import GOLDEN, rel_err
+from oracle import quant_oracle as qo
+from oracle.rwkv7_oracle import Oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _gemv(pm, x):
+    from albatross_b200 import _lib
+    y = torch.empty(pm.n_out, dtype=torch.float16, device="cuda")
+    mat = pm.as_mat()
+    _lib.check(_lib.lib.ab_gemv(C.byref(mat), x.data_ptr(), y.data_ptr(), _stream()), "ab_gemv")
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    return y
+
+
+@pytest.mark.parametrize("fmt", ["int8", "nvfp4"])
+@pytest.mark.parametrize("shape", [(64, 256), (100, 768), (257, 4096)])
+def test_dequantised_weights_bit_exact(fmt, shape):
+    """The kernels' in-register de-quantisation equals the specification bit for bit."""
+    from albatross_b200 import quant
+    torch.manual_seed(3)
+    w = torch.randn(*shape) * 0.02
+    w[1] = 0
+    pm = quant.quantize(w.cuda(), fmt)
+    want = qo.fake_quantize(w.numpy(), fmt)
+    got = pm.dequantize().cpu().numpy()
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+def test_int8_col_scale_dequant_bit_exact():
+    from albatross_b200 import quant
+    torch.manual_seed(4)
+    w = torch.randn(64, 512) * 0.02
+    c = qo.int8_col_scale(w.numpy())
+    pm = quant.quantize_int8(w.cuda(), torch.from_numpy(c).cuda())
+    q, s = qo.int8_quantize(w.numpy(), c)
+    assert np.array_equal(pm.w.cpu().numpy(), q)
+    assert np.array_equal(pm.dequantize().cpu().numpy(), qo.int8_dequantize(q, s, c))
+
+
+def test_gemv_int8_config1_against_reference_fixture():
+    """Baseline config 1: x fp16 [1,4096] ~N(0,1), W fp16 [4096,4096] ~N(0,0.02), seed 0."""
+    from albatross_b200 import quant
+    g = np.load(os.path.join(GOLDEN, "gemv_int8_4096.npz"))
+    torch.manual_seed(0)
+    x = torch.randn(1, 4096).half()
+    w = (torch.randn(4096, 4096) * 0.02).half()
+    pm = quant.quantize_int8(w.cuda())
+    y = _gemv(pm, x.cuda().view(-1)).float().cpu().numpy()
+    assert rel_err(y, g["y"][0]) < 2e-3          # fp16 output rounding; the integer sums are exact
+    c = torch.from_numpy(qo.int8_col_scale(w.float().numpy())).cuda()
+    pm2 = quant.quantize_int8(w.cuda(), c)
+    y2 = _gemv(pm2, x.cuda().view(-1)).float().cpu().numpy()
+    assert rel_err(y2, g["y_colscale"][0]) < 2e-3
+
+
+@pytest.mark.parametrize("fmt", ["int8", "nvfp4", "none"])
+@pytest.mark.parametrize("n,k", [(8, 256), (61, 768), (4096, 1024), (1000, 16384), (5, 3072)])
+def test_gemv_against_oracle(fmt, n, k):
+    """Ragged row counts (not a multiple of the rows per warp), K not a multiple of the 1024 tile."""
+    from albatross_b200 import quant
+    torch.manual_seed(n * 31 + k)
+    w = torch.randn(n, k) * 0.02
+    x = torch.randn(k).half()
+    x[::97] *= 30                                    # activation outliers
+    pm = quant.quantize(w.cuda(), None if fmt == "none" else fmt)
+    wq = qo.fake_quantize(w.half().float().numpy() if fmt == "none" else w.numpy(), fmt)
+    want = wq.astype(np.float64) @ x.double().numpy()
+    got = _gemv(pm, x.cuda()).float().cpu().numpy()
+    assert rel_err(got, want) < 3e-3
+
+
+def test_gemv_zero_and_linearity():
+    from albatross_b200 import quant
+    torch.manual_seed(9)
+    w = torch.randn(512, 1024) * 0.02
+    pm = quant.quantize_int8(w.cuda())
+    z = _gemv(pm, torch.zeros(1024, dtype=torch.float16, device="cuda"))
+    assert torch.count_nonzero(z) == 0
+    x = torch.randn(1024).half().cuda()
+    y1 = _gemv(pm, x).float()
+    y2 = _gemv(pm, (x * 2)).float()                  # scaling by 2 is exact in fp16 and in the fixed-point split
+    assert torch.equal(y2, y1 * 2)
+
+
+@pytest.mark.parametrize("B,T,H", [(1, 1, 2), (3, 1, 4), (2, 7, 2), (1, 33, 1)])
+def test_wkv7_operator_against_oracle(B, T, H):
+    """Same contract as the reference operator: state updated in place, y returned."""
+    from albatross_b200 import RWKV7_BATCH_OP, RWKV7_OP
+    torch.manual_seed(B * 100 + T)
+    Cn = H * 64
+    f = lambda s=1.0: (torch.randn(B, T, Cn) * s).half()
+    r, k, v = f(), f(), f()
+    w = (-torch.nn.functional.softplus(-torch.randn(B, T, Cn)) - 0.5).half()
+    kk = torch.nn.functional.normalize(torch.randn(B, T, H, 64), dim=-1).view(B, T, Cn).half()
+    a, b = -kk, (kk * torch.sigmoid(torch.randn(B, T, Cn)).half())
+    S0 = torch.randn(B, H, 64, 64) * 0.1
+    S_ref = S0.clone()
+    y_ref = Oracle.wkv7_kernel(S_ref, r, w, k, v, a, b)
+    S = S0.clone().cuda()
+    dev = [t.cuda().contiguous() for t in (r, w, k, v, a, b)]
+    y = RWKV7_BATCH_OP(S, *dev)
+    torch.cuda.synchronize()
+    assert rel_err(y.float().cpu(), y_ref.float()) < 2e-3
+    assert rel_err(S.cpu(), S_ref) < 1e-4
+    if B == 1:                                        # the unbatched wrapper takes [T,C] and [H,64,64]
+        S1 = S0[0].clone().cuda()
+        y1 = RWKV7_OP(S1, *[t[0].contiguous() for t in dev])
+        assert torch.equal(y1, y[0]) and torch.equal(S1, S[0])
+
+
+def test_wkv7_operator_rejects_bad_shapes():
+    from albatross_b200 import _lib
+    assert _lib.lib.ab_wkv7_fwd(1, 1, 96, 2, 16, 16, 16, 16, 16, 16, 16, 16, None) == -1
+    assert b"C == H*64" in _lib.lib.ab_last_error()
