@@ -92,16 +92,15 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_stream_kernel(const __gr
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + off) + warp * S;
     off += (size_t)GEMV_WARPS * S * 8;
     off = (off + 127) & ~(size_t)127;
-    signed char* xh = reinterpret_cast<signed char*>(smem + off);
-    off += Kp;
-    unsigned char* xl = smem + off;
-    off += Kp;
-    __half* xf = reinterpret_cast<__half*>(smem + off);
-    off += (size_t)Kp * 2;
     __half* xn = reinterpret_cast<__half*>(smem + off);
     off += (size_t)Kp * 2;
+    signed char* xh = reinterpret_cast<signed char*>(smem + off);
+    unsigned char* xl = smem + off + Kp;
+    if (p.smem_flags & 1) off += (size_t)Kp * 2;
+    __half* xf = reinterpret_cast<__half*>(smem + off);
+    if (p.smem_flags & 2) off += (size_t)Kp * 2;
     __half* dx = reinterpret_cast<__half*>(smem + off);
-    off += (size_t)Kp * 2;
+    if (p.smem_flags & 4) off += (size_t)Kp * 2;
     float* sx = reinterpret_cast<float*>(smem + off);
     off += (size_t)(Kp / 512) * 4;
     float* red = reinterpret_cast<float*>(smem + off);
@@ -183,7 +182,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_stream_kernel(const __gr
             if (p.ln_out && blockIdx.x == 0) p.ln_out[i] = hv;
         }
     }
-    if (p.x_prev) {
+    if (p.smem_flags & 4) {
         __syncthreads();
         for (int i = tid; i < K; i += GEMV_THREADS)
             dx[i] = __float2half_rn(__half2float(p.x_prev[i]) - __half2float(xn[i]));
@@ -378,7 +377,11 @@ size_t gemv_smem_bytes(const GemvParams& p) {
     const size_t Kp = ((size_t)p.K + 511) & ~(size_t)511;
     size_t off = (size_t)GEMV_WARPS * p.stages * GEMV_STAGE_BYTES + (size_t)GEMV_WARPS * p.stages * 8;
     off = (off + 127) & ~(size_t)127;
-    off += Kp * 2 + Kp * 2 * 3 + (Kp / 512) * 4 + 64 * 4;
+    off += Kp * 2;
+    if (p.smem_flags & 1) off += Kp * 2;
+    if (p.smem_flags & 2) off += Kp * 2;
+    if (p.smem_flags & 4) off += Kp * 2;
+    off += (Kp / 512) * 4 + 64 * 4;
     return off;
 }
 
@@ -387,8 +390,10 @@ int gemv_launch(const GemvParams& p_in, cudaStream_t stream) {
     AB_CHECK_ARG(p.nseg >= 1 && p.nseg <= GEMV_MAX_SEG, "gemv: nseg %d out of range", p.nseg);
     AB_CHECK_ARG(p.K >= 16 && p.K % 16 == 0 && p.K <= 32768, "gemv: K=%d must be a multiple of 16 in [16, 32768]", p.K);
     int groups = 0;
+    p.smem_flags = 0;
     for (int s = 0; s < p.nseg; ++s) {
         const GemvSeg& g = p.seg[s];
+        p.smem_flags |= (g.fmt == FMT_I8 ? 1 : 2) | (g.mix ? 4 : 0);
         AB_CHECK_ARG(g.w && g.out && g.n_rows > 0, "gemv: segment %d has a null pointer or no rows", s);
         AB_CHECK_ARG(((uintptr_t)g.w & 15) == 0, "gemv: segment %d weights not 16-byte aligned", s);
         AB_CHECK_ARG(g.fmt == FMT_F16 || g.scale, "gemv: segment %d needs scales", s);
@@ -399,6 +404,7 @@ int gemv_launch(const GemvParams& p_in, cudaStream_t stream) {
         groups += (g.n_rows + R - 1) / R;
     }
     AB_CHECK_ARG(p.emb || p.x, "gemv: no input vector");
+    AB_CHECK_ARG(!(p.smem_flags & 4) || p.x_prev, "gemv: token-shift state missing");
     if (p.stages <= 0) p.stages = 4;
     static int n_sm = 0;
     static size_t max_smem = 0;

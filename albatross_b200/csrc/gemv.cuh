@@ -41,6 +41,7 @@ struct GemvParams {
     const __half* copy_src; // optional: block 0 copies copy_n halves to copy_dst (token-shift state hand-over)
     __half* copy_dst;
     int copy_n;
+    int smem_flags;         // filled by gemv_launch: 1 = int8 rows, 2 = fp16/NVFP4 rows, 4 = token-shift lerp
     int stages;             // pipeline depth per warp
     int use_pdl;            // kernel was launched with programmatic stream serialization
 };
