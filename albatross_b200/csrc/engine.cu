@@ -53,6 +53,7 @@ struct ab_model {
     std::vector<ab_layer> layers;
     int stages = 4;
     int use_pdl = 1;
+    int debug_sync = 0;  // synchronise after every launch and name the one that failed
 };
 
 namespace {
@@ -100,6 +101,19 @@ Workspace carve(const ab_model* m, int B, int T, unsigned char* base) {
         if (_s != OK) return _s;    \
     } while (0)
 
+// Launch + optional post-launch synchronisation that names the failing step.
+#define AB_STEP(m, st, layer, what, call)                                                          \
+    do {                                                                                           \
+        AB_TRY(call);                                                                              \
+        if ((m)->debug_sync) {                                                                     \
+            cudaError_t _e = cudaStreamSynchronize(st);                                            \
+            if (_e != cudaSuccess) {                                                               \
+                set_error("layer %d, %s: %s", (layer), (what), cudaGetErrorString(_e));            \
+                return ERR_CUDA;                                                                   \
+            }                                                                                      \
+        }                                                                                          \
+    } while (0)
+
 int forward_one(ab_model* m, const int32_t* token, void* const* state, const Workspace& ws, __half* logits,
                 cudaStream_t st) {
     const int D = m->d.n_embd, H = D / HEAD;
@@ -123,7 +137,7 @@ int forward_one(ab_model* m, const int32_t* token, void* const* state, const Wor
             if (i > 0) p.seg[n++] = seg_of(L.v1t, L.x_v, EPI_NONE, ws.hv);
             p.seg[n++] = seg_of(L.g1t, L.x_g, EPI_SIGMOID, ws.hg);
             p.nseg = n;
-            AB_TRY(gemv_launch(p, st));
+            AB_STEP(m, st, i, "rkv+adapter-down gemv", gemv_launch(p, st));
         }
         {   // per-head: adapter up-projections, glue, WKV state update, group norm, bonus, gate
             HeadParams h = {};
@@ -136,34 +150,35 @@ int forward_one(ab_model* m, const int32_t* token, void* const* state, const Wor
             h.k_k = (const __half*)L.k_k; h.k_a = (const __half*)L.k_a; h.r_k = (const __half*)L.r_k;
             h.lnx_w = (const __half*)L.lnx_w; h.lnx_b = (const __half*)L.lnx_b;
             h.out = ws.att; h.copy_src = ws.xn; h.copy_dst = att_prev; h.use_pdl = m->use_pdl;
-            AB_TRY(head_launch(h, st));
+            AB_STEP(m, st, i, "head kernel", head_launch(h, st));
         }
         {   // output projection + residual
             GemvParams p = {};
             p.K = D; p.stages = m->stages; p.use_pdl = m->use_pdl; p.x = ws.att; p.nseg = 1;
             p.seg[0] = seg_of(L.output, nullptr, EPI_RESID, ws.x, ws.x);
-            AB_TRY(gemv_launch(p, st));
+            AB_STEP(m, st, i, "output gemv", gemv_launch(p, st));
         }
         {   // LN2 + shift-lerp + ffn key + relu^2
             GemvParams p = {};
             p.K = D; p.stages = m->stages; p.use_pdl = m->use_pdl; p.x = ws.x; p.nseg = 1;
             p.x_prev = ffn_prev; p.ln_w = (const __half*)L.ln2_w; p.ln_b = (const __half*)L.ln2_b; p.ln_out = ws.xn2;
             p.seg[0] = seg_of(L.ffn_key, L.ffn_x_k, EPI_RELU2, ws.kf);
-            AB_TRY(gemv_launch(p, st));
+            AB_STEP(m, st, i, "ffn key gemv", gemv_launch(p, st));
         }
         {   // ffn value + residual; hands the new channel-mix token-shift state over
             GemvParams p = {};
             p.K = 4 * D; p.stages = m->stages; p.use_pdl = m->use_pdl; p.x = ws.kf; p.nseg = 1;
             p.seg[0] = seg_of(L.ffn_value, nullptr, EPI_RESID, ws.x, ws.x);
             p.copy_src = ws.xn2; p.copy_dst = ffn_prev; p.copy_n = D;
-            AB_TRY(gemv_launch(p, st));
+            AB_STEP(m, st, i, "ffn value gemv", gemv_launch(p, st));
         }
     }
     GemvParams p = {};
     p.K = D; p.stages = m->stages; p.use_pdl = m->use_pdl; p.x = ws.x; p.nseg = 1;
     p.ln_w = (const __half*)m->d.lnout_w; p.ln_b = (const __half*)m->d.lnout_b;
     p.seg[0] = seg_of(m->d.head, nullptr, EPI_NONE, logits);
-    return gemv_launch(p, st);
+    AB_STEP(m, st, -1, "head gemv", gemv_launch(p, st));
+    return OK;
 }
 
 int forward_rows(ab_model* m, int B, int T, const int32_t* tokens, void* const* state, const Workspace& ws,
@@ -301,6 +316,7 @@ int ab_model_set_option(ab_model* m, const char* name, int value) {
     AB_CHECK_ARG(m && name, "ab_model_set_option: null pointer");
     if (!strcmp(name, "stages")) { AB_CHECK_ARG(value >= 2 && value <= 8, "stages must be in [2,8]"); m->stages = value; }
     else if (!strcmp(name, "pdl")) m->use_pdl = value != 0;
+    else if (!strcmp(name, "debug_sync")) m->debug_sync = value != 0;
     else { set_error("unknown option %s", name); return ERR_BAD_ARG; }
     return OK;
 }

@@ -76,7 +76,8 @@ def quantize_int8(w: torch.Tensor, col_scale: Optional[torch.Tensor] = None) -> 
     w = w.float()
     if col_scale is not None:
         w = w / col_scale.float()[None, :]
-    s = w.abs().amax(dim=1) / 127.0
+    amax = w.abs().amax(dim=1)
+    s = amax / torch.full_like(amax, 127.0)   # tensor / tensor: a true division on every device
     safe = torch.where(s > 0, s, torch.ones_like(s))
     q = torch.round(w / safe[:, None]).clamp_(-127, 127).to(torch.int8)
     return PackedMatrix(_lib.FMT_I8, w.shape[0], w.shape[1], q.contiguous(), s.contiguous(),
@@ -95,14 +96,15 @@ def quantize_nvfp4(w: torch.Tensor) -> PackedMatrix:
     w = w.float()
     n, k = w.shape
     assert k % 16 == 0, "NVFP4 needs in-features divisible by 16"
-    t = w.abs().amax() / (448.0 * 6.0)
+    amax = w.abs().amax()
+    t = amax / torch.full_like(amax, 448.0 * 6.0)
     if float(t) == 0.0:
         t = torch.ones_like(t)
     blk = w.view(n, k // 16, 16)
     bmax = blk.abs().amax(dim=2)
-    sb8 = (bmax / (6.0 * t)).clamp_(max=448.0).to(torch.float8_e4m3fn)
+    sb8 = (bmax / (torch.full_like(t, 6.0) * t).expand_as(bmax)).clamp_(max=448.0).to(torch.float8_e4m3fn)
     sb = sb8.float()
-    denom = t * sb
+    denom = t.expand_as(sb) * sb
     safe = torch.where(denom > 0, denom, torch.ones_like(denom))
     code = _e2m1_codes(blk / safe[:, :, None])
     code = torch.where((denom > 0)[:, :, None], code, torch.zeros_like(code)).view(n, k)

@@ -87,9 +87,8 @@ class RWKV_x070:
             items = items.items()
         self.z: Dict[str, object] = {}
         self._extra: Dict[str, object] = {}
-        ln0 = {}
         for name, t in items:
-            self._ingest(name, t, ln0)
+            self._ingest(name, t)
         z = self.z
         self.n_head, self.head_size = self._r_k_shape
         assert HEAD_SIZE == self.head_size
@@ -103,10 +102,14 @@ class RWKV_x070:
         self._build_native()
         self._ws: Dict[Tuple[int, int], torch.Tensor] = {}
         self._graphs: Dict[tuple, tuple] = {}
-        self._tok_pinned = torch.empty(1, dtype=torch.int32).pin_memory()
+        # token ids travel host -> device from a ring of pinned slots; a slot is reused only after the
+        # asynchronous copy that read it has completed, so callers need not synchronise between steps
+        self._tok_ring = torch.empty(64, dtype=torch.int32).pin_memory()
+        self._tok_events = [None] * 64
+        self._tok_n = 0
 
     # ---- load-time preparation (reference/rwkv7.py:86-96) -----------------------------------
-    def _ingest(self, name: str, t: torch.Tensor, ln0: dict) -> None:
+    def _ingest(self, name: str, t: torch.Tensor) -> None:
         dev = self.device
         if _is_big(name):
             # storage is [out, in] row-major; the reference views it as [in, out]. Quantise per output row.
@@ -164,7 +167,7 @@ class RWKV_x070:
 
     def __del__(self):
         h = getattr(self, "_handle", None)
-        if h:
+        if h and _lib is not None and getattr(_lib, "lib", None) is not None:
             _lib.lib.ab_model_destroy(h)
             self._handle = None
 
@@ -245,8 +248,16 @@ class RWKV_x070:
                 self._graphs.pop(next(iter(self._graphs)))
             self._graphs[key] = entry
         graph, tok_dev, logits_buf = entry
-        self._tok_pinned[0] = int(idx)
-        tok_dev.copy_(self._tok_pinned, non_blocking=True)
+        slot = self._tok_n % 64
+        self._tok_n += 1
+        ev = self._tok_events[slot]
+        if ev is not None:
+            ev.synchronize()
+        self._tok_ring[slot] = int(idx)
+        tok_dev.copy_(self._tok_ring[slot:slot + 1], non_blocking=True)
+        if ev is None:
+            ev = self._tok_events[slot] = torch.cuda.Event()
+        ev.record()
         graph.replay()
         return logits_buf.clone(), list(state)
 
