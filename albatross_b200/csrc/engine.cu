@@ -51,7 +51,7 @@ using namespace ab;
 struct ab_model {
     ab_model_desc d;
     std::vector<ab_layer> layers;
-    int stages = 4;
+    int stages = 1;
     int use_pdl = 1;
     int debug_sync = 0;  // synchronise after every launch and name the one that failed
 };
@@ -314,7 +314,7 @@ size_t ab_workspace_bytes(const ab_model* m, int B, int T) {
 
 int ab_model_set_option(ab_model* m, const char* name, int value) {
     AB_CHECK_ARG(m && name, "ab_model_set_option: null pointer");
-    if (!strcmp(name, "stages")) { AB_CHECK_ARG(value >= 2 && value <= 8, "stages must be in [2,8]"); m->stages = value; }
+    if (!strcmp(name, "stages")) { AB_CHECK_ARG(value >= 1 && value <= 8, "stages must be in [1,8]"); m->stages = value; }
     else if (!strcmp(name, "pdl")) m->use_pdl = value != 0;
     else if (!strcmp(name, "debug_sync")) m->debug_sync = value != 0;
     else { set_error("unknown option %s", name); return ERR_BAD_ARG; }

@@ -5,9 +5,11 @@
 // with ONE fused launch per group of matrices that share an input:
 //   prologue : optional embedding gather, layer norm (reference/rwkv7.py:140,150,155) and the
 //              token-shift lerps (reference/rwkv7.py:227-228, :306-307), computed per block in smem;
-//   stream   : every warp owns a private ring of shared-memory stages filled by 1-D bulk (TMA)
-//              copies that complete on mbarriers; rows are K-contiguous, so each stage is a few
-//              contiguous runs of HBM; the issue cursor runs `stages` tiles ahead of the consumer;
+//   stream   : one producer warp per block; its lane w feeds consumer warp w's private ring of
+//              shared-memory stages with 1-D bulk (TMA) copies that complete on "full" mbarriers;
+//              consumers hand stages back through "empty" mbarriers. Rows are K-contiguous, so a
+//              stage is a few contiguous runs of HBM. Weights do not depend on the previous kernel,
+//              so the producer starts before the programmatic-dependent-launch wait;
 //   math     : int8 rows  -> dp4a against x split into a signed high byte and an unsigned low byte
 //                            of a 16-bit fixed-point value (one scale per 512 inputs), exact integer sums;
 //              NVFP4 rows -> e2m1 pairs converted in registers to half2, one e4m3 scale per 16 inputs;
@@ -19,64 +21,134 @@ namespace ab {
 
 namespace {
 
-struct Cursor {
-    int s, g, kc;  // segment, row group inside the segment, K chunk
-};
+constexpr int NT_CONS = GEMV_WARPS * 32;  // consumer threads
 
-struct BlockPlan {
-    int g_lo[GEMV_MAX_SEG], g_hi[GEMV_MAX_SEG];  // this block's row-group range inside each segment
-    int nkc;
-};
-
-__device__ __forceinline__ void cursor_settle(const GemvParams& p, const BlockPlan& bp, Cursor& c, int warp) {
-    while (c.s < p.nseg && c.g >= bp.g_hi[c.s]) {
-        ++c.s;
-        if (c.s < p.nseg) c.g = bp.g_lo[c.s] + warp;
-    }
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
 }
-__device__ __forceinline__ void cursor_next(const GemvParams& p, const BlockPlan& bp, Cursor& c, int warp) {
-    if (++c.kc == bp.nkc) {
-        c.kc = 0;
-        c.g += GEMV_WARPS;
-        cursor_settle(p, bp, c, warp);
-    }
-}
+__device__ __forceinline__ void cons_sync() { asm volatile("bar.sync 1, %0;" ::"n"(NT_CONS) : "memory"); }
 
-// Issue the bulk copies of one tile into a stage. Called by the whole warp; lanes < rows issue.
-__device__ __forceinline__ void issue_tile(const GemvParams& p, const Cursor& c, unsigned char* stage, uint64_t* bar,
-                                           int lane, uint64_t policy) {
-    const GemvSeg& sg = p.seg[c.s];
-    const int R = gemv_rows_per_group(sg.fmt);
-    const int row0 = c.g * R;
-    const int rows = min(R, sg.n_rows - row0);
-    const int k0 = c.kc * GEMV_TILE_K;
-    const int kn = min(GEMV_TILE_K, p.K - k0);
-    const int row_bytes = gemv_row_bytes(sg.fmt, p.K);
-    const int off_bytes = gemv_row_bytes(sg.fmt, k0);
-    const int cp_bytes = gemv_row_bytes(sg.fmt, kn);
-    const int tile_row_stride = GEMV_TILE_BYTES / R;
-    const int sc_bytes = (sg.fmt == FMT_FP4) ? kn / 16 : 0;
-    if (lane == 0) mbar_expect_tx(bar, (uint32_t)(rows * (cp_bytes + sc_bytes)));
-    __syncwarp();
-    if (lane < rows) {
-        const unsigned char* src = (const unsigned char*)sg.w + (size_t)(row0 + lane) * row_bytes + off_bytes;
-        bulk_g2s_hint(stage + lane * tile_row_stride, src, (uint32_t)cp_bytes, bar, policy);
-        if (sc_bytes) {
-            const unsigned char* ssrc = (const unsigned char*)sg.scale + (size_t)(row0 + lane) * (p.K / 16) + k0 / 16;
-            bulk_g2s_hint(stage + GEMV_TILE_BYTES + lane * 64, ssrc, (uint32_t)sc_bytes, bar, policy);
-        }
+// this block's row-group range [lo, hi) inside segment s
+__device__ __forceinline__ void seg_range(const GemvParams& p, int s, int G0, int G1, int& lo, int& hi) {
+    int base = 0;
+    for (int i = 0; i < s; ++i) {
+        const int R = gemv_rows_per_group(p.seg[i].fmt, p.K);
+        base += (p.seg[i].n_rows + R - 1) / R;
     }
+    const int R = gemv_rows_per_group(p.seg[s].fmt, p.K);
+    const int n = (p.seg[s].n_rows + R - 1) / R;
+    lo = max(G0, base) - base;
+    hi = min(G1, base + n) - base;
 }
 
-__device__ __forceinline__ float block_sum(float v, float* red, int tid) {
+__device__ __forceinline__ float cons_block_sum(float v, float* red, int tid) {
     v = warp_sum(v);
-    __syncthreads();
+    cons_sync();
     if ((tid & 31) == 0) red[tid >> 5] = v;
-    __syncthreads();
+    cons_sync();
     float t = 0.f;
 #pragma unroll
     for (int i = 0; i < GEMV_WARPS; ++i) t += red[i];
     return t;
+}
+
+// ---- per-format tile consumers: acc[r] += sum over this lane's slice of the tile -----------------
+// tile: R rows of `piece` bytes each; the tile covers kn elements of K starting at k0.
+template <int RMAX>
+__device__ __forceinline__ void consume_i8(const unsigned char* tile, int piece, int R, const signed char* xh,
+                                           const unsigned char* xl, const float* sx, int k0, int kn, int lane,
+                                           float* acc) {
+    for (int j = 0; j * 512 < kn; ++j) {
+        const int k = j * 512 + lane * 16;
+        if (k < kn) {
+            const uint4 a = *reinterpret_cast<const uint4*>(xh + k0 + k);
+            const uint4 b = *reinterpret_cast<const uint4*>(xl + k0 + k);
+            const float sc = sx[(k0 >> 9) + j];
+#pragma unroll
+            for (int r = 0; r < RMAX; ++r) {
+                if (r < R) {
+                    const uint4 w = *reinterpret_cast<const uint4*>(tile + r * piece + k);
+                    int ah = dp4a_ss(w.x, a.x, 0);
+                    int al = dp4a_su(w.x, b.x, 0);
+                    ah = dp4a_ss(w.y, a.y, ah);
+                    al = dp4a_su(w.y, b.y, al);
+                    ah = dp4a_ss(w.z, a.z, ah);
+                    al = dp4a_su(w.z, b.z, al);
+                    ah = dp4a_ss(w.w, a.w, ah);
+                    al = dp4a_su(w.w, b.w, al);
+                    acc[r] = fmaf((float)(ah * 256 + al), sc, acc[r]);
+                }
+            }
+        }
+    }
+}
+
+template <int RMAX>
+__device__ __forceinline__ void consume_f16(const unsigned char* tile, int piece, int R, const __half* xf, int k0,
+                                            int kn, int lane, float* acc) {
+    for (int j = 0; j * 256 < kn; ++j) {
+        const int k = j * 256 + lane * 8;
+        if (k < kn) {
+            const uint4 xv = *reinterpret_cast<const uint4*>(xf + k0 + k);
+            const __half2* x2 = reinterpret_cast<const __half2*>(&xv);
+#pragma unroll
+            for (int r = 0; r < RMAX; ++r) {
+                if (r < R) {
+                    const uint4 wv = *reinterpret_cast<const uint4*>(tile + r * piece + k * 2);
+                    const __half2* w2 = reinterpret_cast<const __half2*>(&wv);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float2 wf = __half22float2(w2[e]);
+                        const float2 xq = __half22float2(x2[e]);
+                        acc[r] = fmaf(wf.x, xq.x, acc[r]);
+                        acc[r] = fmaf(wf.y, xq.y, acc[r]);
+                    }
+                }
+            }
+        }
+    }
+}
+
+template <int RMAX>
+__device__ __forceinline__ void consume_fp4(const unsigned char* tile, int piece, int R, const __half* xf, int k0,
+                                            int kn, int lane, float* acc) {
+    const unsigned char* scales = tile + GEMV_TILE_BYTES;
+    const int srow = kn / 16;  // scale bytes per row in this tile
+    for (int j = 0; j * 1024 < kn; ++j) {
+        const int k = j * 1024 + lane * 32;
+        if (k < kn) {
+            uint4 xv[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) xv[e] = *reinterpret_cast<const uint4*>(xf + k0 + k + e * 8);
+            const __half2* x2 = reinterpret_cast<const __half2*>(xv);
+#pragma unroll
+            for (int r = 0; r < RMAX; ++r) {
+                if (r < R) {
+                    const uint4 wv = *reinterpret_cast<const uint4*>(tile + r * piece + k / 2);
+                    const uint32_t sc2 = *reinterpret_cast<const unsigned short*>(scales + r * srow + k / 16);
+                    const float2 scf = __half22float2(e4m3x2_to_half2(sc2));
+                    const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+                    for (int b = 0; b < 2; ++b) {
+                        __half2 h = __floats2half2_rn(0.f, 0.f);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            const uint32_t byte = (ww[b * 2 + (e >> 2)] >> (8 * (e & 3))) & 0xffu;
+                            h = __hfma2(e2m1x2_to_half2(byte), x2[b * 8 + e], h);
+                        }
+                        const float2 hf = __half22float2(h);
+                        acc[r] = fmaf(hf.x + hf.y, b ? scf.y : scf.x, acc[r]);
+                    }
+                }
+            }
+        }
+    }
 }
 
 __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_stream_kernel(const __grid_constant__ GemvParams p) {
@@ -86,11 +158,11 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_stream_kernel(const __gr
     const int Kp = (K + 511) & ~511;
     const int S = p.stages;
 
-    // ---- shared memory carve-up
-    unsigned char* ring = smem + (size_t)warp * S * GEMV_STAGE_BYTES;
+    // ---- shared memory carve-up (must match gemv_smem_bytes)
     size_t off = (size_t)GEMV_WARPS * S * GEMV_STAGE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + off) + warp * S;
-    off += (size_t)GEMV_WARPS * S * 8;
+    uint64_t* full_bars = reinterpret_cast<uint64_t*>(smem + off);
+    uint64_t* empty_bars = full_bars + GEMV_WARPS * S;
+    off += (size_t)GEMV_WARPS * S * 16;
     off = (off + 127) & ~(size_t)127;
     __half* xn = reinterpret_cast<__half*>(smem + off);
     off += (size_t)Kp * 2;
@@ -105,113 +177,212 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_stream_kernel(const __gr
     off += (size_t)(Kp / 512) * 4;
     float* red = reinterpret_cast<float*>(smem + off);
 
-    // ---- this block's share of every segment (contiguous run of row groups, split evenly)
-    BlockPlan bp;
-    bp.nkc = (K + GEMV_TILE_K - 1) / GEMV_TILE_K;
-    {
-        int total = 0;
-        for (int s = 0; s < p.nseg; ++s)
-            total += (p.seg[s].n_rows + gemv_rows_per_group(p.seg[s].fmt) - 1) / gemv_rows_per_group(p.seg[s].fmt);
-        const int G0 = (int)(((long long)total * blockIdx.x) / gridDim.x);
-        const int G1 = (int)(((long long)total * (blockIdx.x + 1)) / gridDim.x);
-        int base = 0;
-        for (int s = 0; s < GEMV_MAX_SEG; ++s) {
-            if (s < p.nseg) {
-                const int R = gemv_rows_per_group(p.seg[s].fmt);
-                const int n = (p.seg[s].n_rows + R - 1) / R;
-                bp.g_lo[s] = max(G0, base) - base;
-                bp.g_hi[s] = min(G1, base + n) - base;
-                base += n;
-            } else {
-                bp.g_lo[s] = 0;
-                bp.g_hi[s] = 0;
-            }
-        }
+    // ---- this block's contiguous run of row groups over the concatenated segments
+    int total = 0;
+    for (int s = 0; s < p.nseg; ++s) {
+        const int R = gemv_rows_per_group(p.seg[s].fmt, K);
+        total += (p.seg[s].n_rows + R - 1) / R;
     }
+    const int G0 = (int)(((long long)total * blockIdx.x) / gridDim.x);
+    const int G1 = (int)(((long long)total * (blockIdx.x + 1)) / gridDim.x);
 
-    if (lane == 0) {
-        for (int i = 0; i < S; ++i) mbar_init(&bars[i], 1);
+    if (tid == 0) {
+        for (int i = 0; i < GEMV_WARPS * S; ++i) {
+            mbar_init(&full_bars[i], 1);
+            mbar_init(&empty_bars[i], 1);
+        }
         fence_mbar_init();
     }
-    __syncwarp();
+    __syncthreads();
 
-    // ---- start streaming weights before anything that depends on the previous kernel
-    const uint64_t policy = policy_evict_first();
-    Cursor ci{0, bp.g_lo[0] + warp, 0};
-    cursor_settle(p, bp, ci, warp);
-    Cursor cc = ci;
-    for (int i = 0; i < S; ++i) {
-        if (ci.s < p.nseg) {
-            issue_tile(p, ci, ring + (size_t)i * GEMV_STAGE_BYTES, &bars[i], lane, policy);
-            cursor_next(p, bp, ci, warp);
+    if (warp == GEMV_WARPS) {
+        // ================= producer warp: lane w streams consumer warp w's tiles =================
+        if (lane < GEMV_WARPS) {
+            const uint64_t policy = policy_evict_first();
+            unsigned char* ring = smem + (size_t)lane * S * GEMV_STAGE_BYTES;
+            uint64_t* fb = full_bars + lane * S;
+            uint64_t* eb = empty_bars + lane * S;
+            int slot = 0;
+            uint32_t fills = 0;   // tiles issued so far
+            uint32_t ephase = 0;  // parity of the empty barrier to wait for once the ring has wrapped
+            bool dead = false;
+            for (int s = 0; s < p.nseg && !dead; ++s) {
+                int lo, hi;
+                seg_range(p, s, G0, G1, lo, hi);
+                if (lo >= hi) continue;
+                const GemvSeg& sg = p.seg[s];
+                const GemvGeom gm = gemv_geom(sg.fmt, K);
+                const int row_bytes = gemv_row_bytes(sg.fmt, K);
+                const int srow_bytes = K / 16;
+                for (int g = lo + lane; g < hi && !dead; g += GEMV_WARPS) {
+                    const int row0 = g * gm.R;
+                    const int rows = min(gm.R, sg.n_rows - row0);
+                    const unsigned char* src = (const unsigned char*)sg.w + (size_t)row0 * row_bytes;
+                    const unsigned char* ssrc =
+                        sg.fmt == FMT_FP4 ? (const unsigned char*)sg.scale + (size_t)row0 * srow_bytes : nullptr;
+                    for (int kc = 0; kc < gm.nkc; ++kc) {
+                        if (fills >= (uint32_t)S) {  // wait until the consumer has drained this slot
+                            uint32_t it = 0;
+                            while (!mbar_test_wait(&eb[slot], ephase)) {
+                                if (++it > (1u << 24)) {
+                                    dead = true;
+                                    break;
+                                }
+                            }
+                            if (dead) {
+                                atomicOr(&g_device_status, DEV_WAIT_GEMV);
+                                break;
+                            }
+                        }
+                        const int k0 = kc * gm.kc;
+                        const int kn = min(gm.kc, K - k0);
+                        const int cpb = gemv_row_bytes(sg.fmt, kn);
+                        const int scb = ssrc ? kn / 16 : 0;
+                        unsigned char* stage = ring + (size_t)slot * GEMV_STAGE_BYTES;
+                        mbar_expect_tx(&fb[slot], (uint32_t)(rows * (cpb + scb)));
+                        if (gm.contig) {  // whole rows: the group is one contiguous run
+                            bulk_g2s_hint(stage, src, (uint32_t)(rows * cpb), &fb[slot], policy);
+                            if (scb) bulk_g2s_hint(stage + GEMV_TILE_BYTES, ssrc, (uint32_t)(rows * scb), &fb[slot], policy);
+                        } else {
+                            const int koff = gemv_row_bytes(sg.fmt, k0);
+                            for (int r = 0; r < rows; ++r) {
+                                bulk_g2s_hint(stage + r * gm.piece, src + (size_t)r * row_bytes + koff, (uint32_t)cpb,
+                                              &fb[slot], policy);
+                                if (scb)
+                                    bulk_g2s_hint(stage + GEMV_TILE_BYTES + r * scb, ssrc + (size_t)r * srow_bytes + k0 / 16,
+                                                  (uint32_t)scb, &fb[slot], policy);
+                            }
+                        }
+                        ++fills;
+                        if (++slot == S) {
+                            slot = 0;
+                            if (fills > (uint32_t)S) ephase ^= 1;
+                        }
+                    }
+                }
+            }
         }
+        return;
     }
 
+    // ================= consumer warps =================
     if (p.use_pdl) {
         pdl_wait();
         pdl_launch_dependents();
     }
 
     if (p.copy_src && blockIdx.x == 0)
-        for (int i = tid; i < p.copy_n / 8; i += GEMV_THREADS)
+        for (int i = tid; i < p.copy_n / 8; i += NT_CONS)
             reinterpret_cast<uint4*>(p.copy_dst)[i] = reinterpret_cast<const uint4*>(p.copy_src)[i];
 
-    // ---- phase A: input vector, optional layer norm, token-shift difference
+    // ---- phase A: input vector, optional layer norm, token-shift difference (8 halves per thread per pass)
     const __half* xin = p.emb ? p.emb + (size_t)p.token[0] * K : p.x;
-    for (int i = tid; i < K / 8; i += GEMV_THREADS) {
-        uint4 v = reinterpret_cast<const uint4*>(xin)[i];
+    float lsum = 0.f;
+    for (int i = tid; i < K / 8; i += NT_CONS) {
+        const uint4 v = reinterpret_cast<const uint4*>(xin)[i];
         reinterpret_cast<uint4*>(xn)[i] = v;
         if (p.x_copy && blockIdx.x == 0) reinterpret_cast<uint4*>(p.x_copy)[i] = v;
-    }
-    __syncthreads();
-    if (p.ln_w) {
-        float s = 0.f;
-        for (int i = tid; i < K; i += GEMV_THREADS) s += __half2float(xn[i]);
-        const float mean = block_sum(s, red, tid) / (float)K;
-        float q = 0.f;
-        for (int i = tid; i < K; i += GEMV_THREADS) {
-            const float d = __half2float(xn[i]) - mean;
-            q += d * d;
+        const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = __half22float2(h[e]);
+            lsum += f.x + f.y;
         }
-        const float var = block_sum(q, red, tid) / (float)K;
-        const float rstd = rsqrtf(var + 1e-5f);
-        for (int i = tid; i < K; i += GEMV_THREADS) {
-            const float v = (__half2float(xn[i]) - mean) * rstd * __half2float(p.ln_w[i]) + __half2float(p.ln_b[i]);
-            const __half hv = __float2half_rn(v);
-            xn[i] = hv;
-            if (p.ln_out && blockIdx.x == 0) p.ln_out[i] = hv;
+    }
+    if (p.ln_w) {
+        const float mean = cons_block_sum(lsum, red, tid) / (float)K;
+        float q = 0.f;
+        for (int i = tid; i < K / 8; i += NT_CONS) {
+            const uint4 v = reinterpret_cast<const uint4*>(xn)[i];
+            const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 f = __half22float2(h[e]);
+                q += (f.x - mean) * (f.x - mean) + (f.y - mean) * (f.y - mean);
+            }
+        }
+        const float rstd = rsqrtf(cons_block_sum(q, red, tid) / (float)K + 1e-5f);
+        for (int i = tid; i < K / 8; i += NT_CONS) {
+            const uint4 v = reinterpret_cast<const uint4*>(xn)[i];
+            const uint4 wv = reinterpret_cast<const uint4*>(p.ln_w)[i];
+            const uint4 bv = reinterpret_cast<const uint4*>(p.ln_b)[i];
+            const __half2* h = reinterpret_cast<const __half2*>(&v);
+            const __half2* w2 = reinterpret_cast<const __half2*>(&wv);
+            const __half2* b2 = reinterpret_cast<const __half2*>(&bv);
+            uint4 o;
+            __half2* o2 = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 f = __half22float2(h[e]), wf = __half22float2(w2[e]), bf = __half22float2(b2[e]);
+                o2[e] = __floats2half2_rn((f.x - mean) * rstd * wf.x + bf.x, (f.y - mean) * rstd * wf.y + bf.y);
+            }
+            reinterpret_cast<uint4*>(xn)[i] = o;
+            if (p.ln_out && blockIdx.x == 0) reinterpret_cast<uint4*>(p.ln_out)[i] = o;
         }
     }
     if (p.smem_flags & 4) {
-        __syncthreads();
-        for (int i = tid; i < K; i += GEMV_THREADS)
-            dx[i] = __float2half_rn(__half2float(p.x_prev[i]) - __half2float(xn[i]));
+        for (int i = tid; i < K / 8; i += NT_CONS) {  // the same thread wrote xn[i] above: no barrier needed
+            const uint4 v = reinterpret_cast<const uint4*>(xn)[i];
+            const uint4 pv = reinterpret_cast<const uint4*>(p.x_prev)[i];
+            const __half2* h = reinterpret_cast<const __half2*>(&v);
+            const __half2* q2 = reinterpret_cast<const __half2*>(&pv);
+            uint4 o;
+            __half2* o2 = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) o2[e] = __hsub2(q2[e], h[e]);
+            reinterpret_cast<uint4*>(dx)[i] = o;
+        }
     }
-    __syncthreads();
+    cons_sync();
 
-    uint32_t n_consumed = 0;  // tiles this warp has consumed (stage = n % S, parity = (n / S) & 1)
+    unsigned char* ring = smem + (size_t)warp * S * GEMV_STAGE_BYTES;
+    uint64_t* fb = full_bars + warp * S;
+    uint64_t* eb = empty_bars + warp * S;
+    int slot = 0;
+    uint32_t fphase = 0;
     bool failed = false;
 
     for (int s = 0; s < p.nseg; ++s) {
-        if (bp.g_lo[s] >= bp.g_hi[s]) continue;  // block-uniform
+        int lo, hi;
+        seg_range(p, s, G0, G1, lo, hi);
+        if (lo >= hi) continue;  // block-uniform
         const GemvSeg& sg = p.seg[s];
         const int fmt = sg.fmt;
 
-        // ---- phase B: the segment's input in the form its rows consume
-        for (int c0 = warp * 32; c0 < Kp / 16; c0 += GEMV_THREADS) {
-            const int c = c0 + lane;          // 16-element chunk
+        // ---- phase B: the segment's input in the form its rows consume (16 elements per thread per pass)
+        for (int c0 = warp * 32; c0 < Kp / 16; c0 += NT_CONS) {
+            const int c = c0 + lane;
             const bool in = c * 16 < K;
             float v[16];
-            float amax = 0.f;
+            if (in) {
+                const uint4 a0 = reinterpret_cast<const uint4*>(xn)[2 * c], a1 = reinterpret_cast<const uint4*>(xn)[2 * c + 1];
+                const __half2* h0 = reinterpret_cast<const __half2*>(&a0);
+                const __half2* h1 = reinterpret_cast<const __half2*>(&a1);
 #pragma unroll
-            for (int e = 0; e < 16; ++e) {
-                float t = 0.f;
-                if (in) {
-                    const int i = c * 16 + e;
-                    t = __half2float(xn[i]);
-                    if (sg.mix) t = rh(t + rh(__half2float(dx[i]) * __half2float(sg.mix[i])));
+                for (int e = 0; e < 4; ++e) {
+                    const float2 f0 = __half22float2(h0[e]), f1 = __half22float2(h1[e]);
+                    v[2 * e] = f0.x;
+                    v[2 * e + 1] = f0.y;
+                    v[8 + 2 * e] = f1.x;
+                    v[9 + 2 * e] = f1.y;
                 }
-                v[e] = t;
+                if (sg.mix) {
+                    const uint4 d0 = reinterpret_cast<const uint4*>(dx)[2 * c], d1 = reinterpret_cast<const uint4*>(dx)[2 * c + 1];
+                    const uint4 m0 = reinterpret_cast<const uint4*>(sg.mix)[2 * c], m1 = reinterpret_cast<const uint4*>(sg.mix)[2 * c + 1];
+                    const __half2* dd[2] = {reinterpret_cast<const __half2*>(&d0), reinterpret_cast<const __half2*>(&d1)};
+                    const __half2* mm[2] = {reinterpret_cast<const __half2*>(&m0), reinterpret_cast<const __half2*>(&m1)};
+#pragma unroll
+                    for (int hh = 0; hh < 2; ++hh)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float2 df = __half22float2(dd[hh][e]), mf = __half22float2(mm[hh][e]);
+                            v[8 * hh + 2 * e] = rh(v[8 * hh + 2 * e] + rh(df.x * mf.x));
+                            v[8 * hh + 2 * e + 1] = rh(v[8 * hh + 2 * e + 1] + rh(df.y * mf.y));
+                        }
+                }
+            } else {
+#pragma unroll
+                for (int e = 0; e < 16; ++e) v[e] = 0.f;
             }
             if (fmt != FMT_I8) {
                 if (in) {
@@ -222,6 +393,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_stream_kernel(const __gr
                     reinterpret_cast<uint4*>(xf)[c * 2 + 1] = *reinterpret_cast<uint4*>(&h[4]);
                 }
             } else {
+                float amax = 0.f;
 #pragma unroll
                 for (int e = 0; e < 16; ++e) {
                     if (sg.col_scale && in) v[e] *= sg.col_scale[c * 16 + e];
@@ -247,100 +419,39 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_stream_kernel(const __gr
                 if (lane == 0) sx[c0 / 32] = amax / 32767.0f;
             }
         }
-        __syncthreads();
+        cons_sync();
 
         // ---- stream this warp's row groups of the segment
-        const int R = gemv_rows_per_group(fmt);
-        while (cc.s == s) {
+        const GemvGeom gm = gemv_geom(fmt, K);
+        const int R = gm.R;
+        for (int g = lo + warp; g < hi; g += GEMV_WARPS) {
             float acc[8];
 #pragma unroll
             for (int r = 0; r < 8; ++r) acc[r] = 0.f;
-            const int g = cc.g;
-            for (int kc = 0; kc < bp.nkc; ++kc) {
-                const uint32_t st = n_consumed % S;
-                unsigned char* tile = ring + (size_t)st * GEMV_STAGE_BYTES;
-                if (!failed && !mbar_wait_bounded(&bars[st], (n_consumed / S) & 1)) {
+            const int rows = min(R, sg.n_rows - g * R);
+            for (int kc = 0; kc < gm.nkc; ++kc) {
+                const unsigned char* tile = ring + (size_t)slot * GEMV_STAGE_BYTES;
+                if (!failed && !mbar_wait_bounded(&fb[slot], fphase)) {
                     failed = true;
                     if (lane == 0) atomicOr(&g_device_status, DEV_WAIT_GEMV);
                 }
-                const int k0 = kc * GEMV_TILE_K;
+                const int k0 = kc * gm.kc;
+                const int kn = min(gm.kc, K - k0);
                 if (fmt == FMT_I8) {
-#pragma unroll
-                    for (int j = 0; j < 2; ++j) {
-                        const int k = k0 + j * 512 + lane * 16;
-                        if (k < K) {
-                            const uint4 a = *reinterpret_cast<const uint4*>(xh + k);
-                            const uint4 b = *reinterpret_cast<const uint4*>(xl + k);
-                            const float sc = sx[(k0 + j * 512) >> 9];
-#pragma unroll
-                            for (int r = 0; r < 4; ++r) {
-                                const uint4 w = *reinterpret_cast<const uint4*>(tile + r * 1024 + j * 512 + lane * 16);
-                                int ah = dp4a_ss(w.x, a.x, 0);
-                                ah = dp4a_ss(w.y, a.y, ah);
-                                ah = dp4a_ss(w.z, a.z, ah);
-                                ah = dp4a_ss(w.w, a.w, ah);
-                                int al = dp4a_su(w.x, b.x, 0);
-                                al = dp4a_su(w.y, b.y, al);
-                                al = dp4a_su(w.z, b.z, al);
-                                al = dp4a_su(w.w, b.w, al);
-                                acc[r] = fmaf((float)(ah * 256 + al), sc, acc[r]);
-                            }
-                        }
-                    }
+                    if (R <= 2) consume_i8<2>(tile, gm.piece, rows, xh, xl, sx, k0, kn, lane, acc);
+                    else consume_i8<8>(tile, gm.piece, rows, xh, xl, sx, k0, kn, lane, acc);
                 } else if (fmt == FMT_F16) {
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const int k = k0 + j * 256 + lane * 8;
-                        if (k < K) {
-                            const uint4 xv = *reinterpret_cast<const uint4*>(xf + k);
-                            const __half2* x2 = reinterpret_cast<const __half2*>(&xv);
-#pragma unroll
-                            for (int r = 0; r < 2; ++r) {
-                                const uint4 wv = *reinterpret_cast<const uint4*>(tile + r * 2048 + j * 512 + lane * 16);
-                                const __half2* w2 = reinterpret_cast<const __half2*>(&wv);
-#pragma unroll
-                                for (int e = 0; e < 4; ++e) {
-                                    const float2 wf = __half22float2(w2[e]);
-                                    const float2 xq = __half22float2(x2[e]);
-                                    acc[r] = fmaf(wf.x, xq.x, acc[r]);
-                                    acc[r] = fmaf(wf.y, xq.y, acc[r]);
-                                }
-                            }
-                        }
-                    }
-                } else {  // FMT_FP4
-                    const int k = k0 + lane * 32;
-                    if (k < K) {
-                        uint4 xv[4];
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) xv[e] = *reinterpret_cast<const uint4*>(xf + k + e * 8);
-                        const __half2* x2 = reinterpret_cast<const __half2*>(xv);
-#pragma unroll
-                        for (int r = 0; r < 8; ++r) {
-                            const uint4 wv = *reinterpret_cast<const uint4*>(tile + r * 512 + lane * 16);
-                            const uint32_t sc2 = *reinterpret_cast<const unsigned short*>(tile + GEMV_TILE_BYTES + r * 64 + lane * 2);
-                            const float2 scf = __half22float2(e4m3x2_to_half2(sc2));
-                            const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
-#pragma unroll
-                            for (int b = 0; b < 2; ++b) {
-                                __half2 h = __floats2half2_rn(0.f, 0.f);
-#pragma unroll
-                                for (int e = 0; e < 8; ++e) {
-                                    const uint32_t byte = (ww[b * 2 + (e >> 2)] >> (8 * (e & 3))) & 0xffu;
-                                    h = __hfma2(e2m1x2_to_half2(byte), x2[b * 8 + e], h);
-                                }
-                                const float2 hf = __half22float2(h);
-                                acc[r] = fmaf(hf.x + hf.y, b ? scf.y : scf.x, acc[r]);
-                            }
-                        }
-                    }
+                    if (R <= 2) consume_f16<2>(tile, gm.piece, rows, xf, k0, kn, lane, acc);
+                    else consume_f16<8>(tile, gm.piece, rows, xf, k0, kn, lane, acc);
+                } else {
+                    if (R <= 2) consume_fp4<2>(tile, gm.piece, rows, xf, k0, kn, lane, acc);
+                    else consume_fp4<8>(tile, gm.piece, rows, xf, k0, kn, lane, acc);
                 }
                 __syncwarp();
-                ++n_consumed;
-                // refill the stage just drained with the tile `S` ahead
-                if (ci.s < p.nseg) {
-                    issue_tile(p, ci, tile, &bars[st], lane, policy);
-                    cursor_next(p, bp, ci, warp);
+                if (lane == 0) mbar_arrive(&eb[slot]);
+                if (++slot == S) {
+                    slot = 0;
+                    fphase ^= 1;
                 }
             }
             // ---- epilogue for the R rows of this group
@@ -364,10 +475,8 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_stream_kernel(const __gr
                 }
                 sg.out[row] = __float2half_rn(o);
             }
-            cc.kc = bp.nkc - 1;
-            cursor_next(p, bp, cc, warp);
         }
-        __syncthreads();  // all warps are done with this segment's x before it is rebuilt
+        cons_sync();  // all warps are done with this segment's x before it is rebuilt
     }
 }
 
@@ -375,7 +484,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_stream_kernel(const __gr
 
 size_t gemv_smem_bytes(const GemvParams& p) {
     const size_t Kp = ((size_t)p.K + 511) & ~(size_t)511;
-    size_t off = (size_t)GEMV_WARPS * p.stages * GEMV_STAGE_BYTES + (size_t)GEMV_WARPS * p.stages * 8;
+    size_t off = (size_t)GEMV_WARPS * p.stages * GEMV_STAGE_BYTES + (size_t)GEMV_WARPS * p.stages * 16;
     off = (off + 127) & ~(size_t)127;
     off += Kp * 2;
     if (p.smem_flags & 1) off += Kp * 2;
@@ -400,12 +509,12 @@ int gemv_launch(const GemvParams& p_in, cudaStream_t stream) {
         AB_CHECK_ARG(g.fmt != FMT_FP4 || (((uintptr_t)g.scale & 15) == 0 && p.K % 256 == 0),
                      "gemv: segment %d: NVFP4 needs 16-byte aligned block scales and K %% 256 == 0", s);
         AB_CHECK_ARG(g.epi != EPI_RESID || g.resid, "gemv: segment %d residual missing", s);
-        const int R = gemv_rows_per_group(g.fmt);
+        const int R = gemv_rows_per_group(g.fmt, p.K);
         groups += (g.n_rows + R - 1) / R;
     }
     AB_CHECK_ARG(p.emb || p.x, "gemv: no input vector");
     AB_CHECK_ARG(!(p.smem_flags & 4) || p.x_prev, "gemv: token-shift state missing");
-    if (p.stages <= 0) p.stages = 4;
+    if (p.stages <= 0) p.stages = 1;
     static int n_sm = 0;
     static size_t max_smem = 0;
     if (!n_sm) {
@@ -419,12 +528,12 @@ int gemv_launch(const GemvParams& p_in, cudaStream_t stream) {
         n_sm = v;
     }
     size_t smem = gemv_smem_bytes(p);
-    while (smem > max_smem && p.stages > 2) {
+    while (smem > max_smem && p.stages > 1) {
         --p.stages;
         smem = gemv_smem_bytes(p);
     }
     AB_CHECK_ARG(smem <= max_smem, "gemv: K=%d needs %zu bytes of shared memory", p.K, smem);
-    const int grid = max(1, min(n_sm, (groups + GEMV_WARPS - 1) / GEMV_WARPS));
+    const int grid = max(1, min(n_sm, groups));
 
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);

@@ -8,12 +8,12 @@ enum Fmt : int { FMT_F16 = 0, FMT_I8 = 1, FMT_FP4 = 2 };
 enum Epi : int { EPI_NONE = 0, EPI_TANH = 1, EPI_SIGMOID = 2, EPI_RELU2 = 3, EPI_RESID = 4 };
 
 constexpr int GEMV_MAX_SEG = 7;
-constexpr int GEMV_WARPS = 8;
-constexpr int GEMV_THREADS = GEMV_WARPS * 32;
-constexpr int GEMV_TILE_K = 1024;     // K elements covered by one pipeline stage
-constexpr int GEMV_TILE_BYTES = 4096; // weight bytes of one stage (rows_per_group * row bytes of 1024 k)
-constexpr int GEMV_SCALE_BYTES = 512; // NVFP4 block scales of one stage (8 rows * 64)
+constexpr int GEMV_WARPS = 16;                        // consumer warps; one more warp produces
+constexpr int GEMV_THREADS = (GEMV_WARPS + 1) * 32;
+constexpr int GEMV_TILE_BYTES = 8192;  // weight bytes of one pipeline stage
+constexpr int GEMV_SCALE_BYTES = 1024; // NVFP4 block scales of one stage
 constexpr int GEMV_STAGE_BYTES = GEMV_TILE_BYTES + GEMV_SCALE_BYTES;
+constexpr int GEMV_PIECE_BYTES = 4096; // bytes of one row inside a stage: bulk copies below ~4 KB lose bandwidth
 
 // One matrix (a contiguous run of output rows) inside a fused launch.
 struct GemvSeg {
@@ -46,8 +46,29 @@ struct GemvParams {
     int use_pdl;            // kernel was launched with programmatic stream serialization
 };
 
-__host__ __device__ inline int gemv_rows_per_group(int fmt) { return fmt == FMT_I8 ? 4 : (fmt == FMT_F16 ? 2 : 8); }
 __host__ __device__ inline int gemv_row_bytes(int fmt, int K) { return fmt == FMT_I8 ? K : (fmt == FMT_F16 ? 2 * K : K / 2); }
+
+// A stage holds R rows x `piece` bytes of each row. Rows shorter than GEMV_PIECE_BYTES are taken whole,
+// and then the R rows of a group are one contiguous run of memory (a single bulk copy).
+struct GemvGeom {
+    int R;        // rows per group
+    int piece;    // bytes of a row per stage
+    int kc;       // K elements per stage
+    int nkc;      // stages per group
+    int contig;   // rows of a stage are contiguous in memory
+};
+__host__ __device__ inline GemvGeom gemv_geom(int fmt, int K) {
+    GemvGeom g;
+    const int rb = gemv_row_bytes(fmt, K);
+    g.piece = rb < GEMV_PIECE_BYTES ? rb : GEMV_PIECE_BYTES;
+    g.R = GEMV_TILE_BYTES / g.piece;
+    if (g.R > 8) g.R = 8;
+    g.kc = fmt == FMT_I8 ? g.piece : (fmt == FMT_F16 ? g.piece / 2 : g.piece * 2);
+    g.nkc = (K + g.kc - 1) / g.kc;
+    g.contig = g.piece == rb;
+    return g;
+}
+__host__ __device__ inline int gemv_rows_per_group(int fmt, int K) { return gemv_geom(fmt, K).R; }
 
 size_t gemv_smem_bytes(const GemvParams& p);
 int gemv_launch(const GemvParams& p, cudaStream_t stream);

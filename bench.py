@@ -33,6 +33,8 @@ sys.path.insert(0, ROOT)
 WORKLOADS = {
     "decode_bsz1_int8": dict(batch=1, quant="int8"),
     "decode_bsz320_nvfp4": dict(batch=320, quant="nvfp4"),
+    "gemv_int8": dict(batch=1, quant="int8"),
+    "gemv_nvfp4": dict(batch=1, quant="nvfp4"),
 }
 METRIC = "rwkv7_decode_tokens_per_s"
 
@@ -215,6 +217,53 @@ def run_ours(a, rank, world, dev):
 
 
 # ----------------------------------------------------------------------------------------------
+# single-kernel workload: one quantised matrix-vector product (baseline config 1 and its larger shapes)
+# ----------------------------------------------------------------------------------------------
+def run_gemv(a, dev):
+    """Times ab_gemv alone. Each launch streams a different matrix (enough of them to exceed the L2),
+    so every launch reads its weights from HBM."""
+    import ctypes as C
+    from albatross_b200 import _lib, quant
+    torch.cuda.set_device(dev)
+    fmt = "nvfp4" if "nvfp4" in a.workload else "int8"
+    n, k = a.n_out, a.k
+    per = n * k * (1.0 if fmt == "int8" else 0.5625)
+    n_mats = max(4, int(400e6 // per) + 1)
+    torch.manual_seed(0)
+    mats = [quant.quantize((torch.randn(n, k, device=f"cuda:{dev}") * 0.02).half(), fmt) for _ in range(n_mats)]
+    cm = [m.as_mat() for m in mats]
+    x = torch.randn(k, device=f"cuda:{dev}").half()
+    y = torch.empty(n, dtype=torch.float16, device=f"cuda:{dev}")
+    st = torch.cuda.current_stream().cuda_stream
+    call = lambda i: _lib.check(_lib.lib.ab_gemv(C.byref(cm[i % n_mats]), x.data_ptr(), y.data_ptr(), st))
+    for i in range(max(a.warmup, n_mats)):
+        call(i)
+    torch.cuda.synchronize()
+    sampler = ClockSampler(dev)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(a.steps):
+        call(i)
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1) / a.steps
+    alg = mats[0].nbytes() + 2 * (n + k)
+    hbm, _, which = measured_peaks()
+    gbs = alg / (ms * 1e-3) / 1e9
+    return {"metric": "gemv_hbm_gbs", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": a.steps, "warmup": a.warmup,
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": fmt + " weights, fp16 activations", "data": "synthetic",
+            "config": {"workload": a.workload, "n_out": n, "k": k, "matrices_cycled": n_mats,
+                       "l2": "each launch reads a different matrix; the set is larger than L2"},
+            "gpu_launches": a.steps,
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm, "unit": "GB/s", "frac": gbs / hbm, "traffic": None,
+                         "peak_source": which, "kernel": "gemv_stream_kernel", "algorithmic_bytes_per_launch": alg},
+            "clocks": clocks, "device_status": _lib.device_status()}
+
+
+# ----------------------------------------------------------------------------------------------
 # CPU arm: the oracle's restatement of the reference's PyTorch path on the host cores
 # ----------------------------------------------------------------------------------------------
 def run_cpu(a, n_layers_sample: int = 2, steps: int = 6):
@@ -263,6 +312,8 @@ def main():
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host (profiling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--n-out", type=int, default=4096, help="gemv_* workloads: output rows")
+    ap.add_argument("--k", type=int, default=4096, help="gemv_* workloads: input length")
     a = ap.parse_args()
     a.warmup = max(a.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
@@ -283,6 +334,10 @@ def main():
             "e2e": {"value": cb["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
         return
 
+    if a.workload.startswith("gemv_"):
+        if rank == 0:
+            print(json.dumps(run_gemv(a, local)))
+        return
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         torch.cuda.set_device(local)
