@@ -68,11 +68,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// try_wait that lets the hardware park the thread for up to `ns` before it reports "not yet":
+// polling in a tight loop floods the shared-memory pipe that the math loads need.
+__device__ __forceinline__ bool mbar_try_wait_park(uint64_t* bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+        : "memory");
+    return ok != 0;
+}
 // Bounded wait: returns false (and the caller records an error) instead of spinning for ever.
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, uint32_t max_iters = (1u << 22)) {
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, uint32_t max_iters = (1u << 20)) {
     for (uint32_t i = 0; i < max_iters; ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if (i > 64) __nanosleep(32);
+        if (mbar_try_wait_park(bar, parity, 2000u)) return true;
+        if (i > 4) __nanosleep(64);
     }
     return false;
 }

@@ -14,6 +14,7 @@
 #include <vector>
 
 #include "../../include/albatross_b200.h"
+#include "decode.cuh"
 #include "gemm.cuh"
 #include "gemv.cuh"
 #include "head.cuh"
@@ -40,7 +41,7 @@ static GemvSeg seg_of(const ab_mat& m, const void* mix, int epi, void* out, cons
     GemvSeg g = {};
     g.w = m.w; g.scale = m.scale; g.col_scale = m.col_scale; g.tscale = m.tscale;
     g.mix = (const __half*)mix; g.resid = (const __half*)resid; g.out = (__half*)out;
-    g.fmt = m.fmt; g.epi = epi; g.n_rows = m.n_out;
+    g.fmt = m.fmt; g.epi = epi; g.n_rows = m.n_out; g.K = m.k;
     return g;
 }
 
@@ -51,9 +52,10 @@ using namespace ab;
 struct ab_model {
     ab_model_desc d;
     std::vector<ab_layer> layers;
-    int stages = 1;
+    int stages = 2;
     int use_pdl = 1;
     int debug_sync = 0;  // synchronise after every launch and name the one that failed
+    int timeline = 0;    // persistent decode kernel records per-phase timestamps
 };
 
 namespace {
@@ -86,8 +88,7 @@ Workspace carve(const ab_model* m, int B, int T, unsigned char* base) {
     w.hw = take(M * rmax[0]); w.ha = take(M * rmax[1]); w.hv = take(M * rmax[2]); w.hg = take(M * rmax[3]);
     const bool batched = !(B == 1 && T == 1);
     for (int j = 0; j < 6; ++j) w.mix[j] = batched ? take(M * D) : nullptr;
-    w.w_raw = batched ? take(M * D) : nullptr; w.a_raw = batched ? take(M * D) : nullptr;
-    w.vg_raw = batched ? take(M * D) : nullptr; w.g = batched ? take(M * D) : nullptr;
+    w.w_raw = take(M * D); w.a_raw = take(M * D); w.vg_raw = take(M * D); w.g = take(M * D);
     w.xlast = batched ? take((size_t)B * D) : nullptr;
     w.gemm_scratch = base + off;
     off += al(batched ? gemm_scratch_bytes(m->d.head, (int)M) : 0);
@@ -178,6 +179,107 @@ int forward_one(ab_model* m, const int32_t* token, void* const* state, const Wor
     p.ln_w = (const __half*)m->d.lnout_w; p.ln_b = (const __half*)m->d.lnout_b;
     p.seg[0] = seg_of(m->d.head, nullptr, EPI_NONE, logits);
     AB_STEP(m, st, -1, "head gemv", gemv_launch(p, st));
+    return OK;
+}
+
+// The phase list of one token for the persistent kernel: per block
+//   [LN1 + lerps + r/k/v + adapter-down rows] [adapter-up rows] [per-head WKV] [output proj + residual]
+//   [LN2 + lerp + ffn key + relu^2] [ffn value + residual], then [LN_out + head].
+int build_decode_program(ab_model* m, const int32_t* token, void* const* state, const Workspace& ws, __half* logits,
+                         std::vector<unsigned char>& buf, const DecodeProgram* dev_addr) {
+    const int D = m->d.n_embd, H = D / HEAD, L = m->d.n_layer;
+    const int n_phases = 6 * L + 1;
+    buf.assign(sizeof(DecodeProgram) + sizeof(DecodePhase) * (size_t)n_phases, 0);
+    DecodeProgram* prog = reinterpret_cast<DecodeProgram*>(buf.data());
+    prog->n_phases = n_phases;
+    prog->stages = m->stages;
+    prog->Kn = D;
+    prog->Kq = 4 * D;
+    prog->barrier = const_cast<unsigned*>(&dev_addr->barrier_word);
+    prog->timeline = m->timeline ? (unsigned long long*)((unsigned char*)dev_addr + sizeof(DecodeProgram) +
+                                                          sizeof(DecodePhase) * (size_t)n_phases) : nullptr;
+    int n = 0;
+    auto gemv_phase = [&](const GemvParams& g) -> int {
+        DecodePhase& ph = prog->phases[n++];
+        ph.type = PHASE_GEMV;
+        ph.g = g;
+        return gemv_check(ph.g);
+    };
+    for (int i = 0; i < L; ++i) {
+        const ab_layer& Ly = m->layers[i];
+        __half* att_prev = (__half*)state[3 * i];
+        __half* ffn_prev = (__half*)state[3 * i + 2];
+        {
+            GemvParams p = {};
+            p.K = D;
+            if (i == 0) { p.emb = (const __half*)m->d.emb; p.token = token; p.x_copy = ws.x; }
+            else p.x = ws.x;
+            p.x_prev = att_prev; p.ln_w = (const __half*)Ly.ln1_w; p.ln_b = (const __half*)Ly.ln1_b; p.ln_out = ws.xn;
+            int k = 0;
+            p.seg[k++] = seg_of(Ly.receptance, Ly.x_r, EPI_NONE, ws.r);
+            p.seg[k++] = seg_of(Ly.key, Ly.x_k, EPI_NONE, ws.k);
+            p.seg[k++] = seg_of(Ly.value, Ly.x_v, EPI_NONE, ws.v);
+            p.seg[k++] = seg_of(Ly.w1t, Ly.x_w, EPI_TANH, ws.hw);
+            p.seg[k++] = seg_of(Ly.a1t, Ly.x_a, EPI_NONE, ws.ha);
+            if (i > 0) p.seg[k++] = seg_of(Ly.v1t, Ly.x_v, EPI_NONE, ws.hv);
+            p.seg[k++] = seg_of(Ly.g1t, Ly.x_g, EPI_SIGMOID, ws.hg);
+            p.nseg = k;
+            AB_TRY(gemv_phase(p));
+        }
+        {   // adapter up-projections: rows of [n_embd, rank], each with its own short input
+            GemvParams p = {};
+            int k = 0;
+            auto up = [&](const ab_mat& mt, const __half* x, __half* out) {
+                GemvSeg g = seg_of(mt, nullptr, EPI_NONE, out);
+                g.x = x;
+                p.seg[k++] = g;
+            };
+            up(Ly.w2t, ws.hw, ws.w_raw);
+            up(Ly.a2t, ws.ha, ws.a_raw);
+            if (i > 0) up(Ly.v2t, ws.hv, ws.vg_raw);
+            up(Ly.g2t, ws.hg, ws.g);
+            p.nseg = k;
+            AB_TRY(gemv_phase(p));
+        }
+        {
+            DecodePhase& ph = prog->phases[n++];
+            ph.type = PHASE_HEAD;
+            HeadParams& h = ph.h;
+            h.B = 1; h.T = 1; h.D = D; h.H = H; h.layer0 = (i == 0);
+            h.state = (float*)state[3 * i + 1]; h.r = ws.r; h.k = ws.k; h.v = ws.v; h.v_first = ws.vfirst;
+            h.w_raw = ws.w_raw; h.a_raw = ws.a_raw; h.vg_raw = ws.vg_raw; h.g = ws.g;
+            h.w0 = (const __half*)Ly.w0; h.a0 = (const __half*)Ly.a0; h.v0 = (const __half*)Ly.v0;
+            h.k_k = (const __half*)Ly.k_k; h.k_a = (const __half*)Ly.k_a; h.r_k = (const __half*)Ly.r_k;
+            h.lnx_w = (const __half*)Ly.lnx_w; h.lnx_b = (const __half*)Ly.lnx_b;
+            h.out = ws.att; h.copy_src = ws.xn; h.copy_dst = att_prev;
+        }
+        {
+            GemvParams p = {};
+            p.K = D; p.x = ws.att; p.nseg = 1;
+            p.seg[0] = seg_of(Ly.output, nullptr, EPI_RESID, ws.x, ws.x);
+            AB_TRY(gemv_phase(p));
+        }
+        {
+            GemvParams p = {};
+            p.K = D; p.x = ws.x; p.nseg = 1;
+            p.x_prev = ffn_prev; p.ln_w = (const __half*)Ly.ln2_w; p.ln_b = (const __half*)Ly.ln2_b; p.ln_out = ws.xn2;
+            p.seg[0] = seg_of(Ly.ffn_key, Ly.ffn_x_k, EPI_RELU2, ws.kf);
+            AB_TRY(gemv_phase(p));
+        }
+        {
+            GemvParams p = {};
+            p.nseg = 1;
+            p.seg[0] = seg_of(Ly.ffn_value, nullptr, EPI_RESID, ws.x, ws.x);
+            p.seg[0].x = ws.kf;   // 4*n_embd inputs: read straight from global memory
+            p.copy_src = ws.xn2; p.copy_dst = ffn_prev; p.copy_n = D;
+            AB_TRY(gemv_phase(p));
+        }
+    }
+    GemvParams p = {};
+    p.K = D; p.x = ws.x; p.nseg = 1;
+    p.ln_w = (const __half*)m->d.lnout_w; p.ln_b = (const __half*)m->d.lnout_b;
+    p.seg[0] = seg_of(m->d.head, nullptr, EPI_NONE, logits);
+    AB_TRY(gemv_phase(p));
     return OK;
 }
 
@@ -312,11 +414,37 @@ size_t ab_workspace_bytes(const ab_model* m, int B, int T) {
     return carve(m, B, T, nullptr).total;
 }
 
+size_t ab_decode_program_bytes(const ab_model* m) { return m ? decode_program_bytes(m->d.n_layer) : 0; }
+
+int ab_decode_program_build(ab_model* m, const int32_t* token, void* const* state, void* workspace, void* logits,
+                            void* program, void* stream) {
+    AB_CHECK_ARG(m && token && state && workspace && logits && program, "ab_decode_program_build: null pointer");
+    AB_CHECK_ARG(((uintptr_t)workspace & 255) == 0 && ((uintptr_t)program & 255) == 0,
+                 "ab_decode_program_build: workspace and program must be 256-byte aligned");
+    for (int i = 0; i < 3 * m->d.n_layer; ++i) AB_CHECK_ARG(state[i], "ab_decode_program_build: state[%d] is null", i);
+    for (const ab_layer& l : m->layers)
+        AB_CHECK_ARG(l.w2t.w && l.a2t.w && l.g2t.w, "ab_decode_program_build: transposed adapter up-projections missing");
+    const Workspace ws = carve(m, 1, 1, (unsigned char*)workspace);
+    std::vector<unsigned char> buf;
+    AB_TRY(build_decode_program(m, token, state, ws, (__half*)logits, buf, (const DecodeProgram*)program));
+    AB_CUDA(cudaMemcpyAsync(program, buf.data(), buf.size(), cudaMemcpyHostToDevice, (cudaStream_t)stream));
+    AB_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    return OK;
+}
+
+int ab_decode_run(ab_model* m, void* program, void* stream) {
+    AB_CHECK_ARG(m && program, "ab_decode_run: null pointer");
+    const DecodeProgram* prog = (const DecodeProgram*)program;
+    return decode_launch(prog, const_cast<unsigned*>(&prog->barrier_word), m->stages, m->d.n_embd, 4 * m->d.n_embd,
+                         (cudaStream_t)stream);
+}
+
 int ab_model_set_option(ab_model* m, const char* name, int value) {
     AB_CHECK_ARG(m && name, "ab_model_set_option: null pointer");
     if (!strcmp(name, "stages")) { AB_CHECK_ARG(value >= 1 && value <= 8, "stages must be in [1,8]"); m->stages = value; }
     else if (!strcmp(name, "pdl")) m->use_pdl = value != 0;
     else if (!strcmp(name, "debug_sync")) m->debug_sync = value != 0;
+    else if (!strcmp(name, "timeline")) m->timeline = value != 0;
     else { set_error("unknown option %s", name); return ERR_BAD_ARG; }
     return OK;
 }

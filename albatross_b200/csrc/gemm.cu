@@ -52,7 +52,7 @@ int gemm_launch(const ab_mat& m, int rows, const __half* x, __half* y, int epi, 
         p.x = x + (size_t)r * m.k;
         GemvSeg& g = p.seg[0];
         g.w = m.w; g.scale = m.scale; g.col_scale = m.col_scale; g.tscale = m.tscale;
-        g.fmt = m.fmt; g.epi = epi; g.n_rows = m.n_out;
+        g.fmt = m.fmt; g.epi = epi; g.n_rows = m.n_out; g.K = m.k;
         g.out = y + (size_t)r * m.n_out;
         g.resid = resid ? resid + (size_t)r * m.n_out : nullptr;
         s = gemv_launch(p, stream);

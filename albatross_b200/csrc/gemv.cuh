@@ -10,8 +10,8 @@ enum Epi : int { EPI_NONE = 0, EPI_TANH = 1, EPI_SIGMOID = 2, EPI_RELU2 = 3, EPI
 constexpr int GEMV_MAX_SEG = 7;
 constexpr int GEMV_WARPS = 16;                        // consumer warps; one more warp produces
 constexpr int GEMV_THREADS = (GEMV_WARPS + 1) * 32;
-constexpr int GEMV_TILE_BYTES = 8192;  // weight bytes of one pipeline stage
-constexpr int GEMV_SCALE_BYTES = 1024; // NVFP4 block scales of one stage
+constexpr int GEMV_TILE_BYTES = 4096;  // weight bytes of one pipeline stage
+constexpr int GEMV_SCALE_BYTES = 512;  // NVFP4 block scales of one stage
 constexpr int GEMV_STAGE_BYTES = GEMV_TILE_BYTES + GEMV_SCALE_BYTES;
 constexpr int GEMV_PIECE_BYTES = 4096; // bytes of one row inside a stage: bulk copies below ~4 KB lose bandwidth
 
@@ -19,18 +19,20 @@ constexpr int GEMV_PIECE_BYTES = 4096; // bytes of one row inside a stage: bulk 
 struct GemvSeg {
     const void* w;           // int8 [n,K] | fp16 [n,K] | e2m1 pairs [n,K/2]; rows K-contiguous
     const void* scale;       // int8: float[n] row scales | NVFP4: e4m3 [n,K/16] | fp16: unused
-    const __half* mix;       // token-shift lerp vector [K], or null: take the (normalised) input as is
+    const __half* x;         // own plain input vector [K], or null: the launch's (normalised, shifted) input
+    const __half* mix;       // token-shift lerp vector [K], or null: take the input as is (needs x == null)
     const float* col_scale;  // optional per-input-column scale folded into x (int8 only)
     const __half* resid;     // EPI_RESID: vector added to the result (may alias out)
     __half* out;             // [n]
     float tscale;            // NVFP4 per-tensor scale, 1 otherwise
     int fmt, epi, n_rows;
+    int K;                   // input length of this matrix (== GemvParams::K when x is null)
 };
 
-struct GemvParams {
+struct __align__(16) GemvParams {
     GemvSeg seg[GEMV_MAX_SEG];
-    int nseg, K;
-    const __half* x;        // input vector [K] (ignored when emb != null)
+    int nseg, K;            // K: length of the launch's shared input (0 when every segment brings its own)
+    const __half* x;        // shared input vector [K] (ignored when emb != null)
     const __half* emb;      // optional embedding table [V,K]: x = emb[token[0]]
     const int* token;
     const __half* x_prev;   // token-shift state [K] (needed when any seg has mix)
@@ -41,7 +43,6 @@ struct GemvParams {
     const __half* copy_src; // optional: block 0 copies copy_n halves to copy_dst (token-shift state hand-over)
     __half* copy_dst;
     int copy_n;
-    int smem_flags;         // filled by gemv_launch: 1 = int8 rows, 2 = fp16/NVFP4 rows, 4 = token-shift lerp
     int stages;             // pipeline depth per warp
     int use_pdl;            // kernel was launched with programmatic stream serialization
 };
@@ -69,8 +70,14 @@ __host__ __device__ inline GemvGeom gemv_geom(int fmt, int K) {
     return g;
 }
 __host__ __device__ inline int gemv_rows_per_group(int fmt, int K) { return gemv_geom(fmt, K).R; }
+// Relative consumer cost of one row group (stages x per-stage cost of the format): blocks get equal cost,
+// not equal bytes, because fp16 and NVFP4 rows take more instructions per byte than int8 rows.
+__host__ __device__ inline int gemv_group_cost(int fmt, int K) {
+    return gemv_geom(fmt, K).nkc * (fmt == FMT_I8 ? 2 : (fmt == FMT_F16 ? 3 : 5));
+}
 
-size_t gemv_smem_bytes(const GemvParams& p);
+int gemv_check(GemvParams& p);   // validates and fills per-segment defaults
+int gemv_groups(const GemvParams& p);
 int gemv_launch(const GemvParams& p, cudaStream_t stream);
 
 }  // namespace ab

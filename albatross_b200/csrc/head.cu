@@ -11,60 +11,17 @@
 // One block of 256 threads per (sequence, head). Thread (i = tid/4, q = tid%4) keeps columns
 // [16q, 16q+16) of state row i in registers for all T steps, so a warp's state traffic is one
 // contiguous 2 KiB run (8 rows x 256 B) in each direction and row sums need two shuffles.
-#include "head.cuh"
+#include "head_body.cuh"
 
 namespace ab {
 
 namespace {
-
-constexpr int HT = 256;  // threads per block
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
 }
 __device__ __forceinline__ void cp_async_wait_all() {
     asm volatile("cp.async.commit_group;\n cp.async.wait_group 0;" ::: "memory");
-}
-
-struct StateRow {
-    float s[16];
-};
-
-__device__ __forceinline__ void load_state(StateRow& st, const float* base, int i, int q) {
-    const float4* src = reinterpret_cast<const float4*>(base + i * 64 + q * 16);
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-        const float4 f = src[e];
-        st.s[4 * e] = f.x; st.s[4 * e + 1] = f.y; st.s[4 * e + 2] = f.z; st.s[4 * e + 3] = f.w;
-    }
-}
-__device__ __forceinline__ void store_state(const StateRow& st, float* base, int i, int q) {
-    float4* dst = reinterpret_cast<float4*>(base + i * 64 + q * 16);
-#pragma unroll
-    for (int e = 0; e < 4; ++e) dst[e] = make_float4(st.s[4 * e], st.s[4 * e + 1], st.s[4 * e + 2], st.s[4 * e + 3]);
-}
-
-// One recurrence step for this thread's 16 columns. Vectors are indexed by key column j.
-// Returns y_i (valid in all four lanes of the row).
-__device__ __forceinline__ float wkv_step(StateRow& st, const float* w, const float* k, const float* a,
-                                          const float* b, const float* r, float v_i, int q) {
-    float sa = 0.f;
-#pragma unroll
-    for (int e = 0; e < 16; ++e) sa = fmaf(a[q * 16 + e], st.s[e], sa);
-    sa += __shfl_xor_sync(0xffffffffu, sa, 1);
-    sa += __shfl_xor_sync(0xffffffffu, sa, 2);
-    float y = 0.f;
-#pragma unroll
-    for (int e = 0; e < 16; ++e) {
-        const int j = q * 16 + e;
-        float s = st.s[e];
-        s = fmaf(s, w[j], fmaf(k[j], v_i, sa * b[j]));
-        st.s[e] = s;
-        y = fmaf(s, r[j], y);
-    }
-    y += __shfl_xor_sync(0xffffffffu, y, 1);
-    y += __shfl_xor_sync(0xffffffffu, y, 2);
-    return y;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -106,8 +63,8 @@ __global__ void __launch_bounds__(HT) wkv7_kernel(int T, int C, int H, float* __
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(HT) head_fused_kernel(const __grid_constant__ HeadParams p) {
     extern __shared__ __align__(16) unsigned char dsm[];
-    __shared__ float sr[64], sw[64], sk[64], sa_[64], sb[64], sv[64], sy[64];
-    __shared__ float up[4][64];  // adapter up-projection sums (w, a, v-gate, g)
+    __shared__ HeadShared sh;
+    float (*up)[64] = sh.up;
     const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;
     const int tid = threadIdx.x, i = tid >> 2, q = tid & 3, lane = tid & 31, warp = tid >> 5;
     const int D = p.D;
@@ -178,73 +135,7 @@ __global__ void __launch_bounds__(HT) head_fused_kernel(const __grid_constant__ 
         __syncthreads();
     }
 
-    for (int t = 0; t < p.T; ++t) {
-        const size_t off = ((size_t)b * p.T + t) * D + h * 64;
-        if (warp == 0) {
-            // per-channel glue on two channels per lane; head-wide sums are warp shuffles
-            float kk0[2], av[2], rk[2];
-            float ssq = 0.f, rkr = 0.f;
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const int c = lane + 32 * e, gc = h * 64 + c;
-                const float rr = __half2float(p.r[off + c]);
-                const float kr = __half2float(p.k[off + c]);
-                float vv = __half2float(p.v[off + c]);
-                const float w_raw = ups ? up[0][c] : __half2float(p.w_raw[off + c]);
-                const float a_raw = ups ? up[1][c] : __half2float(p.a_raw[off + c]);
-                const float a = rh(sigmoidf_(rh(__half2float(p.a0[gc]) + a_raw)));
-                kk0[e] = rh(kr * __half2float(p.k_k[gc]));
-                ssq = fmaf(kk0[e], kk0[e], ssq);
-                const float k2 = rh(kr * rh(1.f + rh(rh(a - 1.f) * __half2float(p.k_a[gc]))));
-                if (p.layer0) {
-                    p.v_first[off + c] = __float2half_rn(vv);
-                } else {
-                    const float vg_raw = ups ? up[2][c] : __half2float(p.vg_raw[off + c]);
-                    const float vg = rh(sigmoidf_(rh(__half2float(p.v0[gc]) + vg_raw)));
-                    vv = rh(vv + rh(rh(__half2float(p.v_first[off + c]) - vv) * vg));
-                }
-                // decay in fp32 as on the reference's single-token path (reference/rwkv7.py:241)
-                const float wd = __expf(-0.606531f * sigmoidf_(rh(__half2float(p.w0[gc]) + w_raw)));
-                sr[c] = rr; sw[c] = wd; sk[c] = k2; sv[c] = vv;
-                av[e] = a;
-                rk[e] = rh(rh(rr * k2) * __half2float(p.r_k[gc]));
-                rkr += rk[e];
-            }
-            ssq = warp_sum(ssq);
-            rkr = rh(warp_sum(rkr));
-            const float nrm = fmaxf(rh(sqrtf(ssq)), 1e-12f);
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const int c = lane + 32 * e;
-                const float kk = rh(kk0[e] / nrm);
-                sa_[c] = -kk;
-                sb[c] = rh(kk * av[e]);
-            }
-            __syncthreads();
-            const float y = wkv_step(st, sw, sk, sa_, sb, sr, sv[i], q);
-            if (q == 0) sy[i] = rh(y);
-            __syncthreads();
-            // group norm over the head's 64 channels (eps 64e-5), bonus, gate
-            const float y0 = sy[lane], y1 = sy[lane + 32];
-            const float mean = warp_sum(y0 + y1) * (1.f / 64.f);
-            const float d0 = y0 - mean, d1 = y1 - mean;
-            const float var = warp_sum(d0 * d0 + d1 * d1) * (1.f / 64.f);
-            const float rstd = rsqrtf(var + 64e-5f);
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const int c = lane + 32 * e, gc = h * 64 + c;
-                float o = rh((e ? d1 : d0) * rstd * __half2float(p.lnx_w[gc]) + __half2float(p.lnx_b[gc]));
-                o = rh(o + rh(rkr * sv[c]));
-                const float g = ups ? up[3][c] : __half2float(p.g[off + c]);
-                p.out[off + c] = __float2half_rn(o * g);
-            }
-        } else {
-            __syncthreads();
-            const float y = wkv_step(st, sw, sk, sa_, sb, sr, sv[i], q);
-            if (q == 0) sy[i] = rh(y);
-            __syncthreads();
-        }
-    }
+    head_steps(p, b, h, tid, st, sh, ups, SyncBlock());
     store_state(st, sbase, i, q);
 }
 

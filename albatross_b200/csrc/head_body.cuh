@@ -1,0 +1,142 @@
+// Device-side body of the fused per-head time-mix step, shared by the stand-alone kernel (head.cu)
+// and the persistent batch-1 decode kernel (decode.cu). See head.cu for the math and its citations.
+#pragma once
+#include "head.cuh"
+
+namespace ab {
+
+constexpr int HT = 256;  // threads working on one (sequence, head)
+
+struct HeadShared {
+    float r[64], w[64], k[64], a[64], b[64], v[64], y[64];
+    float up[4][64];  // adapter up-projection sums (w, a, v-gate, g) of the batch-1 stand-alone path
+};
+struct SyncBlock {
+    __device__ __forceinline__ void operator()() const { __syncthreads(); }
+};
+struct SyncNamed256 {  // the first 256 threads of a larger block
+    __device__ __forceinline__ void operator()() const { asm volatile("bar.sync 2, 256;" ::: "memory"); }
+};
+// activations may have been written by another SM earlier in the same kernel: bypass L1
+__device__ __forceinline__ float lda(const __half* p) { return __half2float(__ldcg(p)); }
+
+struct StateRow {
+    float s[16];
+};
+
+__device__ __forceinline__ void load_state(StateRow& st, const float* base, int i, int q) {
+    const float4* src = reinterpret_cast<const float4*>(base + i * 64 + q * 16);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const float4 f = src[e];
+        st.s[4 * e] = f.x; st.s[4 * e + 1] = f.y; st.s[4 * e + 2] = f.z; st.s[4 * e + 3] = f.w;
+    }
+}
+__device__ __forceinline__ void store_state(const StateRow& st, float* base, int i, int q) {
+    float4* dst = reinterpret_cast<float4*>(base + i * 64 + q * 16);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) dst[e] = make_float4(st.s[4 * e], st.s[4 * e + 1], st.s[4 * e + 2], st.s[4 * e + 3]);
+}
+
+// One recurrence step for this thread's 16 columns. Vectors are indexed by key column j.
+// Returns y_i (valid in all four lanes of the row).
+__device__ __forceinline__ float wkv_step(StateRow& st, const float* w, const float* k, const float* a,
+                                          const float* b, const float* r, float v_i, int q) {
+    float sa = 0.f;
+#pragma unroll
+    for (int e = 0; e < 16; ++e) sa = fmaf(a[q * 16 + e], st.s[e], sa);
+    sa += __shfl_xor_sync(0xffffffffu, sa, 1);
+    sa += __shfl_xor_sync(0xffffffffu, sa, 2);
+    float y = 0.f;
+#pragma unroll
+    for (int e = 0; e < 16; ++e) {
+        const int j = q * 16 + e;
+        float s = st.s[e];
+        s = fmaf(s, w[j], fmaf(k[j], v_i, sa * b[j]));
+        st.s[e] = s;
+        y = fmaf(s, r[j], y);
+    }
+    y += __shfl_xor_sync(0xffffffffu, y, 1);
+    y += __shfl_xor_sync(0xffffffffu, y, 2);
+    return y;
+}
+
+
+// All T steps of one (sequence b, head h) for the 256 threads tid = 0..255.
+template <class Sync>
+__device__ __forceinline__ void head_steps(const HeadParams& p, int b, int h, int tid, StateRow& st, HeadShared& sh,
+                                           bool ups, Sync sync) {
+    const int i = tid >> 2, q = tid & 3, lane = tid & 31, warp = tid >> 5;
+    const int D = p.D;
+    float* sr = sh.r; float* sw = sh.w; float* sk = sh.k; float* sa_ = sh.a; float* sb = sh.b; float* sv = sh.v; float* sy = sh.y;
+    float (*up)[64] = sh.up;
+    for (int t = 0; t < p.T; ++t) {
+        const size_t off = ((size_t)b * p.T + t) * D + h * 64;
+        if (warp == 0) {
+            // per-channel glue on two channels per lane; head-wide sums are warp shuffles
+            float kk0[2], av[2], rk[2];
+            float ssq = 0.f, rkr = 0.f;
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int c = lane + 32 * e, gc = h * 64 + c;
+                const float rr = lda(p.r + off + c);
+                const float kr = lda(p.k + off + c);
+                float vv = lda(p.v + off + c);
+                const float w_raw = ups ? up[0][c] : lda(p.w_raw + off + c);
+                const float a_raw = ups ? up[1][c] : lda(p.a_raw + off + c);
+                const float a = rh(sigmoidf_(rh(__half2float(p.a0[gc]) + a_raw)));
+                kk0[e] = rh(kr * __half2float(p.k_k[gc]));
+                ssq = fmaf(kk0[e], kk0[e], ssq);
+                const float k2 = rh(kr * rh(1.f + rh(rh(a - 1.f) * __half2float(p.k_a[gc]))));
+                if (p.layer0) {
+                    p.v_first[off + c] = __float2half_rn(vv);
+                } else {
+                    const float vg_raw = ups ? up[2][c] : lda(p.vg_raw + off + c);
+                    const float vg = rh(sigmoidf_(rh(__half2float(p.v0[gc]) + vg_raw)));
+                    vv = rh(vv + rh(rh(lda(p.v_first + off + c) - vv) * vg));
+                }
+                // decay in fp32 as on the reference's single-token path (reference/rwkv7.py:241)
+                const float wd = __expf(-0.606531f * sigmoidf_(rh(__half2float(p.w0[gc]) + w_raw)));
+                sr[c] = rr; sw[c] = wd; sk[c] = k2; sv[c] = vv;
+                av[e] = a;
+                rk[e] = rh(rh(rr * k2) * __half2float(p.r_k[gc]));
+                rkr += rk[e];
+            }
+            ssq = warp_sum(ssq);
+            rkr = rh(warp_sum(rkr));
+            const float nrm = fmaxf(rh(sqrtf(ssq)), 1e-12f);
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int c = lane + 32 * e;
+                const float kk = rh(kk0[e] / nrm);
+                sa_[c] = -kk;
+                sb[c] = rh(kk * av[e]);
+            }
+            sync();
+            const float y = wkv_step(st, sw, sk, sa_, sb, sr, sv[i], q);
+            if (q == 0) sy[i] = rh(y);
+            sync();
+            // group norm over the head's 64 channels (eps 64e-5), bonus, gate
+            const float y0 = sy[lane], y1 = sy[lane + 32];
+            const float mean = warp_sum(y0 + y1) * (1.f / 64.f);
+            const float d0 = y0 - mean, d1 = y1 - mean;
+            const float var = warp_sum(d0 * d0 + d1 * d1) * (1.f / 64.f);
+            const float rstd = rsqrtf(var + 64e-5f);
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int c = lane + 32 * e, gc = h * 64 + c;
+                float o = rh((e ? d1 : d0) * rstd * __half2float(p.lnx_w[gc]) + __half2float(p.lnx_b[gc]));
+                o = rh(o + rh(rkr * sv[c]));
+                const float g = ups ? up[3][c] : lda(p.g + off + c);
+                p.out[off + c] = __float2half_rn(o * g);
+            }
+        } else {
+            sync();
+            const float y = wkv_step(st, sw, sk, sa_, sb, sr, sv[i], q);
+            if (q == 0) sy[i] = rh(y);
+            sync();
+        }
+    }
+}
+
+}  // namespace ab

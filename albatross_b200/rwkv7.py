@@ -70,7 +70,7 @@ def RWKV7_BATCH_OP(state, r, w, k, v, a, b):
 # --------------------------------------------------------------------------------------------
 class RWKV_x070:
     def __init__(self, args, quant: Optional[str] = "int8", state_dict: Optional[Iterable[Tuple[str, torch.Tensor]]] = None,
-                 device: str = "cuda", use_graph: bool = True):
+                 device: str = "cuda", use_graph: bool = True, decode_mode: Optional[str] = None):
         if not torch.cuda.is_available():
             raise RuntimeError("albatross_b200 needs a CUDA device (sm_100a); there is no CPU path")
         self.args = args
@@ -79,6 +79,10 @@ class RWKV_x070:
         self.quant = quant
         self.device = torch.device(device)
         self.use_graph = use_graph and os.environ.get("ALBATROSS_NO_GRAPH", "0") != "1"
+        # batch-1 decode: "persistent" = one resident kernel per token; "graph" = one launch per phase,
+        # replayed from a CUDA graph; "eager" = one launch per phase from the host
+        self.decode_mode = decode_mode or os.environ.get("ALBATROSS_DECODE_MODE") or ("persistent" if self.use_graph else "eager")
+        assert self.decode_mode in ("persistent", "graph", "eager")
 
         items = state_dict
         if items is None:
@@ -102,6 +106,7 @@ class RWKV_x070:
         self._build_native()
         self._ws: Dict[Tuple[int, int], torch.Tensor] = {}
         self._graphs: Dict[tuple, tuple] = {}
+        self._programs: Dict[tuple, tuple] = {}
         # token ids travel host -> device from a ring of pinned slots; a slot is reused only after the
         # asynchronous copy that read it has completed, so callers need not synchronise between steps
         self._tok_ring = torch.empty(64, dtype=torch.int32).pin_memory()
@@ -174,6 +179,7 @@ class RWKV_x070:
     def set_option(self, name: str, value: int) -> None:
         _lib.check(_lib.lib.ab_model_set_option(self._handle, name.encode(), int(value)), "ab_model_set_option")
         self._graphs.clear()
+        self._programs.clear()
 
     # ---- state ------------------------------------------------------------------------------
     def new_state(self, batch: Optional[int] = None) -> List[torch.Tensor]:
@@ -235,7 +241,9 @@ class RWKV_x070:
     @torch.no_grad()
     def forward_one(self, idx: int, state: List[torch.Tensor]):
         self._check_state(state, None)
-        if not self.use_graph:
+        if self.decode_mode == "persistent":
+            return self._forward_one_persistent(idx, state)
+        if self.decode_mode == "eager":
             tok = torch.tensor([int(idx)], dtype=torch.int32, device=self.device)
             logits = torch.empty(self.vocab, dtype=DTYPE, device=self.device)
             self._run(1, 1, tok, state, logits, False)
@@ -248,6 +256,11 @@ class RWKV_x070:
                 self._graphs.pop(next(iter(self._graphs)))
             self._graphs[key] = entry
         graph, tok_dev, logits_buf = entry
+        self._send_token(idx, tok_dev)
+        graph.replay()
+        return logits_buf.clone(), list(state)
+
+    def _send_token(self, idx: int, tok_dev: torch.Tensor) -> None:
         slot = self._tok_n % 64
         self._tok_n += 1
         ev = self._tok_events[slot]
@@ -258,7 +271,39 @@ class RWKV_x070:
         if ev is None:
             ev = self._tok_events[slot] = torch.cuda.Event()
         ev.record()
-        graph.replay()
+
+    def _program_for(self, state: List[torch.Tensor]):
+        key = tuple(t.data_ptr() for t in state)
+        entry = self._programs.get(key)
+        if entry is None:
+            tok_dev = torch.zeros(1, dtype=torch.int32, device=self.device)
+            logits_buf = torch.empty(self.vocab, dtype=DTYPE, device=self.device)
+            prog = torch.zeros(_lib.lib.ab_decode_program_bytes(self._handle) + 256, dtype=torch.uint8, device=self.device)
+            prog_ptr = (prog.data_ptr() + 255) & ~255
+            ws = self._workspace(1, 1)
+            ptrs = (C.c_void_p * len(state))(*[t.data_ptr() for t in state])
+            _lib.check(_lib.lib.ab_decode_program_build(self._handle, tok_dev.data_ptr(), ptrs, (ws.data_ptr() + 255) & ~255,
+                                                        logits_buf.data_ptr(), prog_ptr,
+                                                        torch.cuda.current_stream().cuda_stream), "ab_decode_program_build")
+            if len(self._programs) >= 4:
+                self._programs.pop(next(iter(self._programs)))
+            entry = self._programs[key] = (prog, prog_ptr, tok_dev, logits_buf)
+        return entry
+
+    def decode_timeline(self, state: List[torch.Tensor]):
+        """Per-phase (start, end) timestamps in ns of the last persistent decode step on `state`, as seen by
+        block 0; needs set_option("timeline", 1) before the program for `state` was built."""
+        prog, prog_ptr, _, _ = self._program_for(state)
+        n = 6 * self.n_layer + 1
+        hdr = _lib.lib.ab_decode_program_bytes(self._handle) - 256 - 16 * n
+        off = (prog_ptr - prog.data_ptr()) + hdr
+        torch.cuda.synchronize()
+        return prog[off:off + 16 * n].view(torch.int64).view(n, 2).cpu().numpy()
+
+    def _forward_one_persistent(self, idx: int, state: List[torch.Tensor]):
+        _, prog_ptr, tok_dev, logits_buf = self._program_for(state)
+        self._send_token(idx, tok_dev)
+        _lib.check(_lib.lib.ab_decode_run(self._handle, prog_ptr, torch.cuda.current_stream().cuda_stream), "ab_decode_run")
         return logits_buf.clone(), list(state)
 
     def _capture(self, state: List[torch.Tensor]):

@@ -105,7 +105,7 @@ def run_ours(a, rank, world, dev):
     args = synth.make_args(a.model)
     torch.cuda.set_device(dev)
     model = RWKV_x070(args, quant=wl["quant"], state_dict=synth.iter_checkpoint(a.model, seed=0, device=f"cuda:{dev}"),
-                      device=f"cuda:{dev}", use_graph=not a.no_graph)
+                      device=f"cuda:{dev}", use_graph=not a.no_graph, decode_mode=a.decode_mode)
     if a.stages:
         model.set_option("stages", a.stages)
     if a.no_pdl:
@@ -114,7 +114,7 @@ def run_ours(a, rank, world, dev):
     g = torch.Generator().manual_seed(1000 + rank)
     n_tok = a.warmup + a.steps + 8
     toks = torch.randint(0, V, (n_tok, B), generator=g)
-    launches_per_step = 5 * args.n_layer + 1
+    launches_per_step = 1 if (B == 1 and model.decode_mode == "persistent") else 5 * args.n_layer + 1
 
     def sync_all():
         torch.cuda.synchronize()
@@ -161,6 +161,11 @@ def run_ours(a, rank, world, dev):
         cur = torch.zeros(1, dtype=torch.int32, device=f"cuda:{dev}")
         logits_buf = torch.empty(V, dtype=torch.float16, device=f"cuda:{dev}")
         step_fn = lambda i: (cur.copy_(tok_dev[i]), model._run(1, 1, cur, state, logits_buf, False))
+    elif B == 1 and model.decode_mode == "persistent":
+        _, prog_ptr, tok_buf, logits_buf = model._program_for(state)
+        from albatross_b200 import _lib as _l
+        st_ = torch.cuda.current_stream().cuda_stream
+        step_fn = lambda i: (tok_buf.copy_(tok_dev[i]), _l.check(_l.lib.ab_decode_run(model._handle, prog_ptr, st_)))
     elif B == 1:
         model.forward(0, state)                     # captures the graph for this state
         graph, tok_buf, logits_buf = model._graphs[tuple(t.data_ptr() for t in state)]
@@ -311,6 +316,7 @@ def main():
     ap.add_argument("--stages", type=int, default=0)
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host (profiling)")
+    ap.add_argument("--decode-mode", default=None, choices=["persistent", "graph", "eager"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--n-out", type=int, default=4096, help="gemv_* workloads: output rows")
     ap.add_argument("--k", type=int, default=4096, help="gemv_* workloads: input length")

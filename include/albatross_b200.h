@@ -115,6 +115,16 @@ void ab_model_destroy(ab_model* m);
 size_t ab_workspace_bytes(const ab_model* m, int B, int T);
 int ab_forward(ab_model* m, int B, int T, const int32_t* tokens, void* const* state, void* workspace,
                void* logits, int full_output, void* stream);
+/* Batch-1 decode as ONE persistent kernel per token (same results as ab_forward with B = T = 1).
+ * ab_decode_program_build writes the token's phase list for a fixed set of buffers (token id, state
+ * tensors, workspace, logits) into `program` (device memory, at least ab_decode_program_bytes(m) bytes,
+ * 256-byte aligned) and synchronises `stream`; ab_decode_run launches the kernel (cooperative launch,
+ * one block per SM). A program stays valid while those buffers stay where they are. Replaces the loop
+ * body of RWKV_x070.forward_one (reference/rwkv7.py:128-157). */
+size_t ab_decode_program_bytes(const ab_model* m);
+int ab_decode_program_build(ab_model* m, const int32_t* token, void* const* state, void* workspace, void* logits,
+                            void* program, void* stream);
+int ab_decode_run(ab_model* m, void* program, void* stream);
 /* Tuning knobs: pipeline depth of the streaming kernels and programmatic dependent launch (default on). */
 int ab_model_set_option(ab_model* m, const char* name, int value);
 

@@ -18,10 +18,11 @@ def golden():
 
 
 @pytest.mark.parametrize("fmt", ["none", "int8", "nvfp4"])
-@pytest.mark.parametrize("graph", [False, True])
-def test_single_token_path_matches_reference_fixture(golden, fmt, graph):
-    """forward(int, state) step by step against logits the unmodified reference produced."""
-    model, args = model_for("tiny", fmt, use_graph=graph)
+@pytest.mark.parametrize("mode", ["eager", "graph", "persistent"])
+def test_single_token_path_matches_reference_fixture(golden, fmt, mode):
+    """forward(int, state) step by step against logits the unmodified reference produced, for the three
+    ways the batch-1 step can be launched."""
+    model, args = model_for("tiny", fmt, decode_mode=mode)
     state = None
     outs = []
     for t in golden["tokens"].tolist():
