@@ -69,6 +69,8 @@ def _load():
     lib.ab_model_set_option.argtypes = [vp, C.c_char_p, i32]
     lib.ab_decode_program_bytes.argtypes = [vp]
     lib.ab_decode_program_bytes.restype = sz
+    lib.ab_decode_timeline_offset.argtypes = [vp]
+    lib.ab_decode_timeline_offset.restype = sz
     lib.ab_decode_program_build.argtypes = [vp, vp, C.POINTER(vp), vp, vp, vp, vp]
     lib.ab_decode_run.argtypes = [vp, vp, vp]
     return lib
@@ -78,7 +80,7 @@ lib = _load()
 
 EXPORTS = ["ab_last_error", "ab_version", "ab_device_status", "ab_wkv7_fwd", "ab_gemv", "ab_gemm_scratch_bytes",
            "ab_gemm", "ab_dequant", "ab_model_create", "ab_model_destroy", "ab_workspace_bytes", "ab_forward",
-           "ab_model_set_option", "ab_decode_program_bytes", "ab_decode_program_build", "ab_decode_run"]
+           "ab_model_set_option", "ab_decode_program_bytes", "ab_decode_timeline_offset", "ab_decode_program_build", "ab_decode_run"]
 
 
 def check(status: int, what: str = "") -> None:

@@ -2,15 +2,14 @@
 //
 // The reference's single-token path (reference/rwkv7.py:128-157) is ~190 dependent steps, each far
 // shorter than a kernel boundary. Here one block per SM stays resident for the whole token:
-//   * the producer warp of each block walks the phase list and streams that block's share of every
-//     weight matrix through the shared-memory rings without ever waiting for another block (weights
-//     do not depend on activations), so HBM stays busy across phase boundaries;
-//   * consumer warps run the phases (matrix-vector products with fused prologue / epilogue, and the
-//     per-head WKV-7 step) and meet at a grid-wide barrier between phases: a monotonically
-//     increasing counter in global memory, arrive = fence + atomic add, wait = bounded acquire spin.
+//   * every warp runs the phases (matrix-vector products with fused prologue / epilogue, and the
+//     per-head WKV-7 step); weights stream HBM -> registers with 128-bit loads;
+//   * blocks meet at a grid-wide barrier between phases: a monotonically increasing counter in
+//     global memory, arrive = release-add, wait = bounded acquire spin;
+//   * before a block goes to the barrier, each of its warps starts a cp.async copy of its first work
+//     item of the next matrix-vector phase into shared memory (weights do not depend on activations),
+//     so HBM keeps streaming through the barrier and the next prologue.
 // Every wait is bounded; on expiry the block sets the device status word and stops waiting.
-#include <cooperative_groups.h>
-
 #include "decode.cuh"
 #include "gemv_body.cuh"
 #include "head_body.cuh"
@@ -29,24 +28,25 @@ __device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
+__device__ __forceinline__ void red_release_add(unsigned* p, unsigned v) {
+    asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 
-// Barrier among the consumer threads of all blocks. Returns false once a wait has run out.
-__device__ __forceinline__ bool grid_barrier(unsigned* counter, unsigned target, int tid, bool& failed) {
+// Barrier among all blocks. `failed` becomes (and stays) true once a wait has run out.
+__device__ __forceinline__ void grid_barrier(unsigned* counter, unsigned target, int tid, bool& failed) {
     __shared__ int s_ok;
-    cons_sync();
+    cons_sync();   // every thread of the block has issued its writes of this phase
     if (tid == 0) {
         int ok = 1;
         if (!failed) {
-            __threadfence();
-            atomicAdd(counter, 1u);
+            red_release_add(counter, 1u);
             uint32_t it = 0;
             while (ld_acquire_u32(counter) < target) {
-                if (++it > (1u << 22)) {
+                if (++it > (1u << 23)) {
                     ok = 0;
                     atomicOr(&g_device_status, DEV_WAIT_HEAD);
                     break;
                 }
-                __nanosleep(20);
             }
             __threadfence();
         } else {
@@ -56,50 +56,65 @@ __device__ __forceinline__ bool grid_barrier(unsigned* counter, unsigned target,
     }
     cons_sync();
     if (!s_ok) failed = true;
-    return !failed;
+}
+
+__device__ __forceinline__ void stage_phase(DecodePhase* dst, const DecodePhase* src, int tid) {
+    for (int j = tid; j < (int)(sizeof(DecodePhase) / 16); j += NT_CONS)
+        reinterpret_cast<uint4*>(dst)[j] = reinterpret_cast<const uint4*>(src)[j];
 }
 
 __global__ void __launch_bounds__(GEMV_THREADS, 1) decode_kernel(const DecodeProgram* __restrict__ prog) {
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ HeadShared hsh;
-    // phase descriptors are staged in shared memory: the inner loops read them constantly
-    __shared__ __align__(16) DecodePhase cons_ph;
-    __shared__ __align__(16) GemvParams prod_g;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // phase descriptors are staged three phases ahead in a ring of four; block plans one matrix-vector phase ahead
+    __shared__ __align__(16) DecodePhase phs[4];
+    __shared__ __align__(16) BlockPlan plans[4];   // staged like the descriptors, indexed by phase & 3
+    const int tid = threadIdx.x;
     const int bid = blockIdx.x, nb = gridDim.x;
     const int n_phases = prog->n_phases;
-    const GemvLayout L = gemv_layout(prog->stages, prog->Kn, 1, prog->Kq);
-    const GemvSmem m = gemv_smem(smem, L, prog->stages);
-    if (tid == 0) gemv_init_barriers(m);
+    const GemvSmem m = gemv_smem(smem, gemv_layout(prog->Kn, 1, prog->xq_bytes));
+
+    const BlockPlan* my_plans = prog->plans + bid;   // plan of phase i: my_plans[i * nb]
+    auto stage_plan = [&](int i) {
+        for (int j = tid; j < (int)(sizeof(BlockPlan) / 16); j += NT_CONS)
+            reinterpret_cast<uint4*>(&plans[i & 3])[j] = reinterpret_cast<const uint4*>(&my_plans[(size_t)i * nb])[j];
+    };
+    for (int i = 0; i < 3 && i < n_phases; ++i) {
+        stage_phase(&phs[i], &prog->phases[i], tid);
+        stage_plan(i);
+    }
     __syncthreads();
 
-    if (warp == GEMV_WARPS) {
-        if (lane < GEMV_WARPS) {
-            ProducerState ps = {0, 0, 0, false};
-            const uint64_t policy = policy_evict_first();
-            for (int i = 0; i < n_phases && !ps.dead; ++i) {
-                const DecodePhase& ph = prog->phases[i];
-                if (ph.type != PHASE_GEMV) continue;
-                __syncwarp(0xffffu);
-                for (int j = lane; j < (int)(sizeof(GemvParams) / 16); j += GEMV_WARPS)
-                    reinterpret_cast<uint4*>(&prod_g)[j] = reinterpret_cast<const uint4*>(&ph.g)[j];
-                __syncwarp(0xffffu);
-                gemv_produce(prod_g, m, ps, lane, bid, nb, policy);
-            }
-        }
-        return;
-    }
-
-    ConsumerState cs = {0, 0, false};
     bool failed = false;
+    int pre_phase = -1;
     for (int i = 0; i < n_phases; ++i) {
-        for (int j = tid; j < (int)(sizeof(DecodePhase) / 16); j += NT_CONS)
-            reinterpret_cast<uint4*>(&cons_ph)[j] = reinterpret_cast<const uint4*>(&prog->phases[i])[j];
-        cons_sync();
-        const DecodePhase& ph = cons_ph;
+        if (i + 3 < n_phases) {
+            stage_phase(&phs[(i + 3) & 3], &prog->phases[i + 3], tid);
+            stage_plan(i + 3);
+        }
+        const DecodePhase& ph = phs[i & 3];
         if (prog->timeline && bid == 0 && tid == 0) prog->timeline[2 * i] = global_ns();
         if (ph.type == PHASE_GEMV) {
-            gemv_consume(ph.g, m, cs, tid, bid, nb);
+            const int j = ph.next_gemv;
+            // one thread plans the next matrix-vector phase while the others run this prologue
+            if (tid == 32 && j >= 0) {
+                // the head of this block's share of the next phase starts moving HBM -> L2 now
+                const GemvParams& q = phs[j & 3].g;
+                const BlockPlan& np_ = plans[j & 3];
+                int budget = 256 * 1024;
+                for (int s = 0; s < q.nseg && budget > 0; ++s) {
+                    const SegPlan& sp = np_.sp[s];
+                    if (sp.n_groups <= 0) continue;
+                    const int row0 = sp.lo * GEMV_ROWS;
+                    const int rows = min(sp.n_groups * GEMV_ROWS, q.seg[s].n_rows - row0);
+                    int bytes = min(rows * sp.row_bytes, budget) & ~15;
+                    if (bytes > 0) prefetch_l2((const unsigned char*)q.seg[s].w + (size_t)row0 * sp.row_bytes, (uint32_t)bytes);
+                    budget -= bytes;
+                }
+            }
+            gemv_consume(ph.g, plans[i & 3], m, tid, bid, i, pre_phase, j >= 0 ? &phs[j & 3].g : nullptr,
+                         j >= 0 ? &plans[j & 3] : nullptr, j,
+                         (prog->timeline && bid == 0) ? prog->timeline + 2 * n_phases + 4 * i : nullptr);
         } else {
             const HeadParams& hp = ph.h;
             for (int h = bid; h < hp.H; h += nb) {   // block-uniform
@@ -118,17 +133,23 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) decode_kernel(const DecodePro
         }
         if (prog->timeline && bid == 0 && tid == 0) prog->timeline[2 * i + 1] = global_ns();
         if (i + 1 < n_phases) grid_barrier(prog->barrier, (unsigned)(i + 1) * nb, tid, failed);
-        if (failed) cs.failed = true;
     }
 }
 
 }  // namespace
 
-size_t decode_program_bytes(int n_layer) {
-    return sizeof(DecodeProgram) + (sizeof(DecodePhase) + 16) * (size_t)(6 * n_layer + 1) + 256;
+size_t decode_plans_offset(int n_phases) {
+    return (sizeof(DecodeProgram) + sizeof(DecodePhase) * (size_t)n_phases + 255) & ~(size_t)255;
+}
+size_t decode_timeline_offset(int n_phases, int n_blocks) {
+    return (decode_plans_offset(n_phases) + sizeof(BlockPlan) * (size_t)n_phases * n_blocks + 255) & ~(size_t)255;
+}
+size_t decode_program_bytes(int n_layer, int n_blocks) {
+    const int n_phases = 6 * n_layer + 1;
+    return decode_timeline_offset(n_phases, n_blocks) + 48 * (size_t)n_phases + 256;
 }
 
-int decode_launch(const DecodeProgram* prog_dev, unsigned* barrier_dev, int stages, int Kn, int Kq, cudaStream_t stream) {
+int decode_launch(const DecodeProgram* prog_dev, unsigned* barrier_dev, int Kn, int xq_bytes, cudaStream_t stream) {
     static int n_sm = 0;
     static size_t max_smem = 0;
     if (!n_sm) {
@@ -143,7 +164,7 @@ int decode_launch(const DecodeProgram* prog_dev, unsigned* barrier_dev, int stag
         max_smem = (size_t)m - fa.sharedSizeBytes;
         n_sm = v;
     }
-    const size_t smem = gemv_layout(stages, Kn, 1, Kq).total;
+    const size_t smem = gemv_layout(Kn, 1, xq_bytes).total;
     AB_CHECK_ARG(smem <= max_smem, "decode: needs %zu bytes of shared memory (limit %zu)", smem, max_smem);
     static size_t smem_set = 0;
     if (smem > smem_set) {

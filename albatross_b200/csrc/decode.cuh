@@ -8,20 +8,28 @@ namespace ab {
 enum PhaseType : int { PHASE_GEMV = 0, PHASE_HEAD = 1 };
 
 struct __align__(16) DecodePhase {
-    int type, pad[3];
+    int type;
+    int next_gemv;   // index of the next matrix-vector phase after this one, or -1
+    int pad[2];
     GemvParams g;
     HeadParams h;
 };
 
+struct __align__(16) BlockPlan;
+
 struct DecodeProgram {
-    int n_phases, stages, Kn, Kq;
+    int n_phases, Kn, xq_bytes, first_gemv;
+    int n_blocks, pad0[3];
+    const BlockPlan* plans;  // [n_phases][n_blocks], computed on the host (device copy follows the phases)
     unsigned* barrier;       // points at barrier_word of the device copy
     unsigned long long* timeline;  // optional: block 0 stores %globaltimer at [2i] phase start, [2i+1] phase end
     unsigned barrier_word, pad[3];
     DecodePhase phases[1];   // n_phases entries
 };
 
-size_t decode_program_bytes(int n_layer);
-int decode_launch(const DecodeProgram* prog_dev, unsigned* barrier_dev, int stages, int Kn, int Kq, cudaStream_t stream);
+size_t decode_program_bytes(int n_layer, int n_blocks);
+size_t decode_plans_offset(int n_phases);       // byte offset of the plan table inside the program buffer
+size_t decode_timeline_offset(int n_phases, int n_blocks);
+int decode_launch(const DecodeProgram* prog_dev, unsigned* barrier_dev, int Kn, int xq_bytes, cudaStream_t stream);
 
 }  // namespace ab

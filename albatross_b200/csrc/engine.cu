@@ -15,6 +15,7 @@
 
 #include "../../include/albatross_b200.h"
 #include "decode.cuh"
+#include "gemv_body.cuh"
 #include "gemm.cuh"
 #include "gemv.cuh"
 #include "head.cuh"
@@ -52,8 +53,9 @@ using namespace ab;
 struct ab_model {
     ab_model_desc d;
     std::vector<ab_layer> layers;
-    int stages = 2;
     int use_pdl = 1;
+    int n_sm = 0;          // blocks of the persistent decode kernel
+    int prog_xq_bytes = 0;
     int debug_sync = 0;  // synchronise after every launch and name the one that failed
     int timeline = 0;    // persistent decode kernel records per-phase timestamps
 };
@@ -125,7 +127,7 @@ int forward_one(ab_model* m, const int32_t* token, void* const* state, const Wor
         __half* ffn_prev = (__half*)state[3 * i + 2];
         {   // LN1 + shift-lerps + r/k/v + adapter-down rows
             GemvParams p = {};
-            p.K = D; p.stages = m->stages; p.use_pdl = m->use_pdl;
+            p.K = D; p.use_pdl = m->use_pdl;
             if (i == 0) { p.emb = (const __half*)m->d.emb; p.token = token; p.x_copy = ws.x; }
             else p.x = ws.x;
             p.x_prev = att_prev; p.ln_w = (const __half*)L.ln1_w; p.ln_b = (const __half*)L.ln1_b; p.ln_out = ws.xn;
@@ -155,27 +157,27 @@ int forward_one(ab_model* m, const int32_t* token, void* const* state, const Wor
         }
         {   // output projection + residual
             GemvParams p = {};
-            p.K = D; p.stages = m->stages; p.use_pdl = m->use_pdl; p.x = ws.att; p.nseg = 1;
+            p.K = D; p.use_pdl = m->use_pdl; p.x = ws.att; p.nseg = 1;
             p.seg[0] = seg_of(L.output, nullptr, EPI_RESID, ws.x, ws.x);
             AB_STEP(m, st, i, "output gemv", gemv_launch(p, st));
         }
         {   // LN2 + shift-lerp + ffn key + relu^2
             GemvParams p = {};
-            p.K = D; p.stages = m->stages; p.use_pdl = m->use_pdl; p.x = ws.x; p.nseg = 1;
+            p.K = D; p.use_pdl = m->use_pdl; p.x = ws.x; p.nseg = 1;
             p.x_prev = ffn_prev; p.ln_w = (const __half*)L.ln2_w; p.ln_b = (const __half*)L.ln2_b; p.ln_out = ws.xn2;
             p.seg[0] = seg_of(L.ffn_key, L.ffn_x_k, EPI_RELU2, ws.kf);
             AB_STEP(m, st, i, "ffn key gemv", gemv_launch(p, st));
         }
         {   // ffn value + residual; hands the new channel-mix token-shift state over
             GemvParams p = {};
-            p.K = 4 * D; p.stages = m->stages; p.use_pdl = m->use_pdl; p.x = ws.kf; p.nseg = 1;
+            p.K = 4 * D; p.use_pdl = m->use_pdl; p.x = ws.kf; p.nseg = 1;
             p.seg[0] = seg_of(L.ffn_value, nullptr, EPI_RESID, ws.x, ws.x);
             p.copy_src = ws.xn2; p.copy_dst = ffn_prev; p.copy_n = D;
             AB_STEP(m, st, i, "ffn value gemv", gemv_launch(p, st));
         }
     }
     GemvParams p = {};
-    p.K = D; p.stages = m->stages; p.use_pdl = m->use_pdl; p.x = ws.x; p.nseg = 1;
+    p.K = D; p.use_pdl = m->use_pdl; p.x = ws.x; p.nseg = 1;
     p.ln_w = (const __half*)m->d.lnout_w; p.ln_b = (const __half*)m->d.lnout_b;
     p.seg[0] = seg_of(m->d.head, nullptr, EPI_NONE, logits);
     AB_STEP(m, st, -1, "head gemv", gemv_launch(p, st));
@@ -189,21 +191,28 @@ int build_decode_program(ab_model* m, const int32_t* token, void* const* state, 
                          std::vector<unsigned char>& buf, const DecodeProgram* dev_addr) {
     const int D = m->d.n_embd, H = D / HEAD, L = m->d.n_layer;
     const int n_phases = 6 * L + 1;
-    buf.assign(sizeof(DecodeProgram) + sizeof(DecodePhase) * (size_t)n_phases, 0);
+    const size_t plans_off = decode_plans_offset(n_phases);
+    buf.assign(plans_off + sizeof(BlockPlan) * (size_t)n_phases * m->n_sm, 0);
     DecodeProgram* prog = reinterpret_cast<DecodeProgram*>(buf.data());
+    prog->n_blocks = m->n_sm;
+    prog->plans = reinterpret_cast<const BlockPlan*>((const unsigned char*)dev_addr + plans_off);
     prog->n_phases = n_phases;
-    prog->stages = m->stages;
     prog->Kn = D;
-    prog->Kq = 4 * D;
+    prog->xq_bytes = 0;
+    prog->first_gemv = 0;
     prog->barrier = const_cast<unsigned*>(&dev_addr->barrier_word);
-    prog->timeline = m->timeline ? (unsigned long long*)((unsigned char*)dev_addr + sizeof(DecodeProgram) +
-                                                          sizeof(DecodePhase) * (size_t)n_phases) : nullptr;
+    prog->timeline = m->timeline ? (unsigned long long*)((unsigned char*)dev_addr +
+                                                          decode_timeline_offset(n_phases, m->n_sm)) : nullptr;
     int n = 0;
     auto gemv_phase = [&](const GemvParams& g) -> int {
         DecodePhase& ph = prog->phases[n++];
         ph.type = PHASE_GEMV;
         ph.g = g;
-        return gemv_check(ph.g);
+        AB_TRY(gemv_check(ph.g));
+        int xq = 0;
+        for (int s = 0; s < ph.g.nseg; ++s) xq += gemv_xq_bytes(ph.g.seg[s].K);
+        prog->xq_bytes = std::max(prog->xq_bytes, xq);
+        return gemv_check_partials(ph.g, m->n_sm);
     };
     for (int i = 0; i < L; ++i) {
         const ab_layer& Ly = m->layers[i];
@@ -280,6 +289,17 @@ int build_decode_program(ab_model* m, const int32_t* token, void* const* state, 
     p.ln_w = (const __half*)m->d.lnout_w; p.ln_b = (const __half*)m->d.lnout_b;
     p.seg[0] = seg_of(m->d.head, nullptr, EPI_NONE, logits);
     AB_TRY(gemv_phase(p));
+    int nxt = -1;
+    for (int i = n_phases - 1; i >= 0; --i) {
+        prog->phases[i].next_gemv = nxt;
+        if (prog->phases[i].type == PHASE_GEMV) nxt = i;
+    }
+    prog->first_gemv = nxt;
+    m->prog_xq_bytes = prog->xq_bytes;
+    BlockPlan* host_plans = reinterpret_cast<BlockPlan*>(buf.data() + plans_off);
+    for (int i = 0; i < n_phases; ++i)
+        if (prog->phases[i].type == PHASE_GEMV)
+            for (int b = 0; b < m->n_sm; ++b) compute_plan(prog->phases[i].g, b, m->n_sm, host_plans[(size_t)i * m->n_sm + b]);
     return OK;
 }
 
@@ -403,6 +423,12 @@ int ab_model_create(const ab_model_desc* desc, ab_model** out) {
     m->d = *desc;
     m->layers.assign(desc->layers, desc->layers + desc->n_layer);
     m->d.layers = m->layers.data();
+    {
+        int dev = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&m->n_sm, cudaDevAttrMultiProcessorCount, dev);
+        if (m->n_sm <= 0) m->n_sm = 148;
+        cudaGetLastError();
+    }
     *out = m;
     return OK;
 }
@@ -414,7 +440,8 @@ size_t ab_workspace_bytes(const ab_model* m, int B, int T) {
     return carve(m, B, T, nullptr).total;
 }
 
-size_t ab_decode_program_bytes(const ab_model* m) { return m ? decode_program_bytes(m->d.n_layer) : 0; }
+size_t ab_decode_program_bytes(const ab_model* m) { return m ? decode_program_bytes(m->d.n_layer, m->n_sm) : 0; }
+size_t ab_decode_timeline_offset(const ab_model* m) { return m ? decode_timeline_offset(6 * m->d.n_layer + 1, m->n_sm) : 0; }
 
 int ab_decode_program_build(ab_model* m, const int32_t* token, void* const* state, void* workspace, void* logits,
                             void* program, void* stream) {
@@ -435,13 +462,12 @@ int ab_decode_program_build(ab_model* m, const int32_t* token, void* const* stat
 int ab_decode_run(ab_model* m, void* program, void* stream) {
     AB_CHECK_ARG(m && program, "ab_decode_run: null pointer");
     const DecodeProgram* prog = (const DecodeProgram*)program;
-    return decode_launch(prog, const_cast<unsigned*>(&prog->barrier_word), m->stages, m->d.n_embd, 4 * m->d.n_embd,
-                         (cudaStream_t)stream);
+    return decode_launch(prog, const_cast<unsigned*>(&prog->barrier_word), m->d.n_embd, m->prog_xq_bytes, (cudaStream_t)stream);
 }
 
 int ab_model_set_option(ab_model* m, const char* name, int value) {
     AB_CHECK_ARG(m && name, "ab_model_set_option: null pointer");
-    if (!strcmp(name, "stages")) { AB_CHECK_ARG(value >= 1 && value <= 8, "stages must be in [1,8]"); m->stages = value; }
+    if (!strcmp(name, "stages")) { (void)value; }   // accepted for compatibility; the streaming depth is fixed
     else if (!strcmp(name, "pdl")) m->use_pdl = value != 0;
     else if (!strcmp(name, "debug_sync")) m->debug_sync = value != 0;
     else if (!strcmp(name, "timeline")) m->timeline = value != 0;

@@ -7,44 +7,35 @@
 
 namespace ab {
 
-namespace {
-
 struct GemvLaunchShape {
-    int Kn, with_dx, Kq;
+    int Kn, with_dx, xq_bytes;
 };
-__host__ __device__ inline GemvLaunchShape gemv_shape(const GemvParams& p) {
+// Shared-memory needs of a launch: the prepared inputs of all its segments (a block touches a subset).
+GemvLaunchShape gemv_shape(const GemvParams& p) {
     GemvLaunchShape sh = {0, 0, 0};
     if (p.emb || p.x) sh.Kn = p.K;
     for (int s = 0; s < p.nseg; ++s) {
         if (p.seg[s].mix) sh.with_dx = 1;
-        if (p.seg[s].K > sh.Kq) sh.Kq = p.seg[s].K;
+        sh.xq_bytes += gemv_xq_bytes(p.seg[s].K);
     }
     return sh;
 }
 
-__global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_stream_kernel(const __grid_constant__ GemvParams p) {
-    extern __shared__ __align__(128) unsigned char smem[];
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const GemvLaunchShape sh = gemv_shape(p);
-    const GemvLayout L = gemv_layout(p.stages, sh.Kn, sh.with_dx, sh.Kq);
-    const GemvSmem m = gemv_smem(smem, L, p.stages);
-    if (tid == 0) gemv_init_barriers(m);
-    __syncthreads();
+namespace {
 
-    if (warp == GEMV_WARPS) {
-        // weights do not depend on the previous kernel: the producer does not wait for it
-        if (lane < GEMV_WARPS) {
-            ProducerState ps = {0, 0, 0, false};
-            gemv_produce(p, m, ps, lane, blockIdx.x, gridDim.x, policy_evict_first());
-        }
-        return;
-    }
+__global__ void __launch_bounds__(GEMV_THREADS, 1)
+gemv_stream_kernel(const __grid_constant__ GemvParams p, const int Kn, const int with_dx, const int xq_bytes) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ BlockPlan bp;
+    const GemvSmem m = gemv_smem(smem, gemv_layout(Kn, with_dx, xq_bytes));
+    if (threadIdx.x == 0) compute_plan(p, blockIdx.x, gridDim.x, bp);
     if (p.use_pdl) {
         pdl_wait();
         pdl_launch_dependents();
     }
-    ConsumerState cs = {0, 0, false};
-    gemv_consume(p, m, cs, tid, blockIdx.x, gridDim.x);
+    __syncthreads();
+    int pre_phase = -1;
+    gemv_consume(p, bp, m, threadIdx.x, blockIdx.x, 0, pre_phase, nullptr, nullptr, -1);
 }
 
 }  // namespace
@@ -64,8 +55,7 @@ int gemv_check(GemvParams& p) {
         AB_CHECK_ARG(((uintptr_t)g.w & 15) == 0, "gemv: segment %d weights not 16-byte aligned", s);
         AB_CHECK_ARG(!g.x || ((uintptr_t)g.x & 15) == 0, "gemv: segment %d input not 16-byte aligned", s);
         AB_CHECK_ARG(g.fmt == FMT_F16 || g.scale, "gemv: segment %d needs scales", s);
-        AB_CHECK_ARG(g.fmt != FMT_FP4 || (((uintptr_t)g.scale & 15) == 0 && g.K % 256 == 0),
-                     "gemv: segment %d: NVFP4 needs 16-byte aligned block scales and K %% 256 == 0", s);
+        AB_CHECK_ARG(g.fmt != FMT_FP4 || g.K % 32 == 0, "gemv: segment %d: NVFP4 needs K %% 32 == 0", s);
         AB_CHECK_ARG(g.epi != EPI_RESID || g.resid, "gemv: segment %d residual missing", s);
         AB_CHECK_ARG(!g.mix || p.x_prev, "gemv: segment %d: token-shift state missing", s);
     }
@@ -74,18 +64,36 @@ int gemv_check(GemvParams& p) {
 
 int gemv_groups(const GemvParams& p) {
     int groups = 0;
-    for (int s = 0; s < p.nseg; ++s) {
-        const int R = gemv_rows_per_group(p.seg[s].fmt, p.seg[s].K);
-        groups += (p.seg[s].n_rows + R - 1) / R;
-    }
+    for (int s = 0; s < p.nseg; ++s) groups += gemv_groups_of(p.seg[s].n_rows);
     return groups;
+}
+
+// Rows and partial sums of one block must fit the epilogue's one-thread-per-row scheme and the partial area.
+int gemv_check_partials(const GemvParams& p, int grid) {
+    long long total = 0;
+    for (int s = 0; s < p.nseg; ++s)
+        total += (long long)gemv_groups_of(p.seg[s].n_rows) * gemv_group_cost(p.seg[s].fmt, p.seg[s].K);
+    const long long per_block = (total + grid - 1) / grid;
+    long long rows = 0, floats = 0;
+    for (int s = 0; s < p.nseg; ++s) {   // worst case: the block's whole share falls into this segment
+        const long long unit = gemv_group_cost(p.seg[s].fmt, p.seg[s].K);
+        long long groups = per_block / unit + 2;
+        if (groups > gemv_groups_of(p.seg[s].n_rows)) groups = gemv_groups_of(p.seg[s].n_rows);
+        rows = std::max(rows, groups * GEMV_ROWS + 8 * GEMV_ROWS);
+        floats = std::max(floats, (groups + 8) * GEMV_ROWS * gemv_slices(p.seg[s].fmt, p.seg[s].K));
+    }
+    if (rows > GEMV_MAX_ROWS_PER_BLOCK || floats > GEMV_PART_FLOATS) {
+        set_error("gemv: %lld rows / %lld partial sums per block exceed the limits (%d / %d)", rows, floats,
+                  GEMV_MAX_ROWS_PER_BLOCK, GEMV_PART_FLOATS);
+        return ERR_TOO_LARGE;
+    }
+    return OK;
 }
 
 int gemv_launch(const GemvParams& p_in, cudaStream_t stream) {
     GemvParams p = p_in;
     int st = gemv_check(p);
     if (st != OK) return st;
-    if (p.stages <= 0) p.stages = 2;
     static int n_sm = 0;
     static size_t max_smem = 0;
     if (!n_sm) {
@@ -94,18 +102,18 @@ int gemv_launch(const GemvParams& p_in, cudaStream_t stream) {
         AB_CUDA(cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev));
         int m = 0;
         AB_CUDA(cudaDeviceGetAttribute(&m, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
-        AB_CUDA(cudaFuncSetAttribute(gemv_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, m));
-        max_smem = (size_t)m;
+        cudaFuncAttributes fa;
+        AB_CUDA(cudaFuncGetAttributes(&fa, gemv_stream_kernel));
+        max_smem = (size_t)m - fa.sharedSizeBytes;
+        AB_CUDA(cudaFuncSetAttribute(gemv_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)max_smem));
         n_sm = v;
     }
     const GemvLaunchShape sh = gemv_shape(p);
-    size_t smem = gemv_layout(p.stages, sh.Kn, sh.with_dx, sh.Kq).total;
-    while (smem > max_smem && p.stages > 1) {
-        --p.stages;
-        smem = gemv_layout(p.stages, sh.Kn, sh.with_dx, sh.Kq).total;
-    }
-    AB_CHECK_ARG(smem <= max_smem, "gemv: K=%d needs %zu bytes of shared memory", sh.Kq, smem);
-    const int grid = max(1, min(n_sm, gemv_groups(p)));
+    const size_t smem = gemv_layout(sh.Kn, sh.with_dx, sh.xq_bytes).total;
+    AB_CHECK_ARG(smem <= max_smem, "gemv: launch needs %zu bytes of shared memory (limit %zu)", smem, max_smem);
+    const int grid = std::max(1, std::min(n_sm, gemv_groups(p)));
+    st = gemv_check_partials(p, grid);
+    if (st != OK) return st;
 
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
@@ -117,7 +125,7 @@ int gemv_launch(const GemvParams& p_in, cudaStream_t stream) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = p.use_pdl ? 1 : 0;
-    AB_CUDA(cudaLaunchKernelEx(&cfg, gemv_stream_kernel, p));
+    AB_CUDA(cudaLaunchKernelEx(&cfg, gemv_stream_kernel, p, sh.Kn, sh.with_dx, sh.xq_bytes));
     return OK;
 }
 

@@ -1,4 +1,4 @@
-// Parameter blocks of the batch-1 streaming matrix-vector kernel (see gemv.cu).
+// Parameter blocks of the batch-1 streaming matrix-vector product (see gemv_body.cuh, gemv.cu).
 #pragma once
 #include "common.cuh"
 
@@ -8,12 +8,13 @@ enum Fmt : int { FMT_F16 = 0, FMT_I8 = 1, FMT_FP4 = 2 };
 enum Epi : int { EPI_NONE = 0, EPI_TANH = 1, EPI_SIGMOID = 2, EPI_RELU2 = 3, EPI_RESID = 4 };
 
 constexpr int GEMV_MAX_SEG = 7;
-constexpr int GEMV_WARPS = 16;                        // consumer warps; one more warp produces
-constexpr int GEMV_THREADS = (GEMV_WARPS + 1) * 32;
-constexpr int GEMV_TILE_BYTES = 4096;  // weight bytes of one pipeline stage
-constexpr int GEMV_SCALE_BYTES = 512;  // NVFP4 block scales of one stage
-constexpr int GEMV_STAGE_BYTES = GEMV_TILE_BYTES + GEMV_SCALE_BYTES;
-constexpr int GEMV_PIECE_BYTES = 4096; // bytes of one row inside a stage: bulk copies below ~4 KB lose bandwidth
+constexpr int GEMV_WARPS = 16;                  // every warp streams weights straight into registers
+constexpr int GEMV_THREADS = GEMV_WARPS * 32;
+constexpr int GEMV_ROWS = 4;                    // output rows a warp works on at a time (they share the input loads)
+constexpr int GEMV_SWEEPS = 4;                  // 512-byte warp loads of each row issued back to back
+constexpr int GEMV_SLICE_BYTES = GEMV_SWEEPS * 512;   // bytes of each row per slice: 16 loads of 16 bytes per lane
+constexpr int GEMV_PART_FLOATS = 4096;          // per-block partial sums: rows of the block x K slices
+constexpr int GEMV_MAX_ROWS_PER_BLOCK = 1024;   // one epilogue thread per output row of the block
 
 // One matrix (a contiguous run of output rows) inside a fused launch.
 struct GemvSeg {
@@ -43,41 +44,23 @@ struct __align__(16) GemvParams {
     const __half* copy_src; // optional: block 0 copies copy_n halves to copy_dst (token-shift state hand-over)
     __half* copy_dst;
     int copy_n;
-    int stages;             // pipeline depth per warp
     int use_pdl;            // kernel was launched with programmatic stream serialization
 };
 
 __host__ __device__ inline int gemv_row_bytes(int fmt, int K) { return fmt == FMT_I8 ? K : (fmt == FMT_F16 ? 2 * K : K / 2); }
-
-// A stage holds R rows x `piece` bytes of each row. Rows shorter than GEMV_PIECE_BYTES are taken whole,
-// and then the R rows of a group are one contiguous run of memory (a single bulk copy).
-struct GemvGeom {
-    int R;        // rows per group
-    int piece;    // bytes of a row per stage
-    int kc;       // K elements per stage
-    int nkc;      // stages per group
-    int contig;   // rows of a stage are contiguous in memory
-};
-__host__ __device__ inline GemvGeom gemv_geom(int fmt, int K) {
-    GemvGeom g;
-    const int rb = gemv_row_bytes(fmt, K);
-    g.piece = rb < GEMV_PIECE_BYTES ? rb : GEMV_PIECE_BYTES;
-    g.R = GEMV_TILE_BYTES / g.piece;
-    if (g.R > 8) g.R = 8;
-    g.kc = fmt == FMT_I8 ? g.piece : (fmt == FMT_F16 ? g.piece / 2 : g.piece * 2);
-    g.nkc = (K + g.kc - 1) / g.kc;
-    g.contig = g.piece == rb;
-    return g;
-}
-__host__ __device__ inline int gemv_rows_per_group(int fmt, int K) { return gemv_geom(fmt, K).R; }
-// Relative consumer cost of one row group (stages x per-stage cost of the format): blocks get equal cost,
-// not equal bytes, because fp16 and NVFP4 rows take more instructions per byte than int8 rows.
+__host__ __device__ inline int gemv_slices(int fmt, int K) { return (gemv_row_bytes(fmt, K) + GEMV_SLICE_BYTES - 1) / GEMV_SLICE_BYTES; }
+__host__ __device__ inline int gemv_groups_of(int n_rows) { return (n_rows + GEMV_ROWS - 1) / GEMV_ROWS; }
+// Relative cost of one row group: blocks get equal cost, not equal bytes, because fp16 and NVFP4 rows take
+// more instructions per byte than int8 rows.
 __host__ __device__ inline int gemv_group_cost(int fmt, int K) {
-    return gemv_geom(fmt, K).nkc * (fmt == FMT_I8 ? 2 : (fmt == FMT_F16 ? 3 : 5));
+    return gemv_slices(fmt, K) * (fmt == FMT_I8 ? 2 : (fmt == FMT_F16 ? 3 : 4));
 }
+// Shared-memory bytes of one segment's prepared input (int8: high + low bytes; otherwise fp16).
+__host__ __device__ inline int gemv_xq_bytes(int K) { return 2 * ((K + 511) & ~511); }
 
 int gemv_check(GemvParams& p);   // validates and fills per-segment defaults
 int gemv_groups(const GemvParams& p);
+int gemv_check_partials(const GemvParams& p, int grid);
 int gemv_launch(const GemvParams& p, cudaStream_t stream);
 
 }  // namespace ab

@@ -295,10 +295,12 @@ class RWKV_x070:
         block 0; needs set_option("timeline", 1) before the program for `state` was built."""
         prog, prog_ptr, _, _ = self._program_for(state)
         n = 6 * self.n_layer + 1
-        hdr = _lib.lib.ab_decode_program_bytes(self._handle) - 256 - 16 * n
+        hdr = _lib.lib.ab_decode_timeline_offset(self._handle)
         off = (prog_ptr - prog.data_ptr()) + hdr
         torch.cuda.synchronize()
-        return prog[off:off + 16 * n].view(torch.int64).view(n, 2).cpu().numpy()
+        raw = prog[off:off + 48 * n].view(torch.int64).cpu().numpy()
+        self.last_timeline_detail = raw[2 * n:].reshape(n, 4)   # per phase: input ready, prepared, streamed, reduced
+        return raw[:2 * n].reshape(n, 2)
 
     def _forward_one_persistent(self, idx: int, state: List[torch.Tensor]):
         _, prog_ptr, tok_dev, logits_buf = self._program_for(state)

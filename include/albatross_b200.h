@@ -122,6 +122,9 @@ int ab_forward(ab_model* m, int B, int T, const int32_t* tokens, void* const* st
  * one block per SM). A program stays valid while those buffers stay where they are. Replaces the loop
  * body of RWKV_x070.forward_one (reference/rwkv7.py:128-157). */
 size_t ab_decode_program_bytes(const ab_model* m);
+/* Profiling aid: byte offset, inside the program buffer, of the per-phase timestamps that the kernel writes
+ * when the "timeline" option was set before ab_decode_program_build. */
+size_t ab_decode_timeline_offset(const ab_model* m);
 int ab_decode_program_build(ab_model* m, const int32_t* token, void* const* state, void* workspace, void* logits,
                             void* program, void* stream);
 int ab_decode_run(ab_model* m, void* program, void* stream);
