@@ -87,6 +87,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) decode_kernel(const DecodePro
 
     bool failed = false;
     int pre_phase = -1;
+    unsigned n_barriers = 0;
     for (int i = 0; i < n_phases; ++i) {
         if (i + 3 < n_phases) {
             stage_phase(&phs[(i + 3) & 3], &prog->phases[i + 3], tid);
@@ -132,7 +133,10 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) decode_kernel(const DecodePro
             }
         }
         if (prog->timeline && bid == 0 && tid == 0) prog->timeline[2 * i + 1] = global_ns();
-        if (i + 1 < n_phases) grid_barrier(prog->barrier, (unsigned)(i + 1) * nb, tid, failed);
+        if (i + 1 < n_phases) {
+            if (ph.no_barrier) cons_sync();   // same block produces and consumes: a block barrier orders the global writes
+            else grid_barrier(prog->barrier, (unsigned)(++n_barriers) * nb, tid, failed);
+        }
     }
 }
 

@@ -10,7 +10,8 @@ enum PhaseType : int { PHASE_GEMV = 0, PHASE_HEAD = 1 };
 struct __align__(16) DecodePhase {
     int type;
     int next_gemv;   // index of the next matrix-vector phase after this one, or -1
-    int pad[2];
+    int no_barrier;  // the next phase only consumes what this block itself produced: no grid barrier in between
+    int rows_per_block;  // > 0: block b owns rows [b * rows_per_block, +rows_per_block) of every segment
     GemvParams g;
     HeadParams h;
 };

@@ -249,6 +249,10 @@ int build_decode_program(ab_model* m, const int32_t* token, void* const* state, 
             up(Ly.g2t, ws.hg, ws.g);
             p.nseg = k;
             AB_TRY(gemv_phase(p));
+            if (false && H <= m->n_sm) {   // measured slower than the all-block phase (short rows): block h computes the 64 channels of head h, then runs head h without a grid barrier
+                prog->phases[n - 1].no_barrier = 1;
+                prog->phases[n - 1].rows_per_block = HEAD;
+            }
         }
         {
             DecodePhase& ph = prog->phases[n++];
@@ -299,7 +303,11 @@ int build_decode_program(ab_model* m, const int32_t* token, void* const* state, 
     BlockPlan* host_plans = reinterpret_cast<BlockPlan*>(buf.data() + plans_off);
     for (int i = 0; i < n_phases; ++i)
         if (prog->phases[i].type == PHASE_GEMV)
-            for (int b = 0; b < m->n_sm; ++b) compute_plan(prog->phases[i].g, b, m->n_sm, host_plans[(size_t)i * m->n_sm + b]);
+            for (int b = 0; b < m->n_sm; ++b) {
+                BlockPlan& bp = host_plans[(size_t)i * m->n_sm + b];
+                if (prog->phases[i].rows_per_block > 0) compute_plan_rows(prog->phases[i].g, b, prog->phases[i].rows_per_block, bp);
+                else compute_plan(prog->phases[i].g, b, m->n_sm, bp);
+            }
     return OK;
 }
 

@@ -147,6 +147,40 @@ __host__ __device__ inline void compute_plan(const GemvParams& p, int bid, int n
     bp.valid = 1;
 }
 
+// Plan that gives block `bid` the rows [bid * rows_per_block, (bid + 1) * rows_per_block) of EVERY segment (and
+// nothing to blocks past the last row): used when a later step of the same block consumes exactly those
+// rows, e.g. the per-head adapter up-projections that feed the head's own WKV step.
+__host__ __device__ inline void compute_plan_rows(const GemvParams& p, int bid, int rows_per_block, BlockPlan& bp) {
+    int items = 0, rows = 0, part = 0, xq = 0;
+    for (int s = 0; s < p.nseg; ++s) {
+        const GemvSeg& sg = p.seg[s];
+        const int n = gemv_groups_of(sg.n_rows), gpb = rows_per_block / GEMV_ROWS;
+        int l = bid * gpb, h = l + gpb;
+        if (l > n) l = n;
+        if (h > n) h = n;
+        SegPlan& q = bp.sp[s];
+        q.lo = l;
+        q.n_groups = h - l;
+        q.nks = gemv_slices(sg.fmt, sg.K);
+        q.row_bytes = gemv_row_bytes(sg.fmt, sg.K);
+        q.chunk = q.nks;
+        q.npc = 1;
+        q.item_base = items;
+        q.n_items = q.n_groups * q.npc;
+        q.row_base = rows;
+        q.part_base = part;
+        q.xq_off = xq;
+        items += q.n_items;
+        rows += q.n_groups * GEMV_ROWS;
+        part += q.n_groups * GEMV_ROWS * q.npc;
+        if (q.n_groups > 0) xq += gemv_xq_bytes(sg.K);
+    }
+    bp.n_items = items;
+    bp.n_rows = rows;
+    bp.nseg = p.nseg;
+    bp.valid = 1;
+}
+
 // ---- work items ------------------------------------------------------------------------------------
 // In bytes every format looks the same: an item is GEMV_ROWS rows x 1024 bytes of each row starting at byte
 // `sb`; lane l reads bytes [sb + u*512 + l*16, +16) of each row for u = 0, 1.

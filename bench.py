@@ -114,7 +114,10 @@ def run_ours(a, rank, world, dev):
     g = torch.Generator().manual_seed(1000 + rank)
     n_tok = a.warmup + a.steps + 8
     toks = torch.randint(0, V, (n_tok, B), generator=g)
-    launches_per_step = 1 if (B == 1 and model.decode_mode == "persistent") else 5 * args.n_layer + 1
+    if B > 1:      # gather + per block (2 LN, 2 lerp, 13 matrix products (11 in block 0), WKV) + final LN + head
+        launches_per_step = 1 + 18 * args.n_layer - 2 + 2
+    else:
+        launches_per_step = 1 if model.decode_mode == "persistent" else 5 * args.n_layer + 1
 
     def sync_all():
         torch.cuda.synchronize()

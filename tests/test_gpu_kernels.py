@@ -127,3 +127,54 @@ def test_wkv7_operator_rejects_bad_shapes():
     from albatross_b200 import _lib
     assert _lib.lib.ab_wkv7_fwd(1, 1, 96, 2, 16, 16, 16, 16, 16, 16, 16, 16, None) == -1
     assert b"C == H*64" in _lib.lib.ab_last_error()
+
+
+def _gemm(pm, x, epi=0, resid=None):
+    from albatross_b200 import _lib
+    rows = x.shape[0]
+    y = torch.empty(rows, pm.n_out, dtype=torch.float16, device="cuda")
+    mat = pm.as_mat()
+    scratch = torch.empty(max(256, _lib.lib.ab_gemm_scratch_bytes(C.byref(mat), rows)), dtype=torch.uint8, device="cuda")
+    _lib.check(_lib.lib.ab_gemm(C.byref(mat), rows, x.data_ptr(), y.data_ptr(), epi,
+                                None if resid is None else resid.data_ptr(), scratch.data_ptr(), _stream()), "ab_gemm")
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    return y
+
+
+@pytest.mark.parametrize("fmt", ["int8", "nvfp4", "none"])
+@pytest.mark.parametrize("rows,n,k", [(1, 128, 64), (3, 200, 256), (17, 128, 768), (64, 1000, 1024), (320, 512, 4096),
+                                      (300, 130, 3072), (400, 256, 512)])
+def test_batched_product_against_oracle(fmt, rows, n, k):
+    """Tensor-core path: ragged batch (not a multiple of 16), ragged output rows (not a multiple of 128),
+    batch 320 (two MMAs of N = 160) and more than one batch tile (400 rows)."""
+    from albatross_b200 import quant
+    torch.manual_seed(rows * 7 + n + k)
+    w = torch.randn(n, k) * 0.02
+    x = torch.randn(rows, k).half()
+    pm = quant.quantize(w.cuda(), None if fmt == "none" else fmt)
+    wq = qo.fake_quantize(w.half().float().numpy() if fmt == "none" else w.numpy(), fmt)
+    want = x.double().numpy() @ wq.astype(np.float64).T
+    got = _gemm(pm, x.cuda()).float().cpu().numpy()
+    assert rel_err(got, want) < 3e-3
+
+
+def test_batched_product_small_k_and_epilogues():
+    """Adapter-sized products (K = 16 ... 480, not multiples of the 64-input k-step) and the fused epilogues."""
+    from albatross_b200 import _lib, quant
+    torch.manual_seed(5)
+    for k in (16, 48, 96, 480):
+        w = torch.randn(256, k) * 0.1
+        x = torch.randn(20, k).half()
+        pm = quant.pack_fp16(w.cuda())
+        want = x.double().numpy() @ w.half().double().numpy().T
+        assert rel_err(_gemm(pm, x.cuda()).float().cpu().numpy(), want) < 3e-3
+    w = torch.randn(192, 256) * 0.05
+    x = torch.randn(33, 256).half()
+    pm = quant.quantize_int8(w.cuda())
+    base = x.double().numpy() @ qo.fake_quantize(w.numpy(), "int8").astype(np.float64).T
+    resid = torch.randn(33, 192).half()
+    for epi, fn in ((_lib.EPI_TANH, np.tanh), (_lib.EPI_SIGMOID, lambda v: 1 / (1 + np.exp(-v))),
+                    (_lib.EPI_RELU2, lambda v: np.maximum(v, 0) ** 2), (_lib.EPI_RESID, lambda v: v + resid.double().numpy())):
+        got = _gemm(pm, x.cuda(), epi, resid.cuda() if epi == _lib.EPI_RESID else None).float().cpu().numpy()
+        assert rel_err(got, fn(base)) < 4e-3
