@@ -93,7 +93,17 @@ Workspace carve(const ab_model* m, int B, int T, unsigned char* base) {
     w.w_raw = take(M * D); w.a_raw = take(M * D); w.vg_raw = take(M * D); w.g = take(M * D);
     w.xlast = batched ? take((size_t)B * D) : nullptr;
     w.gemm_scratch = base + off;
-    off += al(batched ? gemm_scratch_bytes(m->d.head, (int)M) : 0);
+    if (batched) {
+        size_t need = gemm_scratch_bytes(m->d.head, (int)M);
+        for (const ab_layer& l : m->layers) {   // the products launched alone may be split along K
+            need = std::max(need, gemm_scratch_bytes(l.output, (int)M));
+            need = std::max(need, gemm_scratch_bytes(l.ffn_key, (int)M));
+            need = std::max(need, gemm_scratch_bytes(l.ffn_value, (int)M));
+            need = std::max(need, gemm_scratch_bytes(l.receptance, (int)M) * 8);   // grouped launches never split more
+            break;                                                                   // all blocks have the same shapes
+        }
+        off += al(need);
+    }
     w.total = off;
     return w;
 }
@@ -311,6 +321,31 @@ int build_decode_program(ab_model* m, const int32_t* token, void* const* state, 
     return OK;
 }
 
+GemmOp gemm_op(const ab_mat& w, const __half* x, __half* y, int epi, const __half* resid = nullptr) {
+    GemmOp o = {};
+    o.w = w; o.x = x; o.y = y; o.epi = epi; o.resid = resid;
+    return o;
+}
+int time_mix_down_ops(const ab_layer& L, int layer, const Workspace& ws, GemmOp* ops) {
+    int n = 0;
+    ops[n++] = gemm_op(L.receptance, ws.mix[0], ws.r, EPI_NONE);
+    ops[n++] = gemm_op(L.key, ws.mix[1], ws.k, EPI_NONE);
+    ops[n++] = gemm_op(L.value, ws.mix[2], ws.v, EPI_NONE);
+    ops[n++] = gemm_op(L.w1t, ws.mix[3], ws.hw, EPI_TANH);
+    ops[n++] = gemm_op(L.a1t, ws.mix[4], ws.ha, EPI_NONE);
+    ops[n++] = gemm_op(L.g1t, ws.mix[5], ws.hg, EPI_SIGMOID);
+    if (layer > 0) ops[n++] = gemm_op(L.v1t, ws.mix[2], ws.hv, EPI_NONE);
+    return n;
+}
+int time_mix_up_ops(const ab_layer& L, int layer, const Workspace& ws, GemmOp* ops) {
+    int n = 0;
+    ops[n++] = gemm_op(L.w2t, ws.hw, ws.w_raw, EPI_NONE);
+    ops[n++] = gemm_op(L.a2t, ws.ha, ws.a_raw, EPI_NONE);
+    ops[n++] = gemm_op(L.g2t, ws.hg, ws.g, EPI_NONE);
+    if (layer > 0) ops[n++] = gemm_op(L.v2t, ws.hv, ws.vg_raw, EPI_NONE);
+    return n;
+}
+
 int forward_rows(ab_model* m, int B, int T, const int32_t* tokens, void* const* state, const Workspace& ws,
                  __half* logits, int full_output, cudaStream_t st) {
     const int D = m->d.n_embd, H = D / HEAD, M = B * T;
@@ -324,18 +359,15 @@ int forward_rows(ab_model* m, int B, int T, const int32_t* tokens, void* const* 
         for (int j = 0; j < 6; ++j) { mp.mix[j] = (const __half*)mv[j]; mp.out[j] = ws.mix[j]; }
         AB_TRY(mix_rows(mp, st));
         void* sc = ws.gemm_scratch;
-        AB_TRY(gemm_launch(L.receptance, M, ws.mix[0], ws.r, EPI_NONE, nullptr, sc, st));
-        AB_TRY(gemm_launch(L.key, M, ws.mix[1], ws.k, EPI_NONE, nullptr, sc, st));
-        AB_TRY(gemm_launch(L.value, M, ws.mix[2], ws.v, EPI_NONE, nullptr, sc, st));
-        AB_TRY(gemm_launch(L.w1t, M, ws.mix[3], ws.hw, EPI_TANH, nullptr, sc, st));
-        AB_TRY(gemm_launch(L.a1t, M, ws.mix[4], ws.ha, EPI_NONE, nullptr, sc, st));
-        AB_TRY(gemm_launch(L.g1t, M, ws.mix[5], ws.hg, EPI_SIGMOID, nullptr, sc, st));
-        AB_TRY(gemm_launch(L.w2t, M, ws.hw, ws.w_raw, EPI_NONE, nullptr, sc, st));
-        AB_TRY(gemm_launch(L.a2t, M, ws.ha, ws.a_raw, EPI_NONE, nullptr, sc, st));
-        AB_TRY(gemm_launch(L.g2t, M, ws.hg, ws.g, EPI_NONE, nullptr, sc, st));
-        if (i > 0) {
-            AB_TRY(gemm_launch(L.v1t, M, ws.mix[2], ws.hv, EPI_NONE, nullptr, sc, st));
-            AB_TRY(gemm_launch(L.v2t, M, ws.hv, ws.vg_raw, EPI_NONE, nullptr, sc, st));
+        {   // r, k, v and the adapter down-projections: one grouped launch
+            GemmOp ops[8];
+            const int n = time_mix_down_ops(L, i, ws, ops);
+            AB_TRY(gemm_group_launch(ops, n, M, sc, st));
+        }
+        {   // adapter up-projections
+            GemmOp ops[8];
+            const int n = time_mix_up_ops(L, i, ws, ops);
+            AB_TRY(gemm_group_launch(ops, n, M, sc, st));
         }
         HeadParams h = {};
         h.B = B; h.T = T; h.D = D; h.H = H; h.layer0 = (i == 0);

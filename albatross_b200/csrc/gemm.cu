@@ -30,16 +30,33 @@ constexpr int G_STAGES = 3;
 constexpr int G_BM = 128;        // weight rows per block
 constexpr int G_BK = 64;         // inputs per k-step (128 bytes of fp16 = one swizzle row)
 constexpr int G_A_BYTES = G_BM * G_BK * 2;
+constexpr int G_RAW_BYTES = 48 * 1024;   // ring of raw (still quantised) weight k-steps filled by cp.async
+constexpr int G_MAX_OPS = 8;
+constexpr int G_COUNTERS = 4096;         // split-K arrival counters at the start of the scratch area
 
-struct GemmParams {
+// One matrix product of a grouped launch.
+struct GemmProb {
     ab_mat w;
     const __half* resid;
     __half* y;
+    int epi;
+    int cta_base;     // first blockIdx.x of this product
+    int ksplit;       // blocks that share one output tile along K
+    int tile_base;    // first split-K tile id (counter / partial index)
+    long long part_base;   // float offset of its split-K partial sums in the scratch area
+};
+struct GemmGroup {
+    GemmProb pr[G_MAX_OPS];
+    int n_prob;
     int rows;       // batch rows (B*T)
     int n_tile;     // batch rows per block tile
     int n_inst;     // MMAs per k-substep (1, or 2 when n_tile > 256)
-    int epi;
     int tmem_cols;
+    unsigned* counters;
+    float* partials;
+};
+struct GemmMaps {
+    CUtensorMap m[G_MAX_OPS];
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -81,6 +98,17 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t* v) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ void cp_async_16(void* dst, const void* src, bool ok) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(ok ? 16 : 0) : "memory");
+}
+__device__ __forceinline__ void cp_async_4(void* dst, const void* src, bool ok) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(ok ? 4 : 0) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
 // K-major operand tile, 128-byte swizzle: rows of 128 bytes, groups of 8 rows 1024 bytes apart.
 __device__ __forceinline__ uint64_t umma_desc_sw128(const void* smem) {
     const uint32_t a = smem_u32(smem);
@@ -101,44 +129,55 @@ __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
     return *reinterpret_cast<const uint32_t*>(&h);
 }
 
-// De-quantise 64 inputs of one weight row into eight 16-byte chunks of fp16 (chunk c = inputs 8c..8c+7).
-__device__ __forceinline__ void dequant_row64(const ab_mat& w, int row, int k0, uint4* out) {
-    const int K = w.k;
-    if (row >= w.n_out) {
-#pragma unroll
-        for (int c = 0; c < 8; ++c) out[c] = make_uint4(0, 0, 0, 0);
-        return;
+// Raw bytes of one weight row per k-step (64 inputs), and 16-byte chunks in them.
+__device__ __forceinline__ int raw_row_bytes(int fmt) { return fmt == FMT_I8 ? 64 : (fmt == FMT_F16 ? 128 : 32); }
+
+// Start copying the raw weights of k-step `ks` of row `row` into a ring slot (chunk-major: chunk q of row r at
+// q * 2048 + r * 16, so that the owner's read-back is conflict free); NVFP4 block scales (4 bytes) follow.
+__device__ __forceinline__ void raw_issue(const ab_mat& w, int row, int r_local, int ks, unsigned char* slot) {
+    const int K = w.k, k0 = ks * G_BK;
+    const int rb = raw_row_bytes(w.fmt), nq = rb / 16;
+    const bool row_ok = row < w.n_out;
+    const unsigned char* src = reinterpret_cast<const unsigned char*>(w.w) +
+                               (row_ok ? ((size_t)row * K + k0) * rb / 64 : 0);
+    const int epc = 16 * 64 / rb;   // inputs per 16-byte chunk
+    for (int q = 0; q < nq; ++q) cp_async_16(slot + q * 2048 + r_local * 16, src + q * 16, row_ok && k0 + q * epc < K);
+    if (w.fmt == FMT_FP4) {
+        const unsigned char* ssrc = reinterpret_cast<const unsigned char*>(w.scale) + (row_ok ? ((size_t)row * K + k0) / 16 : 0);
+        cp_async_4(slot + nq * 2048 + r_local * 4, ssrc, row_ok && k0 < K);
     }
-    if (w.fmt == FMT_I8) {
-        const signed char* src = reinterpret_cast<const signed char*>(w.w) + (size_t)row * K + k0;
+}
+
+// De-quantise the 64 inputs of this thread's row from a landed ring slot into eight 16-byte chunks of fp16
+// (chunk c = inputs 8c..8c+7). Invalid rows / inputs were zero-filled by the copy.
+__device__ __forceinline__ void raw_dequant(int fmt, int r_local, const unsigned char* slot, uint4* out) {
+    if (fmt == FMT_I8) {
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-            uint4 raw = make_uint4(0, 0, 0, 0);
-            if (k0 + q * 16 < K) raw = __ldg(reinterpret_cast<const uint4*>(src + q * 16));
+            const uint4 raw = *reinterpret_cast<const uint4*>(slot + q * 2048 + r_local * 16);
             const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
             uint32_t h[8];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const int b0 = (int)(signed char)(words[e] & 0xff), b1 = (int)(signed char)((words[e] >> 8) & 0xff);
-                const int b2 = (int)(signed char)((words[e] >> 16) & 0xff), b3 = (int)(signed char)(words[e] >> 24);
-                h[2 * e] = pack_h2((float)b0, (float)b1);
-                h[2 * e + 1] = pack_h2((float)b2, (float)b3);
+                // int8 -> fp16 exactly: bytes b0, b1 into the mantissas of 1024 + (b ^ 0x80), then subtract 1152
+                const uint32_t x = words[e] ^ 0x80808080u;
+                const uint32_t lo = __byte_perm(x, 0x64646464u, 0x4140), hi = __byte_perm(x, 0x64646464u, 0x4342);
+                const __half2 bias = __floats2half2_rn(1152.f, 1152.f);
+                const __half2 l2 = __hsub2(*reinterpret_cast<const __half2*>(&lo), bias);
+                const __half2 h2 = __hsub2(*reinterpret_cast<const __half2*>(&hi), bias);
+                h[2 * e] = *reinterpret_cast<const uint32_t*>(&l2);
+                h[2 * e + 1] = *reinterpret_cast<const uint32_t*>(&h2);
             }
             out[2 * q] = make_uint4(h[0], h[1], h[2], h[3]);
             out[2 * q + 1] = make_uint4(h[4], h[5], h[6], h[7]);
         }
-    } else if (w.fmt == FMT_F16) {
-        const __half* src = reinterpret_cast<const __half*>(w.w) + (size_t)row * K + k0;
+    } else if (fmt == FMT_F16) {
 #pragma unroll
-        for (int c = 0; c < 8; ++c)
-            out[c] = (k0 + c * 8 < K) ? __ldg(reinterpret_cast<const uint4*>(src + c * 8)) : make_uint4(0, 0, 0, 0);
+        for (int c = 0; c < 8; ++c) out[c] = *reinterpret_cast<const uint4*>(slot + c * 2048 + r_local * 16);
     } else {
-        const unsigned char* src = reinterpret_cast<const unsigned char*>(w.w) + ((size_t)row * K + k0) / 2;
-        const unsigned char* ssrc = reinterpret_cast<const unsigned char*>(w.scale) + ((size_t)row * K + k0) / 16;
-        const bool in = k0 < K;   // NVFP4 matrices have K % 64 == 0
-        const uint4 r0 = in ? __ldg(reinterpret_cast<const uint4*>(src)) : make_uint4(0, 0, 0, 0);
-        const uint4 r1 = in ? __ldg(reinterpret_cast<const uint4*>(src + 16)) : make_uint4(0, 0, 0, 0);
-        const uint32_t sc4 = in ? __ldg(reinterpret_cast<const uint32_t*>(ssrc)) : 0u;
+        const uint4 r0 = *reinterpret_cast<const uint4*>(slot + r_local * 16);
+        const uint4 r1 = *reinterpret_cast<const uint4*>(slot + 2048 + r_local * 16);
+        const uint32_t sc4 = *reinterpret_cast<const uint32_t*>(slot + 4096 + r_local * 4);
         const uint32_t words[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
 #pragma unroll
         for (int c = 0; c < 8; ++c) {   // chunk c: 8 inputs = 4 bytes; scale block = c / 2
@@ -155,21 +194,42 @@ __device__ __forceinline__ void dequant_row64(const ab_mat& w, int row, int k0, 
     }
 }
 
-__global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x,
-                                                        const __grid_constant__ GemmParams p) {
+__device__ __forceinline__ float apply_epi(int epi, float o) {
+    switch (epi) {
+        case EPI_TANH: return tanhf(o);
+        case EPI_SIGMOID: return sigmoidf_(o);
+        case EPI_RELU2: o = fmaxf(o, 0.f); return o * o;
+        default: return o;
+    }
+}
+
+__global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ GemmMaps maps,
+                                                        const __grid_constant__ GemmGroup g) {
     extern __shared__ __align__(1024) unsigned char gsm[];
     __shared__ uint64_t full_a[G_STAGES], full_b[G_STAGES], empty[G_STAGES], accum_bar;
     __shared__ uint32_t tmem_base_s;
-    __shared__ int s_failed;
+    __shared__ int s_failed, s_last;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    // ---- which product, which tile, which K split
+    int pi = 0;
+    while (pi + 1 < g.n_prob && (int)blockIdx.x >= g.pr[pi + 1].cta_base) ++pi;
+    const GemmProb& pb = g.pr[pi];
+    const int local = blockIdx.x - pb.cta_base;
+    const int m_tile = local / pb.ksplit, z = local - m_tile * pb.ksplit;
+    const int m0 = m_tile * G_BM;
+    const int n0 = blockIdx.y * g.n_tile;
+    const int total_ksteps = (pb.w.k + G_BK - 1) / G_BK;
+    const int ks_begin = (int)((long long)total_ksteps * z / pb.ksplit);
+    const int ks_end = (int)((long long)total_ksteps * (z + 1) / pb.ksplit);
+    const int n_ksteps = ks_end - ks_begin;
+
     unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)gsm + 1023) & ~(uintptr_t)1023);
-    const int b_bytes = p.n_tile * 128;
+    const int b_bytes = g.n_tile * 128;
     unsigned char* smA = base;                                  // G_STAGES x 16 KB
     unsigned char* smB = base + G_STAGES * G_A_BYTES;           // G_STAGES x n_tile x 128 B
-    const int n_inst_cols = p.n_tile / p.n_inst;
-    const int m0 = blockIdx.x * G_BM;
-    const int n0 = blockIdx.y * p.n_tile;
-    const int n_ksteps = (p.w.k + G_BK - 1) / G_BK;
+    unsigned char* smRaw = smB + G_STAGES * b_bytes;            // raw weight ring
+    const int n_inst_cols = g.n_tile / g.n_inst;
 
     if (tid == 0) {
         for (int s = 0; s < G_STAGES; ++s) {
@@ -180,8 +240,9 @@ __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ 
         mbar_init(&accum_bar, 1);
         fence_mbar_init();
         s_failed = 0;
+        s_last = 0;
     }
-    if (warp == 5) tmem_alloc(&tmem_base_s, (uint32_t)p.tmem_cols);
+    if (warp == 5) tmem_alloc(&tmem_base_s, (uint32_t)g.tmem_cols);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -195,49 +256,134 @@ __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ 
             atomicOr(&g_device_status, DEV_WAIT_GEMM);
         }
     };
+
     if (warp < 4) {
         // ===== weight producers: thread = weight row of the tile =====
         const int row = m0 + tid;
-        uint4 cur[8];
-        dequant_row64(p.w, row, 0, cur);
+        const int fmt = pb.w.fmt;
+        const int slot_bytes = raw_row_bytes(fmt) * G_BM + (fmt == FMT_FP4 ? G_BM * 4 : 0);
+        int depth = G_RAW_BYTES / slot_bytes;   // k-steps of raw weights in flight
+        if (depth > 8) depth = 8;
+        for (int i = 0; i < depth - 1; ++i) {
+            if (i < n_ksteps) raw_issue(pb.w, row, tid, ks_begin + i, smRaw + (i % depth) * slot_bytes);
+            cp_async_commit();
+        }
         for (int ks = 0; ks < n_ksteps; ++ks) {
             const int s = ks % G_STAGES, f = ks / G_STAGES;
-            uint4 nxt[8];
-            if (ks + 1 < n_ksteps) dequant_row64(p.w, row, (ks + 1) * G_BK, nxt);   // next k-step's loads in flight
+            const int ahead = ks + depth - 1;
+            if (ahead < n_ksteps) raw_issue(pb.w, row, tid, ks_begin + ahead, smRaw + (ahead % depth) * slot_bytes);
+            cp_async_commit();
+            // all but the newest depth-1 groups have landed: k-step ks is there
+            switch (depth) {
+                case 8: cp_async_wait<7>(); break;
+                case 7: cp_async_wait<6>(); break;
+                case 6: cp_async_wait<5>(); break;
+                case 5: cp_async_wait<4>(); break;
+                case 4: cp_async_wait<3>(); break;
+                case 3: cp_async_wait<2>(); break;
+                default: cp_async_wait<0>(); break;
+            }
+            uint4 cur[8];
+            raw_dequant(fmt, tid, smRaw + (ks % depth) * slot_bytes, cur);
             if (f > 0) wait_ok(&empty[s], (f - 1) & 1);
             unsigned char* dst = smA + s * G_A_BYTES + tid * 128;
 #pragma unroll
             for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(dst + ((c ^ (tid & 7)) << 4)) = cur[c];
             fence_proxy_async();   // generic-proxy stores -> visible to the tensor core's async proxy
             mbar_arrive(&full_a[s]);
-#pragma unroll
-            for (int c = 0; c < 8; ++c) cur[c] = nxt[c];
         }
-        // ===== epilogue: thread = output feature (TMEM lane), loop over batch columns =====
+
+        // ===== epilogue: thread = output feature (TMEM lane) =====
         wait_ok(&accum_bar, 0);
         tc_fence_after();
-        const bool row_ok = row < p.w.n_out;
+        const bool row_ok = row < pb.w.n_out;
         float scale = 1.f;
-        if (row_ok) scale = p.w.fmt == FMT_I8 ? reinterpret_cast<const float*>(p.w.scale)[row] : p.w.tscale;
-        for (int c0 = 0; c0 < p.n_tile; c0 += 16) {
-            if (n0 + c0 >= p.rows) break;   // warp-uniform
-            uint32_t v[16];
-            tc_ld16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, v);
-            if (row_ok) {
+        if (row_ok) scale = fmt == FMT_I8 ? reinterpret_cast<const float*>(pb.w.scale)[row] : pb.w.tscale;
+        const int n_out = pb.w.n_out;
+        __half* tr = reinterpret_cast<__half*>(smA);   // [2][16][128] transpose buffers; the operand stages are idle now
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+        const int n_chunks = (min(g.n_tile, g.rows - n0) + 15) / 16;
+        const bool vec_ok = (n_out % 8) == 0;
+
+        // finished values of one 16-column chunk -> fp16 rows of Y, 16-byte stores along the output features
+        auto emit_chunk = [&](int ci, const float* v) {
+            __half* t = tr + (ci & 1) * (16 * G_BM);
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const int b = n0 + c0 + i;
-                    if (b < p.rows) {
-                        float o = rh(__uint_as_float(v[i]) * scale);
-                        switch (p.epi) {
-                            case EPI_TANH: o = tanhf(o); break;
-                            case EPI_SIGMOID: o = sigmoidf_(o); break;
-                            case EPI_RELU2: o = fmaxf(o, 0.f); o = o * o; break;
-                            case EPI_RESID: o = __half2float(p.resid[(size_t)b * p.w.n_out + row]) + o; break;
-                            default: break;
+            for (int i = 0; i < 16; ++i) t[i * G_BM + tid] = __float2half_rn(apply_epi(pb.epi, rh(v[i] * scale)));
+            epi_sync();
+#pragma unroll
+            for (int rep = 0; rep < 2; ++rep) {
+                const int task = tid + rep * 128;       // 16 batch rows x 16 chunks of 8 features
+                const int bi = task >> 4, ch = task & 15;
+                const int b = n0 + ci * 16 + bi, col = m0 + ch * 8;
+                if (b < g.rows && col < n_out) {
+                    uint4 val = *reinterpret_cast<const uint4*>(t + bi * G_BM + ch * 8);
+                    __half* yp = pb.y + (size_t)b * n_out + col;
+                    if (vec_ok) {
+                        if (pb.epi == EPI_RESID) {
+                            const uint4 rv = *reinterpret_cast<const uint4*>(pb.resid + (size_t)b * n_out + col);
+                            __half2* a2 = reinterpret_cast<__half2*>(&val);
+                            const __half2* r2 = reinterpret_cast<const __half2*>(&rv);
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) a2[e] = __hadd2(r2[e], a2[e]);
                         }
-                        p.y[(size_t)b * p.w.n_out + row] = __float2half_rn(o);
+                        *reinterpret_cast<uint4*>(yp) = val;
+                    } else {
+                        const __half* hv = reinterpret_cast<const __half*>(&val);
+                        for (int e = 0; e < 8 && col + e < n_out; ++e) {
+                            __half o = hv[e];
+                            if (pb.epi == EPI_RESID) o = __hadd(pb.resid[(size_t)b * n_out + col + e], o);
+                            yp[e] = o;
+                        }
                     }
+                }
+            }
+            // the other buffer is used next; this one is rewritten two chunks later, after another epi_sync
+        };
+
+        if (pb.ksplit == 1) {
+            for (int ci = 0; ci < n_chunks; ++ci) {
+                uint32_t raw[16];
+                tc_ld16(lane_addr + (uint32_t)(ci * 16), raw);
+                float v[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(raw[i]);
+                emit_chunk(ci, v);
+            }
+        } else {
+            // split K: park this block's fp32 tile, the last block to arrive sums all of them in a fixed order
+            const int tile = pb.tile_base + m_tile * gridDim.y + blockIdx.y;
+            float* mine = g.partials + pb.part_base +
+                          ((size_t)(m_tile * gridDim.y + blockIdx.y) * pb.ksplit + z) * ((size_t)g.n_tile * G_BM);
+            for (int ci = 0; ci < n_chunks; ++ci) {
+                uint32_t raw[16];
+                tc_ld16(lane_addr + (uint32_t)(ci * 16), raw);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) __stcg(mine + (size_t)(ci * 16 + i) * G_BM + tid, __uint_as_float(raw[i]));
+            }
+            __threadfence();
+            epi_sync();
+            if (tid == 0) {
+                const unsigned old = atomicAdd(&g.counters[tile], 1u);
+                const int last = old == (unsigned)pb.ksplit - 1;
+                if (last) g.counters[tile] = 0;   // leave the counter ready for the next launch
+                s_last = last;
+                __threadfence();
+            }
+            epi_sync();
+            if (s_last) {
+                const float* tile0 = g.partials + pb.part_base +
+                                     ((size_t)(m_tile * gridDim.y + blockIdx.y) * pb.ksplit) * ((size_t)g.n_tile * G_BM);
+                for (int ci = 0; ci < n_chunks; ++ci) {
+                    float v[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) v[i] = 0.f;
+                    for (int zz = 0; zz < pb.ksplit; ++zz) {
+                        const float* src = tile0 + (size_t)zz * g.n_tile * G_BM;
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) v[i] += __ldcg(src + (size_t)(ci * 16 + i) * G_BM + tid);
+                    }
+                    emit_chunk(ci, v);
                 }
             }
         }
@@ -245,12 +391,14 @@ __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ 
     } else if (warp == 4) {
         // ===== activation tiles by TMA =====
         if (lane == 0) {
+            const CUtensorMap* map = &maps.m[pi];
             for (int ks = 0; ks < n_ksteps; ++ks) {
                 const int s = ks % G_STAGES, f = ks / G_STAGES;
                 if (f > 0) wait_ok(&empty[s], (f - 1) & 1);
                 mbar_expect_tx(&full_b[s], (uint32_t)b_bytes);
-                for (int j = 0; j < p.n_inst; ++j)
-                    tma_load_2d(smB + s * b_bytes + j * n_inst_cols * 128, &tmap_x, ks * G_BK, n0 + j * n_inst_cols, &full_b[s]);
+                for (int j = 0; j < g.n_inst; ++j)
+                    tma_load_2d(smB + s * b_bytes + j * n_inst_cols * 128, map, (ks_begin + ks) * G_BK, n0 + j * n_inst_cols,
+                                &full_b[s]);
             }
         }
     } else {
@@ -265,7 +413,7 @@ __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ 
                 const uint64_t da = umma_desc_sw128(smA + s * G_A_BYTES);
 #pragma unroll
                 for (int k4 = 0; k4 < G_BK / 16; ++k4)
-                    for (int j = 0; j < p.n_inst; ++j) {
+                    for (int j = 0; j < g.n_inst; ++j) {
                         const uint64_t db = umma_desc_sw128(smB + s * b_bytes + j * n_inst_cols * 128);
                         // advancing 16 inputs = 32 bytes inside the swizzle row: +2 in the (address >> 4) field
                         tc_mma_f16(tmem_base + (uint32_t)(j * n_inst_cols), da + (uint64_t)(2 * k4), db + (uint64_t)(2 * k4),
@@ -280,7 +428,7 @@ __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ 
     __syncthreads();
     if (warp == 5) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
+        tmem_dealloc(tmem_base, (uint32_t)g.tmem_cols);
     }
 }
 
@@ -333,52 +481,127 @@ int check_mat(const ab_mat& m, const char* what) {
     return OK;
 }
 
-size_t gemm_scratch_bytes(const ab_mat&, int) { return 256; }
+namespace {
 
-int gemm_launch(const ab_mat& m, int rows, const __half* x, __half* y, int epi, const __half* resid, void*,
-                cudaStream_t stream) {
-    int st = check_mat(m, "gemm");
-    if (st != OK) return st;
-    AB_CHECK_ARG(rows > 0 && x && y, "gemm: bad argument");
-    AB_CHECK_ARG(m.col_scale == nullptr, "gemm: per-input-column scales are a batch-1 feature");
-    AB_CHECK_ARG(m.k % 16 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)m.w & 15) == 0, "gemm: k %% 16 and 16-byte alignment needed");
-    AB_CHECK_ARG(m.fmt != FMT_FP4 || (m.k % 64 == 0 && ((uintptr_t)m.scale & 3) == 0), "gemm: NVFP4 needs k %% 64 == 0");
+struct GroupShape {
+    int n_tile, n_inst, tmem_cols, n_tiles_y;
+    int ksplit[G_MAX_OPS];
+    int grid_x;
+    long long part_floats;
+    int n_split_tiles;
+};
 
-    GemmParams p = {};
-    p.w = m; p.resid = resid; p.y = y; p.rows = rows; p.epi = epi;
-    if (rows <= 256) { p.n_tile = (rows + 15) & ~15; p.n_inst = 1; }
-    else if (rows <= 320) { p.n_tile = (rows + 31) & ~31; p.n_inst = 2; }
-    else { p.n_tile = 256; p.n_inst = 1; }
-    p.tmem_cols = 32;
-    while (p.tmem_cols < p.n_tile) p.tmem_cols *= 2;
-    const int n_inst_cols = p.n_tile / p.n_inst;
-
-    EncodeTiledFn encode;
-    st = get_encode_fn(&encode);
-    if (st != OK) return st;
-    CUtensorMap tmap;
-    const cuuint64_t gdim[2] = {(cuuint64_t)m.k, (cuuint64_t)rows};
-    const cuuint64_t gstride[1] = {(cuuint64_t)m.k * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)G_BK, (cuuint32_t)n_inst_cols};
-    const cuuint32_t estr[2] = {1, 1};
-    const CUresult cr = encode(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(x), gdim, gstride, box, estr,
-                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (cr != CUDA_SUCCESS) {
-        set_error("gemm: cuTensorMapEncodeTiled failed with %d (rows=%d k=%d)", (int)cr, rows, m.k);
-        return ERR_CUDA;
+GroupShape group_shape(const GemmOp* ops, int n, int rows) {
+    GroupShape gs = {};
+    if (rows <= 256) { gs.n_tile = (rows + 15) & ~15; gs.n_inst = 1; }
+    else if (rows <= 320) { gs.n_tile = (rows + 31) & ~31; gs.n_inst = 2; }
+    else { gs.n_tile = 256; gs.n_inst = 1; }
+    gs.tmem_cols = 32;
+    while (gs.tmem_cols < gs.n_tile) gs.tmem_cols *= 2;
+    gs.n_tiles_y = (rows + gs.n_tile - 1) / gs.n_tile;
+    int base_ctas = 0;
+    for (int i = 0; i < n; ++i) base_ctas += (ops[i].w.n_out + G_BM - 1) / G_BM * gs.n_tiles_y;
+    for (int i = 0; i < n; ++i) {
+        const int ksteps = (ops[i].w.k + G_BK - 1) / G_BK;
+        int ks = 1;
+        if (base_ctas < 100 && ksteps >= 32) {   // too few tiles to fill the GPU: split the long K loops
+            ks = 148 / base_ctas;
+            if (ks > 8) ks = 8;
+            if (ks > ksteps / 8) ks = ksteps / 8;
+            if (ks < 1) ks = 1;
+        }
+        gs.ksplit[i] = ks;
+        const int m_tiles = (ops[i].w.n_out + G_BM - 1) / G_BM;
+        gs.grid_x += m_tiles * ks;
+        if (ks > 1) {
+            gs.part_floats += (long long)m_tiles * gs.n_tiles_y * ks * gs.n_tile * G_BM;
+            gs.n_split_tiles += m_tiles * gs.n_tiles_y;
+        }
     }
+    return gs;
+}
 
-    const size_t smem = 1024 + (size_t)G_STAGES * (G_A_BYTES + (size_t)p.n_tile * 128);
+}  // namespace
+
+size_t gemm_group_scratch_bytes(const GemmOp* ops, int n, int rows) {
+    const GroupShape gs = group_shape(ops, n, rows);
+    return (size_t)G_COUNTERS * 4 + (size_t)gs.part_floats * 4 + 256;
+}
+size_t gemm_scratch_bytes(const ab_mat& m, int rows) {
+    GemmOp op = {};
+    op.w = m;
+    return gemm_group_scratch_bytes(&op, 1, rows);
+}
+
+int gemm_group_launch(const GemmOp* ops, int n, int rows, void* scratch, cudaStream_t stream) {
+    AB_CHECK_ARG(ops && n >= 1 && n <= G_MAX_OPS && rows > 0, "gemm: bad group (n=%d rows=%d)", n, rows);
+    const GroupShape gs = group_shape(ops, n, rows);
+    AB_CHECK_ARG(gs.n_split_tiles <= G_COUNTERS, "gemm: too many split-K tiles");
+    AB_CHECK_ARG(gs.part_floats == 0 || (scratch && ((uintptr_t)scratch & 15) == 0), "gemm: split-K needs a 16-byte aligned scratch area");
+    EncodeTiledFn encode;
+    int st = get_encode_fn(&encode);
+    if (st != OK) return st;
+
+    GemmGroup g = {};
+    GemmMaps maps;
+    g.n_prob = n; g.rows = rows; g.n_tile = gs.n_tile; g.n_inst = gs.n_inst; g.tmem_cols = gs.tmem_cols;
+    g.counters = reinterpret_cast<unsigned*>(scratch);
+    g.partials = scratch ? reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(scratch) + (size_t)G_COUNTERS * 4) : nullptr;
+    const int n_inst_cols = gs.n_tile / gs.n_inst;
+    int cta = 0, tile = 0;
+    long long part = 0;
+    size_t raw_slot_max = 0;
+    for (int i = 0; i < n; ++i) {
+        const GemmOp& op = ops[i];
+        const ab_mat& m = op.w;
+        st = check_mat(m, "gemm");
+        if (st != OK) return st;
+        AB_CHECK_ARG(op.x && op.y, "gemm: null activation pointer");
+        AB_CHECK_ARG(op.epi >= EPI_NONE && op.epi <= EPI_RESID && (op.epi != EPI_RESID || op.resid), "gemm: bad epilogue");
+        AB_CHECK_ARG(m.col_scale == nullptr, "gemm: per-input-column scales are a batch-1 feature");
+        AB_CHECK_ARG(m.k % 16 == 0 && ((uintptr_t)op.x & 15) == 0 && ((uintptr_t)m.w & 15) == 0, "gemm: k %% 16 and 16-byte alignment needed");
+        AB_CHECK_ARG(m.fmt != FMT_FP4 || (m.k % 64 == 0 && ((uintptr_t)m.scale & 3) == 0), "gemm: NVFP4 needs k %% 64 == 0");
+        GemmProb& pb = g.pr[i];
+        pb.w = m; pb.resid = op.resid; pb.y = op.y; pb.epi = op.epi;
+        pb.cta_base = cta; pb.ksplit = gs.ksplit[i]; pb.tile_base = tile; pb.part_base = part;
+        const int m_tiles = (m.n_out + G_BM - 1) / G_BM;
+        cta += m_tiles * pb.ksplit;
+        if (pb.ksplit > 1) {
+            tile += m_tiles * gs.n_tiles_y;
+            part += (long long)m_tiles * gs.n_tiles_y * pb.ksplit * gs.n_tile * G_BM;
+        }
+        const cuuint64_t gdim[2] = {(cuuint64_t)m.k, (cuuint64_t)rows};
+        const cuuint64_t gstride[1] = {(cuuint64_t)m.k * 2};
+        const cuuint32_t box[2] = {(cuuint32_t)G_BK, (cuuint32_t)n_inst_cols};
+        const cuuint32_t estr[2] = {1, 1};
+        const CUresult cr = encode(&maps.m[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(op.x), gdim, gstride, box,
+                                   estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (cr != CUDA_SUCCESS) {
+            set_error("gemm: cuTensorMapEncodeTiled failed with %d (rows=%d k=%d)", (int)cr, rows, m.k);
+            return ERR_CUDA;
+        }
+        (void)raw_slot_max;
+    }
+    for (int i = n; i < G_MAX_OPS; ++i) maps.m[i] = maps.m[0];
+
+    const size_t smem = 1024 + (size_t)G_STAGES * (G_A_BYTES + (size_t)gs.n_tile * 128) + G_RAW_BYTES;
     static size_t smem_set = 0;
     if (smem > smem_set) {
         AB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         smem_set = smem;
     }
-    const dim3 grid((m.n_out + G_BM - 1) / G_BM, (rows + p.n_tile - 1) / p.n_tile);
-    gemm_tc_kernel<<<grid, GT, smem, stream>>>(tmap, p);
+    const dim3 grid(gs.grid_x, gs.n_tiles_y);
+    gemm_tc_kernel<<<grid, GT, smem, stream>>>(maps, g);
     AB_CUDA(cudaGetLastError());
     return OK;
+}
+
+int gemm_launch(const ab_mat& m, int rows, const __half* x, __half* y, int epi, const __half* resid, void* scratch,
+                cudaStream_t stream) {
+    GemmOp op = {};
+    op.w = m; op.x = x; op.y = y; op.epi = epi; op.resid = resid;
+    return gemm_group_launch(&op, 1, rows, scratch, stream);
 }
 
 int dequant_launch(const ab_mat& m, float* out, cudaStream_t stream) {

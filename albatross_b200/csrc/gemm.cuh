@@ -5,6 +5,18 @@
 
 namespace ab {
 
+// One product of a grouped launch: Y[rows, n_out] = epilogue(X[rows, k] * W^T).
+struct GemmOp {
+    ab_mat w;
+    const __half* x;
+    __half* y;
+    const __half* resid;
+    int epi;
+};
+// Scratch: split-K arrival counters and fp32 partial tiles. It must be zero when first used; the kernels
+// leave the counters at zero again.
+size_t gemm_group_scratch_bytes(const GemmOp* ops, int n, int rows);
+int gemm_group_launch(const GemmOp* ops, int n, int rows, void* scratch, cudaStream_t stream);
 size_t gemm_scratch_bytes(const ab_mat& m, int rows);
 int gemm_launch(const ab_mat& m, int rows, const __half* x, __half* y, int epi, const __half* resid, void* scratch,
                 cudaStream_t stream);

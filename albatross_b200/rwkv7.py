@@ -208,7 +208,7 @@ class RWKV_x070:
         ws = self._ws.get(key)
         if ws is None:
             n = _lib.lib.ab_workspace_bytes(self._handle, B, T)
-            ws = torch.empty(n + 256, dtype=torch.uint8, device=self.device)
+            ws = torch.zeros(n + 256, dtype=torch.uint8, device=self.device)   # split-K counters start at zero
             self._ws = {k: v for k, v in self._ws.items() if k == (1, 1)}  # keep the decode workspace only
             self._ws[key] = ws
         return ws

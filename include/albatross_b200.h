@@ -90,7 +90,8 @@ int ab_gemv(const ab_mat* m, const void* x, void* y, void* stream);
  * Replace the `[B,T,D] @ W` call sites of the batch path (reference/rwkv7.py:283,285,286,300,322,323,220).
  * x fp16 [rows, k] row-major, y fp16 [rows, n_out]; epi is one of AB_EPI_*; resid (fp16 [rows,n_out])
  * is added when epi == AB_EPI_RESID and may alias y. `scratch` holds at least
- * ab_gemm_scratch_bytes(m, rows) bytes. */
+ * ab_gemm_scratch_bytes(m, rows) bytes (split-K arrival counters and fp32 partial tiles); it must be zero the
+ * first time it is used and is left with zeroed counters. Calls that share a scratch area must not overlap. */
 #define AB_EPI_NONE 0
 #define AB_EPI_TANH 1
 #define AB_EPI_SIGMOID 2

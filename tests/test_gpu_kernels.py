@@ -134,7 +134,7 @@ def _gemm(pm, x, epi=0, resid=None):
     rows = x.shape[0]
     y = torch.empty(rows, pm.n_out, dtype=torch.float16, device="cuda")
     mat = pm.as_mat()
-    scratch = torch.empty(max(256, _lib.lib.ab_gemm_scratch_bytes(C.byref(mat), rows)), dtype=torch.uint8, device="cuda")
+    scratch = torch.zeros(max(256, _lib.lib.ab_gemm_scratch_bytes(C.byref(mat), rows)), dtype=torch.uint8, device="cuda")
     _lib.check(_lib.lib.ab_gemm(C.byref(mat), rows, x.data_ptr(), y.data_ptr(), epi,
                                 None if resid is None else resid.data_ptr(), scratch.data_ptr(), _stream()), "ab_gemm")
     torch.cuda.synchronize()
@@ -144,7 +144,7 @@ def _gemm(pm, x, epi=0, resid=None):
 
 @pytest.mark.parametrize("fmt", ["int8", "nvfp4", "none"])
 @pytest.mark.parametrize("rows,n,k", [(1, 128, 64), (3, 200, 256), (17, 128, 768), (64, 1000, 1024), (320, 512, 4096),
-                                      (300, 130, 3072), (400, 256, 512)])
+                                      (300, 130, 3072), (400, 256, 512), (320, 256, 16384)])
 def test_batched_product_against_oracle(fmt, rows, n, k):
     """Tensor-core path: ragged batch (not a multiple of 16), ragged output rows (not a multiple of 128),
     batch 320 (two MMAs of N = 160) and more than one batch tile (400 rows)."""
