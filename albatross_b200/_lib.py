@@ -67,6 +67,7 @@ def _load():
     lib.ab_workspace_bytes.restype = sz
     lib.ab_forward.argtypes = [vp, i32, i32, vp, C.POINTER(vp), vp, vp, i32, vp]
     lib.ab_model_set_option.argtypes = [vp, C.c_char_p, i32]
+    lib.ab_forward_stage.argtypes = [vp, i32, i32, vp, vp, vp, C.POINTER(vp), vp, vp, vp, vp]
     lib.ab_decode_program_bytes.argtypes = [vp]
     lib.ab_decode_program_bytes.restype = sz
     lib.ab_decode_timeline_offset.argtypes = [vp]
@@ -79,7 +80,7 @@ def _load():
 lib = _load()
 
 EXPORTS = ["ab_last_error", "ab_version", "ab_device_status", "ab_wkv7_fwd", "ab_gemv", "ab_gemm_scratch_bytes",
-           "ab_gemm", "ab_dequant", "ab_model_create", "ab_model_destroy", "ab_workspace_bytes", "ab_forward",
+           "ab_gemm", "ab_dequant", "ab_model_create", "ab_model_destroy", "ab_workspace_bytes", "ab_forward", "ab_forward_stage",
            "ab_model_set_option", "ab_decode_program_bytes", "ab_decode_timeline_offset", "ab_decode_program_build", "ab_decode_run"]
 
 

@@ -55,6 +55,7 @@ struct ab_model {
     std::vector<ab_layer> layers;
     int use_pdl = 1;
     int n_sm = 0;          // blocks of the persistent decode kernel
+    int layer_offset = 0;  // pipeline stage: index of this model's first block in the whole network
     int prog_xq_bytes = 0;
     int debug_sync = 0;  // synchronise after every launch and name the one that failed
     int timeline = 0;    // persistent decode kernel records per-phase timestamps
@@ -88,13 +89,13 @@ Workspace carve(const ab_model* m, int B, int T, unsigned char* base) {
     w.r = take(M * D); w.k = take(M * D); w.v = take(M * D); w.vfirst = take(M * D); w.att = take(M * D);
     w.kf = take(M * F);
     w.hw = take(M * rmax[0]); w.ha = take(M * rmax[1]); w.hv = take(M * rmax[2]); w.hg = take(M * rmax[3]);
-    const bool batched = !(B == 1 && T == 1);
+    const bool batched = !(B == 1 && T == 1) || !m->d.emb || !m->d.head.w || m->layer_offset > 0;
     for (int j = 0; j < 6; ++j) w.mix[j] = batched ? take(M * D) : nullptr;
     w.w_raw = take(M * D); w.a_raw = take(M * D); w.vg_raw = take(M * D); w.g = take(M * D);
     w.xlast = batched ? take((size_t)B * D) : nullptr;
     w.gemm_scratch = base + off;
     if (batched) {
-        size_t need = gemm_scratch_bytes(m->d.head, (int)M);
+        size_t need = m->d.head.w ? gemm_scratch_bytes(m->d.head, (int)M) : 256;
         for (const ab_layer& l : m->layers) {   // the products launched alone may be split along K
             need = std::max(need, gemm_scratch_bytes(l.output, (int)M));
             need = std::max(need, gemm_scratch_bytes(l.ffn_key, (int)M));
@@ -346,11 +347,24 @@ int time_mix_up_ops(const ab_layer& L, int layer, const Workspace& ws, GemmOp* o
     return n;
 }
 
-int forward_rows(ab_model* m, int B, int T, const int32_t* tokens, void* const* state, const Workspace& ws,
-                 __half* logits, int full_output, cudaStream_t st) {
+// Pipeline-stage view of a forward pass: where the hidden state comes from and where it goes.
+struct StageIO {
+    const __half* x_in;   // [M, D] hidden state from the previous stage (null: gather the embedding rows)
+    __half* v_first;      // [M, D] layer-0 value, produced by the first stage and read by every later block
+    __half* x_out;        // [M, D] hidden state for the next stage (null: final norm + vocabulary head)
+};
+
+int forward_rows(ab_model* m, int B, int T, const int32_t* tokens, void* const* state, const Workspace& ws_in,
+                 __half* logits, int full_output, cudaStream_t st, const StageIO* io = nullptr) {
     const int D = m->d.n_embd, H = D / HEAD, M = B * T;
-    AB_TRY(gather_rows((const __half*)m->d.emb, tokens, M, D, ws.x, st));
-    for (int i = 0; i < m->d.n_layer; ++i) {
+    Workspace ws = ws_in;
+    if (io && io->v_first) ws.vfirst = io->v_first;
+    if (io && io->x_in) AB_CUDA(cudaMemcpyAsync(ws.x, io->x_in, (size_t)M * D * 2, cudaMemcpyDeviceToDevice, st));
+    else AB_TRY(gather_rows((const __half*)m->d.emb, tokens, M, D, ws.x, st));
+    const int g0 = m->layer_offset;   // index of this model's first block in the whole network
+    for (int li = 0; li < m->d.n_layer; ++li) {
+        const int i = li;
+        const int gi = g0 + li;
         const ab_layer& L = m->layers[i];
         AB_TRY(ln_rows(ws.x, (const __half*)L.ln1_w, (const __half*)L.ln1_b, M, D, 1, 0, ws.xn, st));
         MixParams mp = {};
@@ -361,16 +375,16 @@ int forward_rows(ab_model* m, int B, int T, const int32_t* tokens, void* const* 
         void* sc = ws.gemm_scratch;
         {   // r, k, v and the adapter down-projections: one grouped launch
             GemmOp ops[8];
-            const int n = time_mix_down_ops(L, i, ws, ops);
+            const int n = time_mix_down_ops(L, gi, ws, ops);
             AB_TRY(gemm_group_launch(ops, n, M, sc, st));
         }
         {   // adapter up-projections
             GemmOp ops[8];
-            const int n = time_mix_up_ops(L, i, ws, ops);
+            const int n = time_mix_up_ops(L, gi, ws, ops);
             AB_TRY(gemm_group_launch(ops, n, M, sc, st));
         }
         HeadParams h = {};
-        h.B = B; h.T = T; h.D = D; h.H = H; h.layer0 = (i == 0);
+        h.B = B; h.T = T; h.D = D; h.H = H; h.layer0 = (gi == 0);
         h.state = (float*)state[3 * i + 1]; h.r = ws.r; h.k = ws.k; h.v = ws.v; h.v_first = ws.vfirst;
         h.w_raw = ws.w_raw; h.a_raw = ws.a_raw; h.vg_raw = ws.vg_raw; h.g = ws.g;
         h.w0 = (const __half*)L.w0; h.a0 = (const __half*)L.a0; h.v0 = (const __half*)L.v0;
@@ -387,6 +401,10 @@ int forward_rows(ab_model* m, int B, int T, const int32_t* tokens, void* const* 
         AB_TRY(mix_rows(fp, st));
         AB_TRY(gemm_launch(L.ffn_key, M, ws.mix[0], ws.kf, EPI_RELU2, nullptr, sc, st));
         AB_TRY(gemm_launch(L.ffn_value, M, ws.kf, ws.x, EPI_RESID, ws.x, sc, st));
+    }
+    if (io && io->x_out) {
+        AB_CUDA(cudaMemcpyAsync(io->x_out, ws.x, (size_t)M * D * 2, cudaMemcpyDeviceToDevice, st));
+        return OK;
     }
     if (full_output || T == 1) {
         AB_TRY(ln_rows(ws.x, (const __half*)m->d.lnout_w, (const __half*)m->d.lnout_b, M, D, 1, 0, ws.xn, st));
@@ -445,15 +463,15 @@ int ab_model_create(const ab_model_desc* desc, ab_model** out) {
     AB_CHECK_ARG(desc && out && desc->layers, "ab_model_create: null pointer");
     AB_CHECK_ARG(desc->n_layer > 0 && desc->n_embd > 0 && desc->n_embd % 64 == 0 && desc->vocab > 0,
                  "ab_model_create: bad shape (n_layer=%d n_embd=%d vocab=%d)", desc->n_layer, desc->n_embd, desc->vocab);
-    AB_CHECK_ARG(desc->emb && desc->lnout_w && desc->lnout_b, "ab_model_create: null top-level tensor");
-    AB_TRY(check_mat(desc->head, "head.weight"));
+    // a pipeline stage may lack the embedding table (not the first stage) or the final norm + head (not the last)
+    if (desc->head.w) AB_TRY(check_mat(desc->head, "head.weight"));
     for (int i = 0; i < desc->n_layer; ++i) {
         const ab_layer& l = desc->layers[i];
         const ab_mat* big[6] = {&l.receptance, &l.key, &l.value, &l.output, &l.ffn_key, &l.ffn_value};
         for (const ab_mat* mm : big) AB_TRY(check_mat(*mm, "block matrix"));
         AB_TRY(check_mat(l.w1t, "w1")); AB_TRY(check_mat(l.a1t, "a1")); AB_TRY(check_mat(l.g1t, "g1"));
-        if (i > 0) AB_TRY(check_mat(l.v1t, "v1"));
-        AB_CHECK_ARG(l.w2 && l.a2 && l.g2 && (i == 0 || l.v2), "ab_model_create: layer %d adapter up-projection missing", i);
+        if (l.v1t.w) AB_TRY(check_mat(l.v1t, "v1"));
+        AB_CHECK_ARG(l.w2 && l.a2 && l.g2, "ab_model_create: layer %d adapter up-projection missing", i);
         AB_CHECK_ARG(l.ln1_w && l.ln1_b && l.ln2_w && l.ln2_b && l.x_r && l.x_w && l.x_k && l.x_v && l.x_a && l.x_g &&
                          l.w0 && l.a0 && l.k_k && l.k_a && l.r_k && l.lnx_w && l.lnx_b && l.ffn_x_k,
                      "ab_model_create: layer %d has a null vector", i);
@@ -511,6 +529,7 @@ int ab_model_set_option(ab_model* m, const char* name, int value) {
     else if (!strcmp(name, "pdl")) m->use_pdl = value != 0;
     else if (!strcmp(name, "debug_sync")) m->debug_sync = value != 0;
     else if (!strcmp(name, "timeline")) m->timeline = value != 0;
+    else if (!strcmp(name, "layer_offset")) { AB_CHECK_ARG(value >= 0, "layer_offset must be >= 0"); m->layer_offset = value; }
     else { set_error("unknown option %s", name); return ERR_BAD_ARG; }
     return OK;
 }
@@ -521,9 +540,27 @@ int ab_forward(ab_model* m, int B, int T, const int32_t* tokens, void* const* st
     AB_CHECK_ARG(B > 0 && T > 0, "ab_forward: bad batch shape B=%d T=%d", B, T);
     AB_CHECK_ARG(((uintptr_t)workspace & 255) == 0, "ab_forward: workspace must be 256-byte aligned");
     for (int i = 0; i < 3 * m->d.n_layer; ++i) AB_CHECK_ARG(state[i], "ab_forward: state[%d] is null", i);
+    AB_CHECK_ARG(m->d.emb && m->d.head.w && m->d.lnout_w && m->layer_offset == 0,
+                 "ab_forward: this model is a pipeline stage; use ab_forward_stage");
     const Workspace ws = carve(m, B, T, (unsigned char*)workspace);
     if (B == 1 && T == 1) return forward_one(m, tokens, state, ws, (__half*)logits, (cudaStream_t)stream);
     return forward_rows(m, B, T, tokens, state, ws, (__half*)logits, full_output, (cudaStream_t)stream);
+}
+
+int ab_forward_stage(ab_model* m, int B, int T, const int32_t* tokens, const void* x_in, void* v_first, void* const* state,
+                     void* workspace, void* x_out, void* logits, void* stream) {
+    AB_CHECK_ARG(m && state && workspace && v_first, "ab_forward_stage: null pointer");
+    AB_CHECK_ARG(B > 0 && T > 0, "ab_forward_stage: bad batch shape B=%d T=%d", B, T);
+    AB_CHECK_ARG(((uintptr_t)workspace & 255) == 0, "ab_forward_stage: workspace must be 256-byte aligned");
+    AB_CHECK_ARG((x_in != nullptr) != (tokens != nullptr), "ab_forward_stage: give token ids (first stage) or x_in (later stages)");
+    AB_CHECK_ARG(!tokens || (m->d.emb && m->layer_offset == 0), "ab_forward_stage: token ids need the embedding table and layer_offset 0");
+    AB_CHECK_ARG((x_out != nullptr) != (logits != nullptr), "ab_forward_stage: give x_out (not the last stage) or logits (last stage)");
+    AB_CHECK_ARG(!logits || (m->d.head.w && m->d.lnout_w && m->d.lnout_b), "ab_forward_stage: logits need the final norm and head");
+    for (int i = 0; i < 3 * m->d.n_layer; ++i) AB_CHECK_ARG(state[i], "ab_forward_stage: state[%d] is null", i);
+    const Workspace ws = carve(m, B, T, (unsigned char*)workspace);
+    StageIO io = {(const __half*)x_in, (__half*)v_first, (__half*)x_out};
+    // stages always take the row-wise (batched) program, also at B = T = 1
+    return forward_rows(m, B, T, tokens, state, ws, (__half*)logits, 0, (cudaStream_t)stream, &io);
 }
 
 }  // extern "C"

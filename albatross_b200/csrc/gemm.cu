@@ -223,6 +223,10 @@ __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ 
     const int ks_begin = (int)((long long)total_ksteps * z / pb.ksplit);
     const int ks_end = (int)((long long)total_ksteps * (z + 1) / pb.ksplit);
     const int n_ksteps = ks_end - ks_begin;
+    // Blocks walk K in rotated order: at any moment they read different columns of the (shared) activation
+    // matrix, instead of all hitting the same few L2 lines.
+    const int rot = (int)((blockIdx.x * 7u + blockIdx.y * 3u) % (unsigned)n_ksteps);
+    auto kstep_of = [&](int i) { int k = i + rot; if (k >= n_ksteps) k -= n_ksteps; return ks_begin + k; };
 
     unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)gsm + 1023) & ~(uintptr_t)1023);
     const int b_bytes = g.n_tile * 128;
@@ -265,13 +269,13 @@ __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ 
         int depth = G_RAW_BYTES / slot_bytes;   // k-steps of raw weights in flight
         if (depth > 8) depth = 8;
         for (int i = 0; i < depth - 1; ++i) {
-            if (i < n_ksteps) raw_issue(pb.w, row, tid, ks_begin + i, smRaw + (i % depth) * slot_bytes);
+            if (i < n_ksteps) raw_issue(pb.w, row, tid, kstep_of(i), smRaw + (i % depth) * slot_bytes);
             cp_async_commit();
         }
         for (int ks = 0; ks < n_ksteps; ++ks) {
             const int s = ks % G_STAGES, f = ks / G_STAGES;
             const int ahead = ks + depth - 1;
-            if (ahead < n_ksteps) raw_issue(pb.w, row, tid, ks_begin + ahead, smRaw + (ahead % depth) * slot_bytes);
+            if (ahead < n_ksteps) raw_issue(pb.w, row, tid, kstep_of(ahead), smRaw + (ahead % depth) * slot_bytes);
             cp_async_commit();
             // all but the newest depth-1 groups have landed: k-step ks is there
             switch (depth) {
@@ -397,7 +401,7 @@ __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ 
                 if (f > 0) wait_ok(&empty[s], (f - 1) & 1);
                 mbar_expect_tx(&full_b[s], (uint32_t)b_bytes);
                 for (int j = 0; j < g.n_inst; ++j)
-                    tma_load_2d(smB + s * b_bytes + j * n_inst_cols * 128, map, (ks_begin + ks) * G_BK, n0 + j * n_inst_cols,
+                    tma_load_2d(smB + s * b_bytes + j * n_inst_cols * 128, map, kstep_of(ks) * G_BK, n0 + j * n_inst_cols,
                                 &full_b[s]);
             }
         }

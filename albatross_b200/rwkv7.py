@@ -70,12 +70,19 @@ def RWKV7_BATCH_OP(state, r, w, k, v, a, b):
 # --------------------------------------------------------------------------------------------
 class RWKV_x070:
     def __init__(self, args, quant: Optional[str] = "int8", state_dict: Optional[Iterable[Tuple[str, torch.Tensor]]] = None,
-                 device: str = "cuda", use_graph: bool = True, decode_mode: Optional[str] = None):
+                 device: str = "cuda", use_graph: bool = True, decode_mode: Optional[str] = None,
+                 layer_range: Optional[Tuple[int, int]] = None):
         if not torch.cuda.is_available():
             raise RuntimeError("albatross_b200 needs a CUDA device (sm_100a); there is no CPU path")
         self.args = args
         self.n_embd = args.n_embd
-        self.n_layer = args.n_layer
+        # layer_range = (first, last+1): hold only these blocks (one stage of a layer pipeline); the embedding
+        # table is kept by the stage with block 0, the final norm and head by the stage with the last block
+        self.layer_range = tuple(layer_range) if layer_range is not None else (0, args.n_layer)
+        self.total_layers = args.n_layer
+        self.n_layer = self.layer_range[1] - self.layer_range[0]
+        self.is_first = self.layer_range[0] == 0
+        self.is_last = self.layer_range[1] == args.n_layer
         self.quant = quant
         self.device = torch.device(device)
         self.use_graph = use_graph and os.environ.get("ALBATROSS_NO_GRAPH", "0") != "1"
@@ -91,18 +98,34 @@ class RWKV_x070:
             items = items.items()
         self.z: Dict[str, object] = {}
         self._extra: Dict[str, object] = {}
+        lo, hi = self.layer_range
         for name, t in items:
+            if name.startswith("blocks."):
+                li = int(name.split(".")[1])
+                if "ln0" in name:
+                    if not self.is_first:
+                        continue
+                elif not (lo <= li < hi):
+                    continue
+                else:
+                    name = "blocks.%d.%s" % (li - lo, name.split(".", 2)[2])   # local block index
+            elif name.startswith("emb."):
+                if not self.is_first:
+                    continue
+            elif not self.is_last:      # ln_out.*, head.weight
+                continue
             self._ingest(name, t)
         z = self.z
         self.n_head, self.head_size = self._r_k_shape
         assert HEAD_SIZE == self.head_size
         assert self.head_size == args.head_size
         # ln0 is folded into the embedding table once (reference/rwkv7.py:93)
-        z["emb.weight"] = F.layer_norm(z["emb.weight"], (args.n_embd,), weight=z["blocks.0.ln0.weight"],
-                                       bias=z["blocks.0.ln0.bias"]).contiguous()
-        for s in ("0", "1", "2"):  # layer 0 never uses its v adapter (reference/rwkv7.py:94-96, :239)
-            z["blocks.0.att.v" + s] = z["blocks.0.att.a" + s]
-        self.vocab = z["emb.weight"].shape[0]
+        if self.is_first:
+            z["emb.weight"] = F.layer_norm(z["emb.weight"], (args.n_embd,), weight=z["blocks.0.ln0.weight"],
+                                           bias=z["blocks.0.ln0.bias"]).contiguous()
+            for s in ("0", "1", "2"):  # layer 0 never uses its v adapter (reference/rwkv7.py:94-96, :239)
+                z["blocks.0.att.v" + s] = z["blocks.0.att.a" + s]
+        self.vocab = z["emb.weight"].shape[0] if self.is_first else (z["head.weight"].n_out if self.is_last else args.vocab_size)
         self._build_native()
         self._ws: Dict[Tuple[int, int], torch.Tensor] = {}
         self._graphs: Dict[tuple, tuple] = {}
@@ -152,7 +175,7 @@ class RWKV_x070:
             ly.value, ly.output = z[a + "value.weight"].as_mat(), z[a + "output.weight"].as_mat()
             ly.ffn_key, ly.ffn_value = z[f + "key.weight"].as_mat(), z[f + "value.weight"].as_mat()
             for n in ("w", "a", "v", "g"):
-                if n == "v" and i == 0:
+                if n == "v" and i == 0 and self.is_first:
                     setattr(ly, "v1t", empty)
                     setattr(ly, "v2t", empty)
                     ly.v2 = None
@@ -162,13 +185,18 @@ class RWKV_x070:
                 setattr(ly, n + "2", ptr(a + n + "2"))
         d = _lib.ModelDesc()
         d.n_layer, d.n_embd, d.vocab = L, self.n_embd, self.vocab
-        d.emb, d.lnout_w, d.lnout_b = z["emb.weight"].data_ptr(), z["ln_out.weight"].data_ptr(), z["ln_out.bias"].data_ptr()
-        d.head = z["head.weight"].as_mat()
+        if self.is_first:
+            d.emb = z["emb.weight"].data_ptr()
+        if self.is_last:
+            d.lnout_w, d.lnout_b = z["ln_out.weight"].data_ptr(), z["ln_out.bias"].data_ptr()
+            d.head = z["head.weight"].as_mat()
         d.layers = C.cast(self._layers, C.POINTER(_lib.Layer))
         self._desc = d
         h = C.c_void_p()
         _lib.check(_lib.lib.ab_model_create(C.byref(d), C.byref(h)), "ab_model_create")
         self._handle = h
+        if self.layer_range[0] > 0:
+            _lib.check(_lib.lib.ab_model_set_option(h, b"layer_offset", self.layer_range[0]), "ab_model_set_option")
 
     def __del__(self):
         h = getattr(self, "_handle", None)
@@ -343,6 +371,25 @@ class RWKV_x070:
         logits = torch.empty(shape, dtype=DTYPE, device=self.device)
         self._run(B, T, tok, state, logits, full_output)
         return logits, list(state)
+
+    @torch.no_grad()
+    def forward_stage(self, state: List[torch.Tensor], v_first: torch.Tensor, tokens: Optional[torch.Tensor] = None,
+                      x_in: Optional[torch.Tensor] = None, x_out: Optional[torch.Tensor] = None):
+        """One pipeline stage of a batched decode step (T = 1). The first stage takes `tokens` (int32 [B] on
+        the device), later stages `x_in` (fp16 [B, D]); `v_first` (fp16 [B, D]) is written by the first stage
+        and read by the others; every stage but the last fills `x_out`, the last returns logits [B, V]."""
+        B = v_first.shape[0]
+        self._check_state(state, B)
+        ws = self._workspace(B, 1)
+        ptrs = (C.c_void_p * len(state))(*[t.data_ptr() for t in state])
+        logits = None
+        if self.is_last:
+            logits = torch.empty(B, self.vocab, dtype=DTYPE, device=self.device)
+        _lib.check(_lib.lib.ab_forward_stage(
+            self._handle, B, 1, None if tokens is None else tokens.data_ptr(), None if x_in is None else x_in.data_ptr(),
+            v_first.data_ptr(), ptrs, (ws.data_ptr() + 255) & ~255, None if x_out is None else x_out.data_ptr(),
+            None if logits is None else logits.data_ptr(), torch.cuda.current_stream().cuda_stream), "ab_forward_stage")
+        return logits
 
     # ---- bookkeeping for benchmarks ---------------------------------------------------------
     def weight_bytes(self, include_emb: bool = False) -> int:

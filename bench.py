@@ -35,6 +35,8 @@ WORKLOADS = {
     "decode_bsz320_nvfp4": dict(batch=320, quant="nvfp4"),
     "gemv_int8": dict(batch=1, quant="int8"),
     "gemv_nvfp4": dict(batch=1, quant="nvfp4"),
+    "gemm_int8": dict(batch=320, quant="int8"),
+    "gemm_nvfp4": dict(batch=320, quant="nvfp4"),
 }
 METRIC = "rwkv7_decode_tokens_per_s"
 
@@ -271,6 +273,51 @@ def run_gemv(a, dev):
             "clocks": clocks, "device_status": _lib.device_status()}
 
 
+def run_gemm(a, dev):
+    """Times ab_gemm alone (tensor-core path). Each launch uses a different weight matrix."""
+    import ctypes as C
+    from albatross_b200 import _lib, quant
+    torch.cuda.set_device(dev)
+    fmt = "nvfp4" if "nvfp4" in a.workload else "int8"
+    n, k, rows = a.n_out, a.k, (a.batch or 320)
+    per = n * k * (1.0 if fmt == "int8" else 0.5625)
+    n_mats = max(2, int(300e6 // per) + 1)
+    torch.manual_seed(0)
+    mats = [quant.quantize((torch.randn(n, k, device=f"cuda:{dev}") * 0.02).half(), fmt) for _ in range(n_mats)]
+    cm = [m.as_mat() for m in mats]
+    x = torch.randn(rows, k, device=f"cuda:{dev}").half()
+    y = torch.empty(rows, n, dtype=torch.float16, device=f"cuda:{dev}")
+    scratch = torch.zeros(_lib.lib.ab_gemm_scratch_bytes(C.byref(cm[0]), rows) + 256, dtype=torch.uint8, device=f"cuda:{dev}")
+    st = torch.cuda.current_stream().cuda_stream
+    call = lambda i: _lib.check(_lib.lib.ab_gemm(C.byref(cm[i % n_mats]), rows, x.data_ptr(), y.data_ptr(), 0, None,
+                                                 scratch.data_ptr(), st))
+    for i in range(max(a.warmup, n_mats)):
+        call(i)
+    torch.cuda.synchronize()
+    sampler = ClockSampler(dev)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(a.steps):
+        call(i)
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1) / a.steps
+    flops = 2.0 * rows * n * k
+    _, tf, which = measured_peaks()
+    tfs = flops / (ms * 1e-3) / 1e12
+    return {"metric": "gemm_tflops", "value": tfs, "unit": "TFLOP/s", "n_gpus": 1, "steps": a.steps, "warmup": a.warmup,
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": fmt + " weights de-quantised to fp16 in registers, fp16 activations, fp32 accumulate (tcgen05 kind::f16)",
+            "data": "synthetic", "config": {"workload": a.workload, "n_out": n, "k": k, "batch": rows, "matrices_cycled": n_mats},
+            "gpu_launches": a.steps,
+            "roofline": {"bound": "tensor", "achieved": tfs, "peak": tf, "unit": "TFLOP/s", "frac": tfs / tf, "traffic": None,
+                         "peak_source": which + " (dense bf16 cuBLAS, sustained)", "kernel": "gemm_tc_kernel",
+                         "algorithmic_flops_per_launch": flops},
+            "clocks": clocks, "device_status": _lib.device_status()}
+
+
 # ----------------------------------------------------------------------------------------------
 # CPU arm: the oracle's restatement of the reference's PyTorch path on the host cores
 # ----------------------------------------------------------------------------------------------
@@ -343,6 +390,10 @@ def main():
             "e2e": {"value": cb["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
         return
 
+    if a.workload.startswith("gemm_"):
+        if rank == 0:
+            print(json.dumps(run_gemm(a, local)))
+        return
     if a.workload.startswith("gemv_"):
         if rank == 0:
             print(json.dumps(run_gemv(a, local)))

@@ -116,6 +116,14 @@ void ab_model_destroy(ab_model* m);
 size_t ab_workspace_bytes(const ab_model* m, int B, int T);
 int ab_forward(ab_model* m, int B, int T, const int32_t* tokens, void* const* state, void* workspace,
                void* logits, int full_output, void* stream);
+/* One stage of a layer pipeline (no counterpart in the reference, which is single-GPU; the per-block math is
+ * reference/rwkv7.py:198-216). The model holds a contiguous run of blocks; option "layer_offset" gives the index
+ * of its first block in the whole network (block 0 defines v_first, reference/rwkv7.py:239, :292).
+ * First stage: tokens != NULL (needs desc.emb), later stages: x_in fp16 [B*T, D]. v_first fp16 [B*T, D] is written
+ * by the first stage and read by the others. Last stage: logits fp16 [B,V] (needs desc.head / lnout), other
+ * stages: x_out fp16 [B*T, D]. State and workspace as in ab_forward (sized by ab_workspace_bytes). */
+int ab_forward_stage(ab_model* m, int B, int T, const int32_t* tokens, const void* x_in, void* v_first,
+                     void* const* state, void* workspace, void* x_out, void* logits, void* stream);
 /* Batch-1 decode as ONE persistent kernel per token (same results as ab_forward with B = T = 1).
  * ab_decode_program_build writes the token's phase list for a fixed set of buffers (token id, state
  * tensors, workspace, logits) into `program` (device memory, at least ab_decode_program_bytes(m) bytes,
