@@ -146,6 +146,14 @@ __device__ __forceinline__ __half2 e2m1x2_to_half2(uint32_t byte) {
         : "r"(byte));
     return *reinterpret_cast<__half2*>(&out);
 }
+// Four bytes = eight e2m1 codes -> four half2 (byte i -> out[i], low nibble first): one unpack, four converts.
+__device__ __forceinline__ void e2m1x8_to_half2x4(uint32_t word, uint32_t* out) {
+    asm("{\n .reg .b8 b0, b1, b2, b3;\n mov.b32 {b0, b1, b2, b3}, %4;\n"
+        " cvt.rn.f16x2.e2m1x2 %0, b0;\n cvt.rn.f16x2.e2m1x2 %1, b1;\n"
+        " cvt.rn.f16x2.e2m1x2 %2, b2;\n cvt.rn.f16x2.e2m1x2 %3, b3;\n}"
+        : "=r"(out[0]), "=r"(out[1]), "=r"(out[2]), "=r"(out[3])
+        : "r"(word));
+}
 // Two e4m3 codes (16 bits) -> half2.
 __device__ __forceinline__ __half2 e4m3x2_to_half2(uint32_t two) {
     uint32_t out;

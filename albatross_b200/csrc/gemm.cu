@@ -8,14 +8,17 @@
 //
 // The weights are the M side of the MMA so that every weight byte is read from HBM exactly once per
 // N tile; the batch (up to 320 rows per block: two MMAs of N = 160) is the N side.
-//   warps 0-3 : read this block's 128 weight rows straight from global memory (64 inputs per row and
-//               k-step), de-quantise in registers (int8 -> fp16 exactly; e2m1 x e4m3 block scale -> fp16
-//               exactly) and store them K-major with the 128-byte swizzle the MMA expects; afterwards
-//               they run the epilogue: tcgen05.ld of their 32 TMEM lanes, row / tensor scale, activation
-//               or residual, fp16 stores that are contiguous along the output features;
-//   warp 4    : one thread issues the TMA loads of the activation tile (tensor map over X, 128B swizzle);
-//   warp 5    : allocates TMEM; one thread issues tcgen05.mma (kind::f16) and commits to mbarriers.
-// Three-stage ring, all mbarrier waits bounded (status word on expiry), TMEM freed on every path.
+//   producer groups (G_NG groups of 4 warps; thread = one of the block's 128 weight rows): group g owns
+//               k-steps g, g + G_NG, ... It brings the row's 64 inputs of a k-step in (cp.async ring of raw
+//               quantised bytes; fp16 rows go straight to registers), de-quantises in registers (int8 ->
+//               fp16 exactly; e2m1 x e4m3 block scale -> fp16 exactly) and stores them K-major with the
+//               128-byte swizzle the MMA expects. One warp per scheduler cannot hide the latencies of this
+//               serial instruction stream; several groups on different k-steps can. Afterwards all groups
+//               run the epilogue: tcgen05.ld of 32 columns of their 32 TMEM lanes, row / tensor scale,
+//               activation or residual, fp16 stores (a warp writes 32 consecutive output features);
+//   next warp : one thread issues the TMA loads of the activation tile (tensor map over X, 128B swizzle);
+//   last warp : allocates TMEM; one thread issues tcgen05.mma (kind::f16) and commits to mbarriers.
+// Three-stage operand ring, all mbarrier waits bounded (status word on expiry), TMEM freed on every path.
 #include <cuda.h>
 
 #include "gemm.cuh"
@@ -25,12 +28,18 @@ namespace ab {
 
 namespace {
 
-constexpr int GT = 192;          // threads per block
+#ifndef G_NG_
+#define G_NG_ 2
+#endif
+constexpr int G_NG = G_NG_;      // producer groups
+constexpr int G_PROD = 128 * G_NG;
+constexpr int GT = G_PROD + 64;  // threads per block
 constexpr int G_STAGES = 3;
 constexpr int G_BM = 128;        // weight rows per block
 constexpr int G_BK = 64;         // inputs per k-step (128 bytes of fp16 = one swizzle row)
 constexpr int G_A_BYTES = G_BM * G_BK * 2;
-constexpr int G_RAW_BYTES = 48 * 1024;   // ring of raw (still quantised) weight k-steps filled by cp.async
+constexpr int G_RAW_BYTES = 56 * 1024;   // rings of raw (still quantised) weight k-steps filled by cp.async
+constexpr int G_RAW_GROUP = (G_RAW_BYTES / G_NG) & ~1023;   // one ring per producer group
 constexpr int G_MAX_OPS = 8;
 constexpr int G_COUNTERS = 4096;         // split-K arrival counters at the start of the scratch area
 
@@ -98,6 +107,23 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t* v) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* v) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint4 ldg_nc16(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
 __device__ __forceinline__ void cp_async_16(void* dst, const void* src, bool ok) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(ok ? 16 : 0) : "memory");
 }
@@ -107,7 +133,7 @@ __device__ __forceinline__ void cp_async_4(void* dst, const void* src, bool ok) 
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-__device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, %0;" ::"n"(G_PROD) : "memory"); }
 
 // K-major operand tile, 128-byte swizzle: rows of 128 bytes, groups of 8 rows 1024 bytes apart.
 __device__ __forceinline__ uint64_t umma_desc_sw128(const void* smem) {
@@ -179,14 +205,16 @@ __device__ __forceinline__ void raw_dequant(int fmt, int r_local, const unsigned
         const uint4 r1 = *reinterpret_cast<const uint4*>(slot + 2048 + r_local * 16);
         const uint32_t sc4 = *reinterpret_cast<const uint32_t*>(slot + 4096 + r_local * 4);
         const uint32_t words[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+        // the four block scales of these 64 inputs, each duplicated into both halves of a half2
+        const __half2 s01 = e4m3x2_to_half2(sc4 & 0xffffu), s23 = e4m3x2_to_half2(sc4 >> 16);
+        const __half2 scs[4] = {__low2half2(s01), __high2half2(s01), __low2half2(s23), __high2half2(s23)};
 #pragma unroll
         for (int c = 0; c < 8; ++c) {   // chunk c: 8 inputs = 4 bytes; scale block = c / 2
-            const __half2 s2 = e4m3x2_to_half2((sc4 >> (8 * (c >> 1))) & 0xffu);
-            const __half2 sc = __half2half2(__low2half(s2));
             uint32_t h[4];
+            e2m1x8_to_half2x4(words[c], h);
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const __half2 v = __hmul2(e2m1x2_to_half2((words[c] >> (8 * e)) & 0xffu), sc);   // exact in fp16
+                const __half2 v = __hmul2(*reinterpret_cast<const __half2*>(&h[e]), scs[c >> 1]);   // exact in fp16
                 h[e] = *reinterpret_cast<const uint32_t*>(&v);
             }
             out[c] = make_uint4(h[0], h[1], h[2], h[3]);
@@ -206,7 +234,7 @@ __device__ __forceinline__ float apply_epi(int epi, float o) {
 __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ GemmMaps maps,
                                                         const __grid_constant__ GemmGroup g) {
     extern __shared__ __align__(1024) unsigned char gsm[];
-    __shared__ uint64_t full_a[G_STAGES], full_b[G_STAGES], empty[G_STAGES], accum_bar;
+    __shared__ uint64_t full[G_STAGES], empty[G_STAGES], accum_bar;
     __shared__ uint32_t tmem_base_s;
     __shared__ int s_failed, s_last;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -237,8 +265,7 @@ __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ 
 
     if (tid == 0) {
         for (int s = 0; s < G_STAGES; ++s) {
-            mbar_init(&full_a[s], 128);
-            mbar_init(&full_b[s], 1);
+            mbar_init(&full[s], 5);   // the four warps of the group that owns the k-step + the TMA thread's expect_tx
             mbar_init(&empty[s], 1);
         }
         mbar_init(&accum_bar, 1);
@@ -246,7 +273,7 @@ __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ 
         s_failed = 0;
         s_last = 0;
     }
-    if (warp == 5) tmem_alloc(&tmem_base_s, (uint32_t)g.tmem_cols);
+    if (warp == 4 * G_NG + 1) tmem_alloc(&tmem_base_s, (uint32_t)g.tmem_cols);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -254,6 +281,7 @@ __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ 
 
     // After the first wait that runs out, nobody waits any more: the block drains in bounded time.
     auto wait_ok = [&](uint64_t* bar, uint32_t parity) {
+        if (mbar_try_wait(bar, parity)) return;   // the common case costs one instruction
         if (*reinterpret_cast<volatile int*>(&s_failed)) return;
         if (!mbar_wait_bounded(bar, parity, 1u << 16)) {
             *reinterpret_cast<volatile int*>(&s_failed) = 1;
@@ -261,109 +289,131 @@ __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ 
         }
     };
 
-    if (warp < 4) {
-        // ===== weight producers: thread = weight row of the tile =====
-        const int row = m0 + tid;
+    if (warp < 4 * G_NG) {
+        // ===== weight producers: thread = weight row of the tile, group = every G_NG-th k-step =====
+        const int grp = warp >> 2, r_local = tid & 127;
+        const int row = m0 + r_local;
         const int fmt = pb.w.fmt;
-        const int slot_bytes = raw_row_bytes(fmt) * G_BM + (fmt == FMT_FP4 ? G_BM * 4 : 0);
-        int depth = G_RAW_BYTES / slot_bytes;   // k-steps of raw weights in flight
-        if (depth > 8) depth = 8;
-        for (int i = 0; i < depth - 1; ++i) {
-            if (i < n_ksteps) raw_issue(pb.w, row, tid, kstep_of(i), smRaw + (i % depth) * slot_bytes);
-            cp_async_commit();
-        }
-        for (int ks = 0; ks < n_ksteps; ++ks) {
+        const int n_out = pb.w.n_out;
+        const bool row_ok = row < n_out;
+
+        // de-quantised k-step -> operand stage (swizzled), then tell the MMA warp
+        auto put_stage = [&](int ks, const uint4* cur) {
             const int s = ks % G_STAGES, f = ks / G_STAGES;
-            const int ahead = ks + depth - 1;
-            if (ahead < n_ksteps) raw_issue(pb.w, row, tid, kstep_of(ahead), smRaw + (ahead % depth) * slot_bytes);
-            cp_async_commit();
-            // all but the newest depth-1 groups have landed: k-step ks is there
-            switch (depth) {
-                case 8: cp_async_wait<7>(); break;
-                case 7: cp_async_wait<6>(); break;
-                case 6: cp_async_wait<5>(); break;
-                case 5: cp_async_wait<4>(); break;
-                case 4: cp_async_wait<3>(); break;
-                case 3: cp_async_wait<2>(); break;
-                default: cp_async_wait<0>(); break;
-            }
-            uint4 cur[8];
-            raw_dequant(fmt, tid, smRaw + (ks % depth) * slot_bytes, cur);
             if (f > 0) wait_ok(&empty[s], (f - 1) & 1);
-            unsigned char* dst = smA + s * G_A_BYTES + tid * 128;
+            unsigned char* dst = smA + s * G_A_BYTES + r_local * 128;
 #pragma unroll
-            for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(dst + ((c ^ (tid & 7)) << 4)) = cur[c];
+            for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(dst + ((c ^ (r_local & 7)) << 4)) = cur[c];
             fence_proxy_async();   // generic-proxy stores -> visible to the tensor core's async proxy
-            mbar_arrive(&full_a[s]);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&full[s]);   // one arrival per warp of the owning group
+        };
+
+        if (fmt == FMT_F16) {
+            // fp16 rows need no conversion: global -> registers one own k-step ahead -> operand stage
+            const unsigned char* rowp = reinterpret_cast<const unsigned char*>(pb.w.w) + (row_ok ? (size_t)row * pb.w.k * 2 : 0);
+            auto fetch = [&](int ks, uint4* dst) {
+                const int k0 = kstep_of(ks) * G_BK;
+#pragma unroll
+                for (int c = 0; c < 8; ++c)
+                    dst[c] = (row_ok && k0 + c * 8 < pb.w.k) ? ldg_nc16(rowp + (size_t)(k0 + c * 8) * 2) : make_uint4(0, 0, 0, 0);
+            };
+            uint4 nxt[8];
+            if (grp < n_ksteps) fetch(grp, nxt);
+            for (int ks = grp; ks < n_ksteps; ks += G_NG) {
+                uint4 cur[8];
+#pragma unroll
+                for (int c = 0; c < 8; ++c) cur[c] = nxt[c];
+                if (ks + G_NG < n_ksteps) fetch(ks + G_NG, nxt);
+                put_stage(ks, cur);
+            }
+        } else {
+            unsigned char* ring = smRaw + grp * G_RAW_GROUP;
+            const int slot_bytes = raw_row_bytes(fmt) * G_BM + (fmt == FMT_FP4 ? G_BM * 4 : 0);
+            int depth = G_RAW_GROUP / slot_bytes;   // own k-steps of raw weights in flight
+            if (depth > 6) depth = 6;
+            for (int j = 0; j < depth - 1; ++j) {
+                const int ks = grp + j * G_NG;
+                if (ks < n_ksteps) raw_issue(pb.w, row, r_local, kstep_of(ks), ring + (j % depth) * slot_bytes);
+                cp_async_commit();
+            }
+            int j = 0;
+            for (int ks = grp; ks < n_ksteps; ks += G_NG, ++j) {
+                const int ja = j + depth - 1, ks_a = grp + ja * G_NG;
+                if (ks_a < n_ksteps) raw_issue(pb.w, row, r_local, kstep_of(ks_a), ring + (ja % depth) * slot_bytes);
+                cp_async_commit();
+                // all but the newest depth-1 groups have landed: k-step ks is there
+                switch (depth) {
+                    case 6: cp_async_wait<5>(); break;
+                    case 5: cp_async_wait<4>(); break;
+                    case 4: cp_async_wait<3>(); break;
+                    case 3: cp_async_wait<2>(); break;
+                    case 2: cp_async_wait<1>(); break;
+                    default: cp_async_wait<0>(); break;
+                }
+                uint4 cur[8];
+                raw_dequant(fmt, r_local, ring + (j % depth) * slot_bytes, cur);
+                put_stage(ks, cur);
+            }
         }
 
-        // ===== epilogue: thread = output feature (TMEM lane) =====
+        // ===== epilogue: thread = output feature (TMEM lane); groups take turns on chunks of 32 batch rows =====
         wait_ok(&accum_bar, 0);
         tc_fence_after();
-        const bool row_ok = row < pb.w.n_out;
         float scale = 1.f;
         if (row_ok) scale = fmt == FMT_I8 ? reinterpret_cast<const float*>(pb.w.scale)[row] : pb.w.tscale;
-        const int n_out = pb.w.n_out;
-        __half* tr = reinterpret_cast<__half*>(smA);   // [2][16][128] transpose buffers; the operand stages are idle now
-        const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
-        const int n_chunks = (min(g.n_tile, g.rows - n0) + 15) / 16;
-        const bool vec_ok = (n_out % 8) == 0;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+        const int n_valid = min(g.n_tile, g.rows - n0);
+        const int n_chunks = (n_valid + 31) / 32;
+        const int epi = pb.epi;
 
-        // finished values of one 16-column chunk -> fp16 rows of Y, 16-byte stores along the output features
-        auto emit_chunk = [&](int ci, const float* v) {
-            __half* t = tr + (ci & 1) * (16 * G_BM);
+        // finished sums of 32 batch rows of this thread's feature -> fp16, stored straight to Y: the 32 lanes of a
+        // warp write 32 consecutive features (64 bytes) of one batch row per instruction
+        auto emit32 = [&](int ci, const float* v) {
+            const int c0 = ci * 32;
+            const size_t off = (size_t)(n0 + c0) * n_out + row;
+            __half* yp = pb.y + off;
+            if (!row_ok) return;
+            if (epi == EPI_RESID) {
+                const __half* rp = pb.resid + off;
 #pragma unroll
-            for (int i = 0; i < 16; ++i) t[i * G_BM + tid] = __float2half_rn(apply_epi(pb.epi, rh(v[i] * scale)));
-            epi_sync();
+                for (int h8 = 0; h8 < 32; h8 += 8) {   // eight loads in flight, then eight stores
+                    __half rs[8];
 #pragma unroll
-            for (int rep = 0; rep < 2; ++rep) {
-                const int task = tid + rep * 128;       // 16 batch rows x 16 chunks of 8 features
-                const int bi = task >> 4, ch = task & 15;
-                const int b = n0 + ci * 16 + bi, col = m0 + ch * 8;
-                if (b < g.rows && col < n_out) {
-                    uint4 val = *reinterpret_cast<const uint4*>(t + bi * G_BM + ch * 8);
-                    __half* yp = pb.y + (size_t)b * n_out + col;
-                    if (vec_ok) {
-                        if (pb.epi == EPI_RESID) {
-                            const uint4 rv = *reinterpret_cast<const uint4*>(pb.resid + (size_t)b * n_out + col);
-                            __half2* a2 = reinterpret_cast<__half2*>(&val);
-                            const __half2* r2 = reinterpret_cast<const __half2*>(&rv);
+                    for (int i = 0; i < 8; ++i) rs[i] = c0 + h8 + i < n_valid ? rp[(size_t)(h8 + i) * n_out] : __half(0.f);
 #pragma unroll
-                            for (int e = 0; e < 4; ++e) a2[e] = __hadd2(r2[e], a2[e]);
-                        }
-                        *reinterpret_cast<uint4*>(yp) = val;
-                    } else {
-                        const __half* hv = reinterpret_cast<const __half*>(&val);
-                        for (int e = 0; e < 8 && col + e < n_out; ++e) {
-                            __half o = hv[e];
-                            if (pb.epi == EPI_RESID) o = __hadd(pb.resid[(size_t)b * n_out + col + e], o);
-                            yp[e] = o;
-                        }
-                    }
+                    for (int i = 0; i < 8; ++i)
+                        if (c0 + h8 + i < n_valid)
+                            yp[(size_t)(h8 + i) * n_out] = __hadd(rs[i], __float2half_rn(v[h8 + i] * scale));
                 }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    if (c0 + i < n_valid) yp[(size_t)i * n_out] = __float2half_rn(apply_epi(epi, rh(v[i] * scale)));
             }
-            // the other buffer is used next; this one is rewritten two chunks later, after another epi_sync
         };
 
         if (pb.ksplit == 1) {
-            for (int ci = 0; ci < n_chunks; ++ci) {
-                uint32_t raw[16];
-                tc_ld16(lane_addr + (uint32_t)(ci * 16), raw);
-                float v[16];
+            for (int ci = grp; ci < n_chunks; ci += G_NG) {
+                uint32_t raw[32];
+                tc_ld32(lane_addr + (uint32_t)(ci * 32), raw);
+                float v[32];
 #pragma unroll
-                for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(raw[i]);
-                emit_chunk(ci, v);
+                for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(raw[i]);
+                emit32(ci, v);
             }
         } else {
             // split K: park this block's fp32 tile, the last block to arrive sums all of them in a fixed order
             const int tile = pb.tile_base + m_tile * gridDim.y + blockIdx.y;
-            float* mine = g.partials + pb.part_base +
-                          ((size_t)(m_tile * gridDim.y + blockIdx.y) * pb.ksplit + z) * ((size_t)g.n_tile * G_BM);
-            for (int ci = 0; ci < n_chunks; ++ci) {
-                uint32_t raw[16];
-                tc_ld16(lane_addr + (uint32_t)(ci * 16), raw);
+            const size_t tile_floats = (size_t)g.n_tile * G_BM;
+            float* tile0 = g.partials + pb.part_base + ((size_t)(m_tile * gridDim.y + blockIdx.y) * pb.ksplit) * tile_floats;
+            float* mine = tile0 + (size_t)z * tile_floats;
+            for (int ci = grp; ci < n_chunks; ci += G_NG) {
+                uint32_t raw[32];
+                tc_ld32(lane_addr + (uint32_t)(ci * 32), raw);
 #pragma unroll
-                for (int i = 0; i < 16; ++i) __stcg(mine + (size_t)(ci * 16 + i) * G_BM + tid, __uint_as_float(raw[i]));
+                for (int i = 0; i < 32; ++i)
+                    if (ci * 32 + i < g.n_tile) __stcg(mine + (size_t)(ci * 32 + i) * G_BM + r_local, __uint_as_float(raw[i]));
             }
             __threadfence();
             epi_sync();
@@ -376,61 +426,76 @@ __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ 
             }
             epi_sync();
             if (s_last) {
-                const float* tile0 = g.partials + pb.part_base +
-                                     ((size_t)(m_tile * gridDim.y + blockIdx.y) * pb.ksplit) * ((size_t)g.n_tile * G_BM);
-                for (int ci = 0; ci < n_chunks; ++ci) {
-                    float v[16];
+                for (int ci = grp; ci < n_chunks; ci += G_NG) {
+                    float v[32];
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) v[i] = 0.f;
+                    for (int i = 0; i < 32; ++i) v[i] = 0.f;
                     for (int zz = 0; zz < pb.ksplit; ++zz) {
-                        const float* src = tile0 + (size_t)zz * g.n_tile * G_BM;
+                        const float* src = tile0 + (size_t)zz * tile_floats;
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) v[i] += __ldcg(src + (size_t)(ci * 16 + i) * G_BM + tid);
+                        for (int i = 0; i < 32; ++i)
+                            if (ci * 32 + i < g.n_tile) v[i] += __ldcg(src + (size_t)(ci * 32 + i) * G_BM + r_local);
                     }
-                    emit_chunk(ci, v);
+                    emit32(ci, v);
                 }
             }
         }
         tc_fence_before();
-    } else if (warp == 4) {
+    } else if (warp == 4 * G_NG) {
         // ===== activation tiles by TMA =====
         if (lane == 0) {
             const CUtensorMap* map = &maps.m[pi];
             for (int ks = 0; ks < n_ksteps; ++ks) {
                 const int s = ks % G_STAGES, f = ks / G_STAGES;
                 if (f > 0) wait_ok(&empty[s], (f - 1) & 1);
-                mbar_expect_tx(&full_b[s], (uint32_t)b_bytes);
+                mbar_expect_tx(&full[s], (uint32_t)b_bytes);
                 for (int j = 0; j < g.n_inst; ++j)
                     tma_load_2d(smB + s * b_bytes + j * n_inst_cols * 128, map, kstep_of(ks) * G_BK, n0 + j * n_inst_cols,
-                                &full_b[s]);
+                                &full[s]);
             }
         }
     } else {
         // ===== MMA issue =====
         if (lane == 0) {
+            // One thread feeds the tensor core, so its instruction stream is kept short: descriptors are built
+            // once, a stage or a 16-input step further is an add to the (address >> 4) field.
             const uint32_t idesc = umma_idesc_f16(n_inst_cols);
+            const uint64_t da0 = umma_desc_sw128(smA), db0 = umma_desc_sw128(smB);
+            const uint64_t a_stage = (uint64_t)(G_A_BYTES >> 4), b_stage = (uint64_t)(b_bytes >> 4);
+            const uint64_t b_half = (uint64_t)((n_inst_cols * 128) >> 4);
+            const uint32_t d1 = tmem_base + (uint32_t)n_inst_cols;
+            const bool two = g.n_inst == 2;
+            int s = 0;
+            uint32_t parity = 0;
+            uint64_t da = da0, db = db0;
             for (int ks = 0; ks < n_ksteps; ++ks) {
-                const int s = ks % G_STAGES, f = ks / G_STAGES;
-                wait_ok(&full_a[s], f & 1);
-                wait_ok(&full_b[s], f & 1);
+                wait_ok(&full[s], parity);
                 tc_fence_after();
-                const uint64_t da = umma_desc_sw128(smA + s * G_A_BYTES);
+                const uint32_t acc0 = ks > 0 ? 1u : 0u;
+                // advancing 16 inputs = 32 bytes inside the swizzle row: +2 in the (address >> 4) field
+                tc_mma_f16(tmem_base, da, db, idesc, acc0);
+                if (two) tc_mma_f16(d1, da, db + b_half, idesc, acc0);
 #pragma unroll
-                for (int k4 = 0; k4 < G_BK / 16; ++k4)
-                    for (int j = 0; j < g.n_inst; ++j) {
-                        const uint64_t db = umma_desc_sw128(smB + s * b_bytes + j * n_inst_cols * 128);
-                        // advancing 16 inputs = 32 bytes inside the swizzle row: +2 in the (address >> 4) field
-                        tc_mma_f16(tmem_base + (uint32_t)(j * n_inst_cols), da + (uint64_t)(2 * k4), db + (uint64_t)(2 * k4),
-                                   idesc, (ks > 0 || k4 > 0) ? 1u : 0u);
-                    }
+                for (int k4 = 1; k4 < G_BK / 16; ++k4) {
+                    tc_mma_f16(tmem_base, da + (uint64_t)(2 * k4), db + (uint64_t)(2 * k4), idesc, 1u);
+                    if (two) tc_mma_f16(d1, da + (uint64_t)(2 * k4), db + b_half + (uint64_t)(2 * k4), idesc, 1u);
+                }
                 tc_commit(&empty[s]);   // the stage may be refilled once these MMAs have read it
+                da += a_stage;
+                db += b_stage;
+                if (++s == G_STAGES) {
+                    s = 0;
+                    parity ^= 1u;
+                    da = da0;
+                    db = db0;
+                }
             }
             tc_commit(&accum_bar);
         }
         tc_fence_before();
     }
     __syncthreads();
-    if (warp == 5) {
+    if (warp == 4 * G_NG + 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, (uint32_t)g.tmem_cols);
     }
@@ -554,7 +619,6 @@ int gemm_group_launch(const GemmOp* ops, int n, int rows, void* scratch, cudaStr
     const int n_inst_cols = gs.n_tile / gs.n_inst;
     int cta = 0, tile = 0;
     long long part = 0;
-    size_t raw_slot_max = 0;
     for (int i = 0; i < n; ++i) {
         const GemmOp& op = ops[i];
         const ab_mat& m = op.w;
@@ -585,7 +649,6 @@ int gemm_group_launch(const GemmOp* ops, int n, int rows, void* scratch, cudaStr
             set_error("gemm: cuTensorMapEncodeTiled failed with %d (rows=%d k=%d)", (int)cr, rows, m.k);
             return ERR_CUDA;
         }
-        (void)raw_slot_max;
     }
     for (int i = n; i < G_MAX_OPS; ++i) maps.m[i] = maps.m[0];
 
