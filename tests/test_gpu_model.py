@@ -75,6 +75,25 @@ def test_batch_path_against_oracle(fmt):
         model.forward_batch([[1, 2], [3]], None)         # ragged batches are rejected, as in the reference
 
 
+def test_wide_batch_decode_uses_the_persistent_head_kernel():
+    """B*H >= 512 single-step batches take the persistent (sequence, head) kernel with the bulk-copied state ring;
+    more items than resident blocks, so every block walks several items and reuses its stages."""
+    model, args = model_for("tiny", "int8")
+    o, _ = oracle_for("tiny", "int8")
+    B = 700
+    prompts = [seeded_tokens(args.vocab_size, 2, seed=s) for s in range(B)]
+    st_ref = new_state(args.n_layer, args.n_embd, batch=B)
+    want, st_ref = o.forward_tokens(prompts, st_ref)
+    got, state = model.forward_batch(prompts, None)
+    for step in range(3):
+        toks = [[int(want[b].argmax())] for b in range(B)]
+        want, st_ref = o.forward_tokens(toks, st_ref)
+        got, state = model.forward_batch(toks, state)
+        assert rel_err(got.float().cpu().numpy(), want.numpy()) <= LOGIT_REL_TOL
+    for i in range(args.n_layer):
+        assert rel_err(state[3 * i + 1].cpu().numpy(), st_ref[3 * i + 1].numpy()) <= LOGIT_REL_TOL
+
+
 def test_state_is_updated_in_place_and_forkable():
     model, args = model_for("tiny", "int8")
     state = model.new_state()
