@@ -144,20 +144,26 @@ __global__ void __launch_bounds__(HT) head_fused_kernel(const __grid_constant__ 
 // Batched single-step kernel (T = 1, many sequences): persistent blocks walk a list of (sequence, head) items.
 // ---------------------------------------------------------------------------------------------
 // The state (16 KiB per item, read once and written once per token) is all of the traffic, so the kernel is built
-// around keeping it moving:
+// around keeping it moving, and nothing on an item's critical path waits for a global load:
 //   * warps 0-7 (256 threads) run the recurrence. The item's state arrives as ONE 16 KiB bulk copy into a ring of
 //     HB_STAGES shared-memory stages (mbarrier, byte-counted), up to HB_STAGES-1 items ahead of the one being worked on;
 //     the updated state goes straight from registers to global memory.
-//   * warp 8 does the per-channel glue (k normalisation and modulation, v residual gate, decay) of item n+1 while
-//     warps 0-7 are on item n, and the group norm / bonus / gate of item n afterwards; its lane 0 issues the bulk copies.
+//   * warp 8 ("pre") turns the projections of item n+1 into the vectors of the recurrence (k normalisation and
+//     modulation, v residual gate, decay) while warps 0-7 are on item n; its inputs were fetched an item earlier.
+//     Its lane 0 issues the bulk copies.
+//   * warp 9 ("post") turns the read-out of item n into the block output (group norm, bonus, gate).
 // Thread (i = tid/4, q = tid%4) owns, of state row i, the four 16-byte chunks {4m + q, m = 0..3} and visits them in
 // the order m = (e + i) % 4: a quarter-warp then reads eight different bank groups of the stage (no conflicts).
+// Helper lanes own channels 2*lane and 2*lane+1 (one 32-bit load per vector).
 constexpr int HB_STAGES = 4;
-constexpr int HB_THREADS = HT + 32;
+constexpr int HB_THREADS = HT + 64;
 constexpr int HB_STATE_BYTES = 64 * 64 * 4;
 
 struct HeadVec {
     float r[64], w[64], k[64], a[64], b[64], v[64];
+};
+struct HeadPost {   // what the output stage needs from the input stage
+    float v[64];
     float rkr;
     float pad[3];
 };
@@ -167,23 +173,33 @@ __device__ __forceinline__ void bar_arrive_id(int id, int n) { asm volatile("bar
 __device__ __forceinline__ void st_cs16(float* p, float4 v) {
     asm volatile("st.global.cs.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
 }
+// two adjacent fp16 channels; activations bypass L1 (written by another SM in an earlier kernel)
+__device__ __forceinline__ float2 ld2a(const __half* p) { return __half22float2(__ldcg(reinterpret_cast<const __half2*>(p))); }
+__device__ __forceinline__ float2 ld2p(const __half* p) { return __half22float2(__ldg(reinterpret_cast<const __half2*>(p))); }
 
-__global__ void __launch_bounds__(HB_THREADS) head_batch_kernel(const __grid_constant__ HeadParams p, int n_items) {
+__global__ void __launch_bounds__(HB_THREADS, 3) head_batch_kernel(const __grid_constant__ HeadParams p, int n_items) {
     extern __shared__ __align__(128) unsigned char dsm[];   // HB_STAGES x 16 KiB
     __shared__ __align__(16) HeadVec vec[2];
-    __shared__ float sy[2][64];
+    __shared__ __align__(16) HeadPost post[3];
+    __shared__ float sy[4][64];
     __shared__ uint64_t full[HB_STAGES];
     __shared__ int s_failed;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n_mine = ((int)blockIdx.x < n_items) ? (n_items - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
     auto item_of = [&](int n) { return (int)blockIdx.x + n * (int)gridDim.x; };
+    auto off_of = [&](int n) {   // element offset of the item's 64 channels in a [B, D] activation
+        const int it = item_of(n), b = it / p.H, h = it - b * p.H;
+        return (size_t)b * p.D + h * 64;
+    };
     if (tid == 0) {
         for (int s = 0; s < HB_STAGES; ++s) mbar_init(&full[s], 1);
         fence_mbar_init();
         s_failed = 0;
     }
     __syncthreads();
-    // named barriers: 1, 2 = vectors of an even / odd item are ready; 3, 4 = its read-out is ready
+    // Named barriers. 1, 2: the vectors of an even / odd item are ready (pre arrives, warps 0-7 wait).
+    // 3, 4: the recurrence of an even / odd item is done (warps 0-7 arrive, pre and post wait).
+    constexpr int N_VEC = HT + 32, N_DONE = HT + 64;
     if (warp == 8) {
         auto load_state_of = [&](int n) {
             const int s = n % HB_STAGES;
@@ -197,95 +213,106 @@ __global__ void __launch_bounds__(HB_THREADS) head_batch_kernel(const __grid_con
             pdl_wait();
             pdl_launch_dependents();
         }
-        // activations of the two channels of this lane, fetched one item ahead
-        struct Act { float r[2], k[2], v[2], w_raw[2], a_raw[2], vg_raw[2], vf[2]; };
+        struct Act { float2 r, k, v, w_raw, a_raw, vg_raw, vf; };
         auto fetch = [&](int n, Act& a) {
-            const int it = item_of(n), b = it / p.H, h = it - b * p.H;
-            const size_t off = (size_t)b * p.D + h * 64;
+            const size_t o = off_of(n) + 2 * lane;
+            a.r = ld2a(p.r + o); a.k = ld2a(p.k + o); a.v = ld2a(p.v + o);
+            a.w_raw = ld2a(p.w_raw + o); a.a_raw = ld2a(p.a_raw + o);
+            if (!p.layer0) { a.vg_raw = ld2a(p.vg_raw + o); a.vf = ld2a(p.v_first + o); }
+        };
+        // reference/rwkv7.py:284-297 for one (sequence, head)
+        auto glue = [&](int n, const Act& a, HeadVec& o, HeadPost& po) {
+            const int it = item_of(n), h = it % p.H;
+            const int gc = h * 64 + 2 * lane;
+            const float2 a0 = ld2p(p.a0 + gc), k_k = ld2p(p.k_k + gc), k_a = ld2p(p.k_a + gc);
+            const float2 w0 = ld2p(p.w0 + gc), r_k = ld2p(p.r_k + gc);
+            const float rr[2] = {a.r.x, a.r.y}, kr[2] = {a.k.x, a.k.y};
+            float vv[2] = {a.v.x, a.v.y};
+            const float a_raw[2] = {a.a_raw.x, a.a_raw.y}, w_raw[2] = {a.w_raw.x, a.w_raw.y};
+            const float a0_[2] = {a0.x, a0.y}, kk_[2] = {k_k.x, k_k.y}, ka_[2] = {k_a.x, k_a.y};
+            const float w0_[2] = {w0.x, w0.y}, rk_[2] = {r_k.x, r_k.y};
+            if (p.layer0) {
+                *reinterpret_cast<__half2*>(p.v_first + off_of(n) + 2 * lane) = __floats2half2_rn(vv[0], vv[1]);
+            } else {
+                const float2 v0 = ld2p(p.v0 + gc);
+                const float v0_[2] = {v0.x, v0.y}, vg_raw[2] = {a.vg_raw.x, a.vg_raw.y}, vf[2] = {a.vf.x, a.vf.y};
 #pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const int c = lane + 32 * e;
-                a.r[e] = lda(p.r + off + c);
-                a.k[e] = lda(p.k + off + c);
-                a.v[e] = lda(p.v + off + c);
-                a.w_raw[e] = lda(p.w_raw + off + c);
-                a.a_raw[e] = lda(p.a_raw + off + c);
-                if (!p.layer0) {
-                    a.vg_raw[e] = lda(p.vg_raw + off + c);
-                    a.vf[e] = lda(p.v_first + off + c);
+                for (int e = 0; e < 2; ++e) {
+                    const float vg = rh(sigmoidf_(rh(v0_[e] + vg_raw[e])));
+                    vv[e] = rh(vv[e] + rh(rh(vf[e] - vv[e]) * vg));
                 }
             }
-        };
-        // reference/rwkv7.py:284-297 for one (sequence, head): vectors of the recurrence into `o`
-        auto glue = [&](int n, const Act& a, HeadVec& o) {
-            const int it = item_of(n), b = it / p.H, h = it - b * p.H;
-            const size_t off = (size_t)b * p.D + h * 64;
             float kk0[2], av[2];
             float ssq = 0.f, rkr = 0.f;
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
-                const int c = lane + 32 * e, gc = h * 64 + c;
-                const float rr = a.r[e], kr = a.k[e];
-                float vv = a.v[e];
-                const float aa = rh(sigmoidf_(rh(__half2float(p.a0[gc]) + a.a_raw[e])));
-                kk0[e] = rh(kr * __half2float(p.k_k[gc]));
+                const int c = 2 * lane + e;
+                const float aa = rh(sigmoidf_(rh(a0_[e] + a_raw[e])));
+                kk0[e] = rh(kr[e] * kk_[e]);
                 ssq = fmaf(kk0[e], kk0[e], ssq);
-                const float k2 = rh(kr * rh(1.f + rh(rh(aa - 1.f) * __half2float(p.k_a[gc]))));
-                if (p.layer0) {
-                    p.v_first[off + c] = __float2half_rn(vv);
-                } else {
-                    const float vg = rh(sigmoidf_(rh(__half2float(p.v0[gc]) + a.vg_raw[e])));
-                    vv = rh(vv + rh(rh(a.vf[e] - vv) * vg));
-                }
-                const float wd = __expf(-0.606531f * sigmoidf_(rh(__half2float(p.w0[gc]) + a.w_raw[e])));
-                o.r[c] = rr; o.w[c] = wd; o.k[c] = k2; o.v[c] = vv;
+                const float k2 = rh(kr[e] * rh(1.f + rh(rh(aa - 1.f) * ka_[e])));
+                // decay in fp32 as on the reference's single-token path (reference/rwkv7.py:241)
+                const float wd = __expf(-0.606531f * sigmoidf_(rh(w0_[e] + w_raw[e])));
+                o.r[c] = rr[e]; o.w[c] = wd; o.k[c] = k2; o.v[c] = vv[e];
+                po.v[c] = vv[e];
                 av[e] = aa;
-                rkr += rh(rh(rr * k2) * __half2float(p.r_k[gc]));
+                rkr += rh(rh(rr[e] * k2) * rk_[e]);
             }
             ssq = warp_sum(ssq);
             rkr = rh(warp_sum(rkr));
             const float nrm = fmaxf(rh(sqrtf(ssq)), 1e-12f);
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
-                const int c = lane + 32 * e;
                 const float kk = rh(kk0[e] / nrm);
-                o.a[c] = -kk;
-                o.b[c] = rh(kk * av[e]);
+                o.a[2 * lane + e] = -kk;
+                o.b[2 * lane + e] = rh(kk * av[e]);
             }
-            if (lane == 0) o.rkr = rkr;
+            if (lane == 0) po.rkr = rkr;
         };
-        Act act;
+        Act cur, nxt;
         if (n_mine > 0) {
-            fetch(0, act);
-            glue(0, act, vec[0]);
-            bar_arrive_id(1, HB_THREADS);
+            fetch(0, cur);
+            if (n_mine > 1) fetch(1, nxt);
+            glue(0, cur, vec[0], post[0]);
+            bar_arrive_id(1, N_VEC);
+            cur = nxt;
         }
-        for (int n = 0; n < n_mine; ++n) {
-            if (n + 1 < n_mine) {
-                fetch(n + 1, act);
-                glue(n + 1, act, vec[(n + 1) & 1]);
-                bar_arrive_id(1 + ((n + 1) & 1), HB_THREADS);
+        for (int n = 0; n + 1 < n_mine; ++n) {
+            // cur = inputs of item n+1 (fetched an iteration ago); start on those of item n+2
+            if (n + 2 < n_mine) fetch(n + 2, nxt);
+            if (n > 0) {
+                bar_sync_id(3 + ((n - 1) & 1), N_DONE);   // item n-1 is through: its vectors and its stage are free
+                if (lane == 0 && n - 1 + HB_STAGES < n_mine) load_state_of(n - 1 + HB_STAGES);
             }
-            bar_sync_id(3 + (n & 1), HB_THREADS);   // item n: state consumed, read-out in sy
-            if (lane == 0 && n + HB_STAGES < n_mine) load_state_of(n + HB_STAGES);
+            glue(n + 1, cur, vec[(n + 1) & 1], post[(n + 1) % 3]);
+            bar_arrive_id(1 + ((n + 1) & 1), N_VEC);
+            cur = nxt;
+        }
+        // the barriers of the last items still expect this warp
+        for (int n = max(n_mine - 1, 1); n <= n_mine; ++n) bar_sync_id(3 + ((n - 1) & 1), N_DONE);
+    } else if (warp == 9) {
+        if (p.use_pdl) pdl_wait();
+        float2 g_cur = make_float2(0.f, 0.f), g_nxt = g_cur;
+        if (n_mine > 0) g_cur = ld2a(p.g + off_of(0) + 2 * lane);
+        for (int n = 0; n < n_mine; ++n) {
+            if (n + 1 < n_mine) g_nxt = ld2a(p.g + off_of(n + 1) + 2 * lane);
+            const int it = item_of(n), h = it % p.H, gc = h * 64 + 2 * lane;
+            const float2 lw = ld2p(p.lnx_w + gc), lb = ld2p(p.lnx_b + gc);
+            bar_sync_id(3 + (n & 1), N_DONE);
             // group norm over the head's 64 channels (eps 64e-5), bonus, gate (reference/rwkv7.py:297-299)
-            const int it = item_of(n), b = it / p.H, h = it - b * p.H;
-            const size_t off = (size_t)b * p.D + h * 64;
-            const HeadVec& cv = vec[n & 1];
-            const float y0 = sy[n & 1][lane], y1 = sy[n & 1][lane + 32];
-            const float mean = warp_sum(y0 + y1) * (1.f / 64.f);
-            const float d0 = y0 - mean, d1 = y1 - mean;
+            const HeadPost& po = post[n % 3];
+            const float2 y2 = *reinterpret_cast<const float2*>(&sy[n & 3][2 * lane]);
+            const float mean = warp_sum(y2.x + y2.y) * (1.f / 64.f);
+            const float d0 = y2.x - mean, d1 = y2.y - mean;
             const float var = warp_sum(d0 * d0 + d1 * d1) * (1.f / 64.f);
             const float rstd = rsqrtf(var + 64e-5f);
-            const float rkr = cv.rkr;
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const int c = lane + 32 * e, gc = h * 64 + c;
-                float o = rh((e ? d1 : d0) * rstd * __half2float(p.lnx_w[gc]) + __half2float(p.lnx_b[gc]));
-                o = rh(o + rh(rkr * cv.v[c]));
-                p.out[off + c] = __float2half_rn(o * lda(p.g + off + c));
-            }
-            __syncwarp();
+            const float rkr = po.rkr;
+            const float2 v2 = *reinterpret_cast<const float2*>(&po.v[2 * lane]);
+            float o0 = rh(d0 * rstd * lw.x + lb.x), o1 = rh(d1 * rstd * lw.y + lb.y);
+            o0 = rh(o0 + rh(rkr * v2.x));
+            o1 = rh(o1 + rh(rkr * v2.y));
+            *reinterpret_cast<__half2*>(p.out + off_of(n) + 2 * lane) = __floats2half2_rn(o0 * g_cur.x, o1 * g_cur.y);
+            g_cur = g_nxt;
         }
     } else {
         const int i = tid >> 2, q = tid & 3;
@@ -300,15 +327,14 @@ __global__ void __launch_bounds__(HB_THREADS) head_batch_kernel(const __grid_con
             float4 st[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) st[e] = *reinterpret_cast<const float4*>(srow + 16 * ((e + i) & 3) + 4 * q);
-            bar_sync_id(1 + (n & 1), HB_THREADS);
+            bar_sync_id(1 + (n & 1), N_VEC);
             const HeadVec& cv = vec[n & 1];
             float sa = 0.f;
-            float4 a4[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                a4[e] = *reinterpret_cast<const float4*>(cv.a + 16 * ((e + i) & 3) + 4 * q);
-                sa = fmaf(a4[e].x, st[e].x, sa); sa = fmaf(a4[e].y, st[e].y, sa);
-                sa = fmaf(a4[e].z, st[e].z, sa); sa = fmaf(a4[e].w, st[e].w, sa);
+                const float4 a4 = *reinterpret_cast<const float4*>(cv.a + 16 * ((e + i) & 3) + 4 * q);
+                sa = fmaf(a4.x, st[e].x, sa); sa = fmaf(a4.y, st[e].y, sa);
+                sa = fmaf(a4.z, st[e].z, sa); sa = fmaf(a4.w, st[e].w, sa);
             }
             sa += __shfl_xor_sync(0xffffffffu, sa, 1);
             sa += __shfl_xor_sync(0xffffffffu, sa, 2);
@@ -329,8 +355,8 @@ __global__ void __launch_bounds__(HB_THREADS) head_batch_kernel(const __grid_con
             }
             y += __shfl_xor_sync(0xffffffffu, y, 1);
             y += __shfl_xor_sync(0xffffffffu, y, 2);
-            if (q == 0) sy[n & 1][i] = rh(y);
-            bar_arrive_id(3 + (n & 1), HB_THREADS);
+            if (q == 0) sy[n & 3][i] = rh(y);
+            bar_arrive_id(3 + (n & 1), N_DONE);
         }
     }
 }
