@@ -366,12 +366,16 @@ int forward_rows(ab_model* m, int B, int T, const int32_t* tokens, void* const* 
         const int i = li;
         const int gi = g0 + li;
         const ab_layer& L = m->layers[i];
-        AB_TRY(ln_rows(ws.x, (const __half*)L.ln1_w, (const __half*)L.ln1_b, M, D, 1, 0, ws.xn, st));
         MixParams mp = {};
         mp.xn = ws.xn; mp.x_prev = (__half*)state[3 * i]; mp.B = B; mp.T = T; mp.D = D; mp.n_mix = 6;
         const void* mv[6] = {L.x_r, L.x_k, L.x_v, L.x_w, L.x_a, L.x_g};
         for (int j = 0; j < 6; ++j) { mp.mix[j] = (const __half*)mv[j]; mp.out[j] = ws.mix[j]; }
-        AB_TRY(mix_rows(mp, st));
+        if (ln_mix_rows_ok(mp)) {
+            AB_TRY(ln_mix_rows(ws.x, (const __half*)L.ln1_w, (const __half*)L.ln1_b, mp, st));
+        } else {
+            AB_TRY(ln_rows(ws.x, (const __half*)L.ln1_w, (const __half*)L.ln1_b, M, D, 1, 0, ws.xn, st));
+            AB_TRY(mix_rows(mp, st));
+        }
         void* sc = ws.gemm_scratch;
         {   // r, k, v and the adapter down-projections: one grouped launch
             GemmOp ops[8];
@@ -394,11 +398,15 @@ int forward_rows(ab_model* m, int B, int T, const int32_t* tokens, void* const* 
         AB_TRY(head_launch(h, st));
         AB_TRY(gemm_launch(L.output, M, ws.att, ws.x, EPI_RESID, ws.x, sc, st));
 
-        AB_TRY(ln_rows(ws.x, (const __half*)L.ln2_w, (const __half*)L.ln2_b, M, D, 1, 0, ws.xn, st));
         MixParams fp = {};
         fp.xn = ws.xn; fp.x_prev = (__half*)state[3 * i + 2]; fp.B = B; fp.T = T; fp.D = D; fp.n_mix = 1;
         fp.mix[0] = (const __half*)L.ffn_x_k; fp.out[0] = ws.mix[0];
-        AB_TRY(mix_rows(fp, st));
+        if (ln_mix_rows_ok(fp)) {
+            AB_TRY(ln_mix_rows(ws.x, (const __half*)L.ln2_w, (const __half*)L.ln2_b, fp, st));
+        } else {
+            AB_TRY(ln_rows(ws.x, (const __half*)L.ln2_w, (const __half*)L.ln2_b, M, D, 1, 0, ws.xn, st));
+            AB_TRY(mix_rows(fp, st));
+        }
         AB_TRY(gemm_launch(L.ffn_key, M, ws.mix[0], ws.kf, EPI_RELU2, nullptr, sc, st));
         AB_TRY(gemm_launch(L.ffn_value, M, ws.kf, ws.x, EPI_RESID, ws.x, sc, st));
     }

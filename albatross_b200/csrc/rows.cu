@@ -66,6 +66,82 @@ __global__ void __launch_bounds__(RT) mix_rows_kernel(MixParams p) {
     }
 }
 
+// T == 1: layer norm and token-shift lerps of one row in one pass; the row stays in registers (16-byte loads and
+// stores), the normalised row becomes the new token-shift state. Same rounding points as ln_rows + mix_rows.
+constexpr int LM_MAXV = 4;   // 16-byte chunks per thread: D <= 8 * RT * LM_MAXV
+__global__ void __launch_bounds__(RT) ln_mix_rows_kernel(const __half* __restrict__ x, const __half* __restrict__ w,
+                                                         const __half* __restrict__ b, const __grid_constant__ MixParams p) {
+    __shared__ float red[RT / 32];
+    const size_t m = blockIdx.x;
+    const int nv = p.D / 8;
+    const uint4* xr = reinterpret_cast<const uint4*>(x + m * p.D);
+    uint4 raw[LM_MAXV], prv[LM_MAXV];
+    float s = 0.f;
+#pragma unroll
+    for (int v = 0; v < LM_MAXV; ++v) {
+        const int i = threadIdx.x + v * RT;
+        if (i < nv) {
+            raw[v] = xr[i];
+            prv[v] = reinterpret_cast<const uint4*>(p.x_prev + m * p.D)[i];
+            const __half2* h = reinterpret_cast<const __half2*>(&raw[v]);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { const float2 f = __half22float2(h[e]); s += f.x + f.y; }
+        }
+    }
+    const float mean = block_sum_rt(s, red) / (float)p.D;
+    float q = 0.f;
+#pragma unroll
+    for (int v = 0; v < LM_MAXV; ++v) {
+        if (threadIdx.x + v * RT < nv) {
+            const __half2* h = reinterpret_cast<const __half2*>(&raw[v]);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 f = __half22float2(h[e]);
+                q += (f.x - mean) * (f.x - mean) + (f.y - mean) * (f.y - mean);
+            }
+        }
+    }
+    const float rstd = rsqrtf(block_sum_rt(q, red) / (float)p.D + 1e-5f);
+#pragma unroll
+    for (int v = 0; v < LM_MAXV; ++v) {
+        const int i = threadIdx.x + v * RT;
+        if (i < nv) {
+            const uint4 wv = reinterpret_cast<const uint4*>(w)[i], bv = reinterpret_cast<const uint4*>(b)[i];
+            const __half2* h = reinterpret_cast<const __half2*>(&raw[v]);
+            const __half2* wh = reinterpret_cast<const __half2*>(&wv);
+            const __half2* bh = reinterpret_cast<const __half2*>(&bv);
+            const __half2* ph = reinterpret_cast<const __half2*>(&prv[v]);
+            uint4 xn;
+            __half2* xh = reinterpret_cast<__half2*>(&xn);
+            float c[8], d[8];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 f = __half22float2(h[e]), wf = __half22float2(wh[e]), bf = __half22float2(bh[e]);
+                xh[e] = __floats2half2_rn((f.x - mean) * rstd * wf.x + bf.x, (f.y - mean) * rstd * wf.y + bf.y);
+                const float2 cf = __half22float2(xh[e]), pf = __half22float2(ph[e]);
+                c[2 * e] = cf.x; c[2 * e + 1] = cf.y;
+                d[2 * e] = rh(pf.x - cf.x); d[2 * e + 1] = rh(pf.y - cf.y);
+            }
+            reinterpret_cast<uint4*>(p.x_prev + m * p.D)[i] = xn;
+#pragma unroll
+            for (int j = 0; j < 6; ++j) {
+                if (j < p.n_mix) {
+                    const uint4 mv = reinterpret_cast<const uint4*>(p.mix[j])[i];
+                    const __half2* mh = reinterpret_cast<const __half2*>(&mv);
+                    uint4 o;
+                    __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float2 mf = __half22float2(mh[e]);
+                        oh[e] = __floats2half2_rn(c[2 * e] + rh(d[2 * e] * mf.x), c[2 * e + 1] + rh(d[2 * e + 1] * mf.y));
+                    }
+                    reinterpret_cast<uint4*>(p.out[j] + m * p.D)[i] = o;
+                }
+            }
+        }
+    }
+}
+
 // x_prev[b] = xn[b, T-1]
 __global__ void __launch_bounds__(RT) last_rows_kernel(const __half* __restrict__ xn, int T, int D, __half* __restrict__ x_prev) {
     const size_t b = blockIdx.x;
@@ -86,6 +162,13 @@ int ln_rows(const __half* x, const __half* w, const __half* b, int rows, int D, 
             cudaStream_t s) {
     AB_CHECK_ARG(x && w && b && out && rows > 0, "ln_rows: bad argument");
     ln_rows_kernel<<<rows, RT, 0, s>>>(x, w, b, D, stride, offset, out);
+    AB_CUDA(cudaGetLastError());
+    return OK;
+}
+bool ln_mix_rows_ok(const MixParams& p) { return p.T == 1 && p.D % 8 == 0 && p.D <= 8 * RT * LM_MAXV; }
+int ln_mix_rows(const __half* x, const __half* w, const __half* b, const MixParams& p, cudaStream_t s) {
+    AB_CHECK_ARG(x && w && b && p.x_prev && p.n_mix >= 1 && p.n_mix <= 6 && p.B > 0 && ln_mix_rows_ok(p), "ln_mix_rows: bad argument");
+    ln_mix_rows_kernel<<<p.B, RT, 0, s>>>(x, w, b, p);
     AB_CUDA(cudaGetLastError());
     return OK;
 }
