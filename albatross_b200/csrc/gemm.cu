@@ -681,3 +681,58 @@ int dequant_launch(const ab_mat& m, float* out, cudaStream_t stream) {
 }
 
 }  // namespace ab
+
+// ---------------------------------------------------------------------------------------------
+// Batched product with built-in scratch: the split-K counters and partial tiles live in a fixed array of this
+// module instead of a caller-supplied buffer, so the call neither takes nor makes a device allocation.
+// ---------------------------------------------------------------------------------------------
+namespace ab {
+namespace {
+
+static __device__ __align__(256) unsigned char g_static_scratch[AB_GEMM_STATIC_SCRATCH_BYTES];
+
+constexpr int STATIC_MAX_DEVICES = 64;
+
+// Address of the array on the current device, looked up once per device; the counters are cleared on `stream`
+// when a device is first used (the kernels need them at zero and leave them at zero).
+int static_scratch(void** out, cudaStream_t stream) {
+    static void* ptrs[STATIC_MAX_DEVICES] = {};
+    int dev = 0;
+    AB_CUDA(cudaGetDevice(&dev));
+    AB_CHECK_ARG(dev >= 0 && dev < STATIC_MAX_DEVICES, "ab_gemm_static: device index %d not supported", dev);
+    if (!ptrs[dev]) {
+        void* ptr = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+        if (e != cudaSuccess || !ptr) {
+            set_error("ab_gemm_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+            return ERR_CUDA;
+        }
+        AB_CUDA(cudaMemsetAsync(ptr, 0, (size_t)G_COUNTERS * 4, stream));
+        ptrs[dev] = ptr;
+    }
+    *out = ptrs[dev];
+    return OK;
+}
+
+}  // namespace
+}  // namespace ab
+
+extern "C" int ab_gemm_static(const ab_mat* m, int rows, const void* x, void* y, int epi, const void* resid, void* stream) {
+    using namespace ab;
+    AB_CHECK_ARG(m && x && y, "ab_gemm_static: null pointer");
+    AB_CHECK_ARG(epi >= EPI_NONE && epi <= EPI_RESID && (epi != EPI_RESID || resid), "ab_gemm_static: bad epilogue");
+    AB_CHECK_ARG(rows > 0, "ab_gemm_static: rows must be positive");
+    int st = check_mat(*m, "ab_gemm_static");
+    if (st != OK) return st;
+    const size_t need = gemm_scratch_bytes(*m, rows);
+    if (need > (size_t)AB_GEMM_STATIC_SCRATCH_BYTES) {
+        set_error("ab_gemm_static: this product needs %zu bytes of split-K scratch, the built-in area holds %zu "
+                  "(n_out=%d k=%d rows=%d); use ab_gemm with a caller-supplied scratch buffer",
+                  need, (size_t)AB_GEMM_STATIC_SCRATCH_BYTES, m->n_out, m->k, rows);
+        return ERR_TOO_LARGE;
+    }
+    void* scratch = nullptr;
+    st = static_scratch(&scratch, (cudaStream_t)stream);
+    if (st != OK) return st;
+    return gemm_launch(*m, rows, (const __half*)x, (__half*)y, epi, (const __half*)resid, scratch, (cudaStream_t)stream);
+}

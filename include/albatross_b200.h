@@ -101,6 +101,22 @@ size_t ab_gemm_scratch_bytes(const ab_mat* m, int rows);
 int ab_gemm(const ab_mat* m, int rows, const void* x, void* y, int epi, const void* resid, void* scratch,
             void* stream);
 
+/* ab_gemm without a scratch argument (no counterpart in the reference). The split-K counters and partial tiles
+ * live in a fixed AB_GEMM_STATIC_SCRATCH_BYTES array inside the library, so the call neither receives nor makes
+ * any device allocation. It is for callers that have no device memory to hand over and must not create any at
+ * this point: an operator running under a host framework that owns the whole device heap through its own caching
+ * allocator (a raw allocation there can fail although the pool has room, and allocating or freeing may synchronise
+ * the device in the middle of a decode step), or a code path whose buffers are all planned ahead of time.
+ * Same results as ab_gemm. Products that need more scratch than the array holds (ab_gemm_scratch_bytes(m, rows) >
+ * AB_GEMM_STATIC_SCRATCH_BYTES: long-k products with few output rows at large batch) fail with AB_ERR_TOO_LARGE
+ * and a message; use ab_gemm for those. The first call on each device looks the array up (cudaGetSymbolAddress,
+ * a host-side call, not a stream operation) and clears its counters on `stream`: make that first call during
+ * set-up, before any stream capture begins. There is ONE array per device: two ab_gemm_static calls that can
+ * overlap in time (different streams, or different host threads on different streams) race on it; keep them
+ * on one stream or order them with events. */
+#define AB_GEMM_STATIC_SCRATCH_BYTES (8u * 1024u * 1024u)
+int ab_gemm_static(const ab_mat* m, int rows, const void* x, void* y, int epi, const void* resid, void* stream);
+
 /* ---- de-quantisation dump (parity checks) ---------------------------------------------------
  * Writes the kernels' in-register de-quantised weights as fp32 [n_out,k] (tensor/row/column scales applied). */
 int ab_dequant(const ab_mat* m, float* out, void* stream);
