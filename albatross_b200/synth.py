@@ -5,7 +5,9 @@ weights that have the shapes and value distributions the reference loader expect
 (reference/rwkv7.py:79-96 lists every key it reads; benchmark.py:26-40 the model sizes).
 
 Each tensor is drawn from its own generator seeded by (seed, key), so a tensor's values do not
-depend on the order of generation, on the device, or on which other tensors were requested.
+depend on the order of generation or on which other tensors were requested. CPU and CUDA generators
+are different streams: a checkpoint drawn on the device (the 7.2B benchmark models) is reproducible
+on the device, but is not the checkpoint the same seed gives on the CPU; parity tests draw on the CPU.
 """
 from __future__ import annotations
 
@@ -94,7 +96,7 @@ def tensor_specs(n_layer: int, n_embd: int, vocab: int, ranks) -> Iterator[Tuple
 def make_tensor(seed: int, key: str, shape, dist, device="cpu") -> torch.Tensor:
     kind, p0, p1 = dist
     if device != "cpu" and torch.device(device).type == "cuda":
-        # Large tensors (7.2B) are drawn on the device: same (seed, key) -> same stream there.
+        # Large tensors (7.2B) are drawn on the device: same (seed, key) -> same values on every CUDA run.
         g = torch.Generator(device=device)
         g.manual_seed((seed * 1000003 + zlib.crc32(key.encode())) & 0x7FFFFFFFFFFF)
         t = torch.empty(shape, dtype=torch.float32, device=device)

@@ -60,7 +60,9 @@ def run_reference(ref_mod, raw, args, dtype, toks):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py <directory that contains the reference checkout as 'reference'>")
+    ref_root = sys.argv[1]
     sys.path.insert(0, ref_root)
     real_load = torch.load
     torch.load = lambda f, *a, **k: real_load(f, map_location="cpu")
