@@ -380,12 +380,12 @@ int forward_rows(ab_model* m, int B, int T, const int32_t* tokens, void* const* 
         {   // r, k, v and the adapter down-projections: one grouped launch
             GemmOp ops[8];
             const int n = time_mix_down_ops(L, gi, ws, ops);
-            AB_TRY(gemm_group_launch(ops, n, M, sc, st));
+            AB_TRY(gemm_group_launch(ops, n, M, sc, st, m->use_pdl));
         }
         {   // adapter up-projections
             GemmOp ops[8];
             const int n = time_mix_up_ops(L, gi, ws, ops);
-            AB_TRY(gemm_group_launch(ops, n, M, sc, st));
+            AB_TRY(gemm_group_launch(ops, n, M, sc, st, m->use_pdl));
         }
         HeadParams h = {};
         h.B = B; h.T = T; h.D = D; h.H = H; h.layer0 = (gi == 0);
@@ -394,9 +394,9 @@ int forward_rows(ab_model* m, int B, int T, const int32_t* tokens, void* const* 
         h.w0 = (const __half*)L.w0; h.a0 = (const __half*)L.a0; h.v0 = (const __half*)L.v0;
         h.k_k = (const __half*)L.k_k; h.k_a = (const __half*)L.k_a; h.r_k = (const __half*)L.r_k;
         h.lnx_w = (const __half*)L.lnx_w; h.lnx_b = (const __half*)L.lnx_b;
-        h.out = ws.att;
+        h.out = ws.att; h.use_pdl = m->use_pdl;
         AB_TRY(head_launch(h, st));
-        AB_TRY(gemm_launch(L.output, M, ws.att, ws.x, EPI_RESID, ws.x, sc, st));
+        AB_TRY(gemm_launch(L.output, M, ws.att, ws.x, EPI_RESID, ws.x, sc, st, m->use_pdl));
 
         MixParams fp = {};
         fp.xn = ws.xn; fp.x_prev = (__half*)state[3 * i + 2]; fp.B = B; fp.T = T; fp.D = D; fp.n_mix = 1;
@@ -407,8 +407,8 @@ int forward_rows(ab_model* m, int B, int T, const int32_t* tokens, void* const* 
             AB_TRY(ln_rows(ws.x, (const __half*)L.ln2_w, (const __half*)L.ln2_b, M, D, 1, 0, ws.xn, st));
             AB_TRY(mix_rows(fp, st));
         }
-        AB_TRY(gemm_launch(L.ffn_key, M, ws.mix[0], ws.kf, EPI_RELU2, nullptr, sc, st));
-        AB_TRY(gemm_launch(L.ffn_value, M, ws.kf, ws.x, EPI_RESID, ws.x, sc, st));
+        AB_TRY(gemm_launch(L.ffn_key, M, ws.mix[0], ws.kf, EPI_RELU2, nullptr, sc, st, m->use_pdl));
+        AB_TRY(gemm_launch(L.ffn_value, M, ws.kf, ws.x, EPI_RESID, ws.x, sc, st, m->use_pdl));
     }
     if (io && io->x_out) {
         AB_CUDA(cudaMemcpyAsync(io->x_out, ws.x, (size_t)M * D * 2, cudaMemcpyDeviceToDevice, st));
@@ -416,10 +416,10 @@ int forward_rows(ab_model* m, int B, int T, const int32_t* tokens, void* const* 
     }
     if (full_output || T == 1) {
         AB_TRY(ln_rows(ws.x, (const __half*)m->d.lnout_w, (const __half*)m->d.lnout_b, M, D, 1, 0, ws.xn, st));
-        return gemm_launch(m->d.head, M, ws.xn, logits, EPI_NONE, nullptr, ws.gemm_scratch, st);
+        return gemm_launch(m->d.head, M, ws.xn, logits, EPI_NONE, nullptr, ws.gemm_scratch, st, m->use_pdl);
     }
     AB_TRY(ln_rows(ws.x, (const __half*)m->d.lnout_w, (const __half*)m->d.lnout_b, B, D, T, T - 1, ws.xlast, st));
-    return gemm_launch(m->d.head, B, ws.xlast, logits, EPI_NONE, nullptr, ws.gemm_scratch, st);
+    return gemm_launch(m->d.head, B, ws.xlast, logits, EPI_NONE, nullptr, ws.gemm_scratch, st, m->use_pdl);
 }
 
 }  // namespace

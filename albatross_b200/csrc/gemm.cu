@@ -21,6 +21,8 @@
 // Three-stage operand ring, all mbarrier waits bounded (status word on expiry), TMEM freed on every path.
 #include <cuda.h>
 
+#include <type_traits>
+
 #include "gemm.cuh"
 #include "gemv.cuh"
 
@@ -53,6 +55,7 @@ struct GemmProb {
     int ksplit;       // blocks that share one output tile along K
     int tile_base;    // first split-K tile id (counter / partial index)
     long long part_base;   // float offset of its split-K partial sums in the scratch area
+    int tma_out;      // output (and residual) tiles go through shared memory and the TMA unit
 };
 struct GemmGroup {
     GemmProb pr[G_MAX_OPS];
@@ -65,7 +68,9 @@ struct GemmGroup {
     float* partials;
 };
 struct GemmMaps {
-    CUtensorMap m[G_MAX_OPS];
+    CUtensorMap m[G_MAX_OPS];   // activations X
+    CUtensorMap y[G_MAX_OPS];   // outputs Y, boxes of 32 batch rows x 128 features
+    CUtensorMap r[G_MAX_OPS];   // residuals, same boxes
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -77,6 +82,14 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
             smem_u32(dst)),
         "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
         : "memory");
+}
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int y, const void* src) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map), "r"(x), "r"(y),
+                 "r"(smem_u32(src))
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit_and_drain_reads() {
+    asm volatile("cp.async.bulk.commit_group;\n cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
 __device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols)
@@ -222,6 +235,13 @@ __device__ __forceinline__ void raw_dequant(int fmt, int r_local, const unsigned
     }
 }
 
+template <int EPI>
+__device__ __forceinline__ float apply_epi_t(float o) {
+    if (EPI == EPI_TANH) return tanhf(o);
+    if (EPI == EPI_SIGMOID) return sigmoidf_(o);
+    if (EPI == EPI_RELU2) { o = fmaxf(o, 0.f); return o * o; }
+    return o;
+}
 __device__ __forceinline__ float apply_epi(int epi, float o) {
     switch (epi) {
         case EPI_TANH: return tanhf(o);
@@ -234,7 +254,7 @@ __device__ __forceinline__ float apply_epi(int epi, float o) {
 __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ GemmMaps maps,
                                                         const __grid_constant__ GemmGroup g) {
     extern __shared__ __align__(1024) unsigned char gsm[];
-    __shared__ uint64_t full[G_STAGES], empty[G_STAGES], accum_bar;
+    __shared__ uint64_t full[G_STAGES], empty[G_STAGES], accum_bar, resid_bar;
     __shared__ uint32_t tmem_base_s;
     __shared__ int s_failed, s_last;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -269,6 +289,7 @@ __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ 
             mbar_init(&empty[s], 1);
         }
         mbar_init(&accum_bar, 1);
+        mbar_init(&resid_bar, 1);
         fence_mbar_init();
         s_failed = 0;
         s_last = 0;
@@ -278,6 +299,9 @@ __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ 
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_s;
+    // Under programmatic stream serialisation the next grid may start now; like this one it begins with its weight
+    // stream (weights are never written) and waits for its predecessor before it touches activations or outputs.
+    if (tid == 0) pdl_launch_dependents();
 
     // After the first wait that runs out, nobody waits any more: the block drains in bounded time.
     auto wait_ok = [&](uint64_t* bar, uint32_t parity) {
@@ -320,6 +344,7 @@ __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ 
             };
             uint4 nxt[8];
             if (grp < n_ksteps) fetch(grp, nxt);
+            pdl_wait();
             for (int ks = grp; ks < n_ksteps; ks += G_NG) {
                 uint4 cur[8];
 #pragma unroll
@@ -337,6 +362,7 @@ __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ 
                 if (ks < n_ksteps) raw_issue(pb.w, row, r_local, kstep_of(ks), ring + (j % depth) * slot_bytes);
                 cp_async_commit();
             }
+            pdl_wait();
             int j = 0;
             for (int ks = grp; ks < n_ksteps; ks += G_NG, ++j) {
                 const int ja = j + depth - 1, ks_a = grp + ja * G_NG;
@@ -393,15 +419,64 @@ __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ 
             }
         };
 
+        // Preferred way out: the finished tile is laid out in shared memory as [batch row][128 features] fp16 (the
+        // operand stages are idle by now) and leaves through the TMA unit in full lines; the unit clips rows and
+        // features beyond the matrix. A residual tile comes in the same way and is updated in place.
+        __half* stg = reinterpret_cast<__half*>(smA);
+        const bool staged = pb.tma_out != 0;
+        auto stage32 = [&](int ci, const float* v) {
+            __half* t = stg + (size_t)ci * 32 * G_BM + r_local;
+            auto body = [&](auto E) {
+                constexpr int EP = decltype(E)::value;
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    if (EP == EPI_RESID) t[i * G_BM] = __hadd(t[i * G_BM], __float2half_rn(v[i] * scale));
+                    else t[i * G_BM] = __float2half_rn(apply_epi_t<EP>(rh(v[i] * scale)));
+                }
+            };
+            switch (epi) {
+                case EPI_TANH: body(std::integral_constant<int, EPI_TANH>()); break;
+                case EPI_SIGMOID: body(std::integral_constant<int, EPI_SIGMOID>()); break;
+                case EPI_RELU2: body(std::integral_constant<int, EPI_RELU2>()); break;
+                case EPI_RESID: body(std::integral_constant<int, EPI_RESID>()); break;
+                default: body(std::integral_constant<int, EPI_NONE>()); break;
+            }
+        };
+        auto emit = [&](int ci, const float* v) {
+            if (staged) stage32(ci, v);
+            else emit32(ci, v);
+        };
+        // residual tiles on their way in (only blocks that will write the output need them)
+        auto fetch_resid = [&]() {
+            if (!(staged && epi == EPI_RESID)) return;
+            if (tid == 0) {
+                mbar_expect_tx(&resid_bar, (uint32_t)(n_chunks * 32 * G_BM * 2));
+                for (int ci = 0; ci < n_chunks; ++ci)
+                    tma_load_2d(stg + (size_t)ci * 32 * G_BM, &maps.r[pi], m0, n0 + ci * 32, &resid_bar);
+            }
+            wait_ok(&resid_bar, 0);
+        };
+        auto flush = [&]() {
+            if (!staged) return;
+            fence_proxy_async();
+            epi_sync();
+            if (tid == 0) {
+                for (int ci = 0; ci < n_chunks; ++ci) tma_store_2d(&maps.y[pi], m0, n0 + ci * 32, stg + (size_t)ci * 32 * G_BM);
+                bulk_commit_and_drain_reads();   // the shared memory must outlive the unit's reads
+            }
+        };
+
         if (pb.ksplit == 1) {
+            fetch_resid();
             for (int ci = grp; ci < n_chunks; ci += G_NG) {
                 uint32_t raw[32];
                 tc_ld32(lane_addr + (uint32_t)(ci * 32), raw);
                 float v[32];
 #pragma unroll
                 for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(raw[i]);
-                emit32(ci, v);
+                emit(ci, v);
             }
+            flush();
         } else {
             // split K: park this block's fp32 tile, the last block to arrive sums all of them in a fixed order
             const int tile = pb.tile_base + m_tile * gridDim.y + blockIdx.y;
@@ -426,6 +501,7 @@ __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ 
             }
             epi_sync();
             if (s_last) {
+                fetch_resid();
                 for (int ci = grp; ci < n_chunks; ci += G_NG) {
                     float v[32];
 #pragma unroll
@@ -436,8 +512,9 @@ __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ 
                         for (int i = 0; i < 32; ++i)
                             if (ci * 32 + i < g.n_tile) v[i] += __ldcg(src + (size_t)(ci * 32 + i) * G_BM + r_local);
                     }
-                    emit32(ci, v);
+                    emit(ci, v);
                 }
+                flush();
             }
         }
         tc_fence_before();
@@ -445,6 +522,7 @@ __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ 
         // ===== activation tiles by TMA =====
         if (lane == 0) {
             const CUtensorMap* map = &maps.m[pi];
+            pdl_wait();
             for (int ks = 0; ks < n_ksteps; ++ks) {
                 const int s = ks % G_STAGES, f = ks / G_STAGES;
                 if (f > 0) wait_ok(&empty[s], (f - 1) & 1);
@@ -602,7 +680,7 @@ size_t gemm_scratch_bytes(const ab_mat& m, int rows) {
     return gemm_group_scratch_bytes(&op, 1, rows);
 }
 
-int gemm_group_launch(const GemmOp* ops, int n, int rows, void* scratch, cudaStream_t stream) {
+int gemm_group_launch(const GemmOp* ops, int n, int rows, void* scratch, cudaStream_t stream, bool pdl) {
     AB_CHECK_ARG(ops && n >= 1 && n <= G_MAX_OPS && rows > 0, "gemm: bad group (n=%d rows=%d)", n, rows);
     const GroupShape gs = group_shape(ops, n, rows);
     AB_CHECK_ARG(gs.n_split_tiles <= G_COUNTERS, "gemm: too many split-K tiles");
@@ -649,8 +727,29 @@ int gemm_group_launch(const GemmOp* ops, int n, int rows, void* scratch, cudaStr
             set_error("gemm: cuTensorMapEncodeTiled failed with %d (rows=%d k=%d)", (int)cr, rows, m.k);
             return ERR_CUDA;
         }
+        // output / residual tiles through the TMA unit when the row pitch and the pointers allow it
+        pb.tma_out = (m.n_out % 8 == 0 && m.n_out >= G_BM && ((uintptr_t)op.y & 15) == 0 &&
+                      (op.epi != EPI_RESID || ((uintptr_t)op.resid & 15) == 0)) ? 1 : 0;
+        maps.y[i] = maps.m[i];
+        maps.r[i] = maps.m[i];
+        if (pb.tma_out) {
+            const cuuint64_t odim[2] = {(cuuint64_t)m.n_out, (cuuint64_t)rows};
+            const cuuint64_t ostride[1] = {(cuuint64_t)m.n_out * 2};
+            const cuuint32_t obox[2] = {(cuuint32_t)G_BM, 32};
+            CUresult c2 = encode(&maps.y[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, op.y, odim, ostride, obox, estr,
+                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (c2 == CUDA_SUCCESS && op.epi == EPI_RESID)
+                c2 = encode(&maps.r[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(op.resid), odim, ostride, obox,
+                            estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (c2 != CUDA_SUCCESS) {
+                set_error("gemm: cuTensorMapEncodeTiled (output) failed with %d (rows=%d n_out=%d)", (int)c2, rows, m.n_out);
+                return ERR_CUDA;
+            }
+        }
     }
-    for (int i = n; i < G_MAX_OPS; ++i) maps.m[i] = maps.m[0];
+    for (int i = n; i < G_MAX_OPS; ++i) { maps.m[i] = maps.m[0]; maps.y[i] = maps.m[0]; maps.r[i] = maps.m[0]; }
 
     const size_t smem = 1024 + (size_t)G_STAGES * (G_A_BYTES + (size_t)gs.n_tile * 128) + G_RAW_BYTES;
     static size_t smem_set = 0;
@@ -658,17 +757,25 @@ int gemm_group_launch(const GemmOp* ops, int n, int rows, void* scratch, cudaStr
         AB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         smem_set = smem;
     }
-    const dim3 grid(gs.grid_x, gs.n_tiles_y);
-    gemm_tc_kernel<<<grid, GT, smem, stream>>>(maps, g);
-    AB_CUDA(cudaGetLastError());
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(gs.grid_x, gs.n_tiles_y);
+    cfg.blockDim = dim3(GT);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    AB_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_kernel, maps, g));
     return OK;
 }
 
 int gemm_launch(const ab_mat& m, int rows, const __half* x, __half* y, int epi, const __half* resid, void* scratch,
-                cudaStream_t stream) {
+                cudaStream_t stream, bool pdl) {
     GemmOp op = {};
     op.w = m; op.x = x; op.y = y; op.epi = epi; op.resid = resid;
-    return gemm_group_launch(&op, 1, rows, scratch, stream);
+    return gemm_group_launch(&op, 1, rows, scratch, stream, pdl);
 }
 
 int dequant_launch(const ab_mat& m, float* out, cudaStream_t stream) {
