@@ -73,6 +73,9 @@ struct Workspace {
     size_t total;
 };
 
+int time_mix_down_ops(const ab_layer& L, int layer, const Workspace& ws, GemmOp* ops);
+int time_mix_up_ops(const ab_layer& L, int layer, const Workspace& ws, GemmOp* ops);
+
 Workspace carve(const ab_model* m, int B, int T, unsigned char* base) {
     const size_t M = (size_t)B * T, D = m->d.n_embd, F = 4 * D;
     const ab_layer& l0 = m->layers[0];
@@ -100,8 +103,13 @@ Workspace carve(const ab_model* m, int B, int T, unsigned char* base) {
             need = std::max(need, gemm_scratch_bytes(l.output, (int)M));
             need = std::max(need, gemm_scratch_bytes(l.ffn_key, (int)M));
             need = std::max(need, gemm_scratch_bytes(l.ffn_value, (int)M));
-            need = std::max(need, gemm_scratch_bytes(l.receptance, (int)M) * 8);   // grouped launches never split more
-            break;                                                                   // all blocks have the same shapes
+        }
+        for (size_t i = 0; i < m->layers.size(); ++i) {   // the two grouped launches of every block
+            GemmOp ops[8];
+            int n = time_mix_down_ops(m->layers[i], (int)i + m->layer_offset, w, ops);
+            need = std::max(need, gemm_group_scratch_bytes(ops, n, (int)M));
+            n = time_mix_up_ops(m->layers[i], (int)i + m->layer_offset, w, ops);
+            need = std::max(need, gemm_group_scratch_bytes(ops, n, (int)M));
         }
         off += al(need);
     }

@@ -646,13 +646,24 @@ GroupShape group_shape(const GemmOp* ops, int n, int rows) {
     gs.tmem_cols = 32;
     while (gs.tmem_cols < gs.n_tile) gs.tmem_cols *= 2;
     gs.n_tiles_y = (rows + gs.n_tile - 1) / gs.n_tile;
-    int base_ctas = 0;
-    for (int i = 0; i < n; ++i) base_ctas += (ops[i].w.n_out + G_BM - 1) / G_BM * gs.n_tiles_y;
+    int base_ctas = 0, slow_ctas = 0;
+    for (int i = 0; i < n; ++i) {
+        const int c = (ops[i].w.n_out + G_BM - 1) / G_BM * gs.n_tiles_y;
+        base_ctas += c;
+        if (ops[i].w.fmt == FMT_F16 && ops[i].w.k >= 32 * G_BK) slow_ctas += c;
+    }
     for (int i = 0; i < n; ++i) {
         const int ksteps = (ops[i].w.k + G_BK - 1) / G_BK;
         int ks = 1;
         if (base_ctas < 100 && ksteps >= 32) {   // too few tiles to fill the GPU: split the long K loops
             ks = 148 / base_ctas;
+            if (ks > 8) ks = 8;
+            if (ks > ksteps / 8) ks = ksteps / 8;
+            if (ks < 1) ks = 1;
+        } else if (base_ctas < 148 && slow_ctas > 0 && ops[i].w.fmt == FMT_F16 && ksteps >= 32) {
+            // A nearly full grid whose fp16 products (twice to four times the bytes per k-step of the quantised
+            // ones, fetched only two k-steps ahead) would finish last: the idle SMs take slices of their K loops.
+            ks = 1 + (148 - base_ctas) / slow_ctas;
             if (ks > 8) ks = 8;
             if (ks > ksteps / 8) ks = ksteps / 8;
             if (ks < 1) ks = 1;

@@ -62,7 +62,7 @@ __global__ void __launch_bounds__(HT) wkv7_kernel(int T, int C, int H, float* __
 // Fused kernel
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(HT) head_fused_kernel(const __grid_constant__ HeadParams p) {
-    extern __shared__ __align__(16) unsigned char dsm[];
+    extern __shared__ __align__(128) unsigned char dsm[];
     __shared__ HeadShared sh;
     float (*up)[64] = sh.up;
     const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;
