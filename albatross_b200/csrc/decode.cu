@@ -102,7 +102,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) decode_kernel(const DecodePro
                 // the head of this block's share of the next phase starts moving HBM -> L2 now
                 const GemvParams& q = phs[j & 3].g;
                 const BlockPlan& np_ = plans[j & 3];
-                int budget = 256 * 1024;
+                int budget = prog->l2_prefetch_bytes;
                 for (int s = 0; s < q.nseg && budget > 0; ++s) {
                     const SegPlan& sp = np_.sp[s];
                     if (sp.n_groups <= 0) continue;
@@ -113,8 +113,9 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) decode_kernel(const DecodePro
                     budget -= bytes;
                 }
             }
-            gemv_consume(ph.g, plans[i & 3], m, tid, bid, i, pre_phase, j >= 0 ? &phs[j & 3].g : nullptr,
-                         j >= 0 ? &plans[j & 3] : nullptr, j,
+            const bool pre = j >= 0 && prog->smem_prefetch;
+            gemv_consume(ph.g, plans[i & 3], m, tid, bid, i, pre_phase, pre ? &phs[j & 3].g : nullptr,
+                         pre ? &plans[j & 3] : nullptr, j,
                          (prog->timeline && bid == 0) ? prog->timeline + 2 * n_phases + 4 * i : nullptr);
         } else {
             const HeadParams& hp = ph.h;

@@ -59,6 +59,9 @@ struct ab_model {
     int prog_xq_bytes = 0;
     int debug_sync = 0;  // synchronise after every launch and name the one that failed
     int timeline = 0;    // persistent decode kernel records per-phase timestamps
+    int l2_prefetch_kb = 0;   // persistent decode kernel: L2 prefetch of the next phase, per block
+    int smem_prefetch = 0;
+    int merge_ups = 0;   // persistent decode kernel: block h computes the adapter outputs of head h and runs it without a grid barrier
 };
 
 namespace {
@@ -219,6 +222,8 @@ int build_decode_program(ab_model* m, const int32_t* token, void* const* state, 
     prog->Kn = D;
     prog->xq_bytes = 0;
     prog->first_gemv = 0;
+    prog->l2_prefetch_bytes = m->l2_prefetch_kb * 1024;
+    prog->smem_prefetch = m->smem_prefetch;
     prog->barrier = const_cast<unsigned*>(&dev_addr->barrier_word);
     prog->timeline = m->timeline ? (unsigned long long*)((unsigned char*)dev_addr +
                                                           decode_timeline_offset(n_phases, m->n_sm)) : nullptr;
@@ -268,7 +273,7 @@ int build_decode_program(ab_model* m, const int32_t* token, void* const* state, 
             up(Ly.g2t, ws.hg, ws.g);
             p.nseg = k;
             AB_TRY(gemv_phase(p));
-            if (false && H <= m->n_sm) {   // measured slower than the all-block phase (short rows): block h computes the 64 channels of head h, then runs head h without a grid barrier
+            if (m->merge_ups && H <= m->n_sm) {   // measured slower than the all-block phase (short rows): block h computes the 64 channels of head h, then runs head h without a grid barrier
                 prog->phases[n - 1].no_barrier = 1;
                 prog->phases[n - 1].rows_per_block = HEAD;
             }
@@ -545,6 +550,9 @@ int ab_model_set_option(ab_model* m, const char* name, int value) {
     else if (!strcmp(name, "pdl")) m->use_pdl = value != 0;
     else if (!strcmp(name, "debug_sync")) m->debug_sync = value != 0;
     else if (!strcmp(name, "timeline")) m->timeline = value != 0;
+    else if (!strcmp(name, "l2_prefetch_kb")) m->l2_prefetch_kb = value < 0 ? 0 : value;
+    else if (!strcmp(name, "smem_prefetch")) m->smem_prefetch = value != 0;
+    else if (!strcmp(name, "merge_ups")) m->merge_ups = value != 0;
     else if (!strcmp(name, "layer_offset")) { AB_CHECK_ARG(value >= 0, "layer_offset must be >= 0"); m->layer_offset = value; }
     else { set_error("unknown option %s", name); return ERR_BAD_ARG; }
     return OK;

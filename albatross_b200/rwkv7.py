@@ -392,6 +392,22 @@ class RWKV_x070:
         return logits
 
     # ---- bookkeeping for benchmarks ---------------------------------------------------------
+    def packed_matrices(self, suffix: str) -> List[PackedMatrix]:
+        """The packed matrices whose checkpoint key ends in `suffix`, in block order (e.g. "ffn.key.weight")."""
+        keys = sorted((k for k, v in self.z.items() if k.endswith(suffix) and isinstance(v, PackedMatrix)),
+                      key=lambda k: int(k.split(".")[1]) if k.startswith("blocks.") else -1)
+        return [self.z[k] for k in keys]
+
+    def matrix_params(self) -> int:
+        """Multiply-accumulates per sequence and step: elements of every matrix a decode step multiplies by."""
+        n = 0
+        for k, v in self.z.items():
+            if isinstance(v, PackedMatrix):
+                n += v.n_out * v.k
+            elif k.split(".")[-1] in ("w1", "w2", "a1", "a2", "v1", "v2", "g1", "g2") and not k.startswith("blocks.0.att.v"):
+                n += v.numel()
+        return n
+
     def weight_bytes(self, include_emb: bool = False) -> int:
         """Bytes a decode step streams: every tensor except the embedding table (cf. benchmark.py:47-52)."""
         n = 0

@@ -24,6 +24,9 @@ CONFIGS = {
     "tiny": (2, 256, 512, (32, 32, 16, 48)),
     "0.1b": (12, 768, 65536, (64, 64, 32, 128)),
     "7.2b": (32, 4096, 65536, (128, 128, 96, 480)),
+    # the 7.2B block shapes with fewer blocks: small enough on the device for a profiler capture
+    "7.2b-l4": (4, 4096, 65536, (128, 128, 96, 480)),
+    "7.2b-l2": (2, 4096, 65536, (128, 128, 96, 480)),
 }
 
 

@@ -88,6 +88,47 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+# DRAM bytes (read + write) of ONE launch from the profiler captures summarised under profiles/ (taken on a model
+# with the same block shapes and fewer blocks; both kernels' traffic is proportional to the blocks processed).
+TRAFFIC = {
+    # kernel: (bytes per block, bytes independent of the block count)
+}
+
+
+def traffic_per_launch(kernel: str, n_layer: int):
+    t = TRAFFIC.get(kernel)
+    return None if t is None else t[0] * n_layer + t[1]
+
+
+def time_gemm_alone(model, B: int, dev: int, steps: int) -> dict:
+    """CUDA-event time of ab_gemm on the channel-mix key matrices of the model, one block after the other
+    (32 different matrices: 1.2 GB of NVFP4, so every launch streams its weights from HBM)."""
+    import ctypes as C
+    from albatross_b200 import _lib
+    mats = model.packed_matrices("ffn.key.weight")
+    n_out, k = mats[0].n_out, mats[0].k
+    cm = [m.as_mat() for m in mats]
+    x = torch.randn(B, k, device=f"cuda:{dev}").half()
+    y = torch.empty(B, n_out, dtype=torch.float16, device=f"cuda:{dev}")
+    scratch = torch.zeros(_lib.lib.ab_gemm_scratch_bytes(C.byref(cm[0]), B) + 256, dtype=torch.uint8, device=f"cuda:{dev}")
+    st = torch.cuda.current_stream().cuda_stream
+    n = max(steps, 32)
+    call = lambda i: _lib.check(_lib.lib.ab_gemm(C.byref(cm[i % len(cm)]), B, x.data_ptr(), y.data_ptr(), 3, None,
+                                                 scratch.data_ptr(), st))
+    for i in range(len(cm)):
+        call(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(n):
+        call(i)
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / n
+    flops = 2.0 * B * n_out * k
+    return {"us": us, "flops": flops, "tflops": flops / (us * 1e-6) / 1e12, "launches": n}
+
+
 def algorithmic_bytes(model, batch: int) -> dict:
     """Bytes one decode step must move: every weight once, the kv state read + written, the WKV vectors."""
     L, D = model.n_layer, model.n_embd
@@ -116,8 +157,8 @@ def run_ours(a, rank, world, dev):
     g = torch.Generator().manual_seed(1000 + rank)
     n_tok = a.warmup + a.steps + 8
     toks = torch.randint(0, V, (n_tok, B), generator=g)
-    if B > 1:      # gather + per block (2 LN, 2 lerp, 13 matrix products (11 in block 0), WKV) + final LN + head
-        launches_per_step = 1 + 18 * args.n_layer - 2 + 2
+    if B > 1:      # gather + per block (2 LN+lerp, 2 grouped + 3 single matrix products, WKV) + final LN + head
+        launches_per_step = 1 + 8 * args.n_layer + 2
     else:
         launches_per_step = 1 if model.decode_mode == "persistent" else 5 * args.n_layer + 1
 
@@ -150,6 +191,8 @@ def run_ours(a, rank, world, dev):
     for i in range(a.warmup):
         e2e_step(i)
     sync_all()
+    sampler = ClockSampler(dev)     # runs across both timed regions (the GPU is under load from here to the end)
+    sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(a.warmup, a.warmup + a.steps):
@@ -182,8 +225,6 @@ def run_ours(a, rank, world, dev):
     for i in range(a.warmup):
         step_fn(i)
     sync_all()
-    sampler = ClockSampler(dev)
-    sampler.start()
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(a.steps + 1)]
     ev[0].record()
     for i in range(a.steps):
@@ -196,18 +237,36 @@ def run_ours(a, rank, world, dev):
     value = world * B * a.steps / (total_ms * 1e-3)
 
     from albatross_b200 import _lib
-    status = _lib.device_status()
     hbm, tf, which = measured_peaks()
     ab = algorithmic_bytes(model, B)
     ms_step = total_ms / a.steps
-    achieved = ab["total"] / (ms_step * 1e-3) / 1e9
+    if B == 1:
+        # One persistent kernel per token (or a graph of matrix-vector launches): the step IS the dominant kernel.
+        achieved = ab["total"] / (ms_step * 1e-3) / 1e9
+        kernel = "decode_kernel (one launch per token)" if model.decode_mode == "persistent" else "gemv_stream_kernel"
+        roofline = {"bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s", "frac": achieved / hbm,
+                    "traffic": traffic_per_launch("decode_kernel", args.n_layer) if model.decode_mode == "persistent" else None,
+                    "peak_source": which, "kernel": kernel, "algorithmic_bytes_per_launch": ab}
+    else:
+        # The tensor-core products take the largest share of the step; the largest of them (channel-mix key,
+        # n_out = 4 * n_embd) is timed alone, live, on the model's own packed weights of every block in turn.
+        gm = time_gemm_alone(model, B, dev, a.steps)
+        flops_step = 2.0 * B * model.matrix_params()
+        roofline = {"bound": "tensor", "achieved": gm["tflops"], "peak": tf, "unit": "TFLOP/s", "frac": gm["tflops"] / tf,
+                    "traffic": traffic_per_launch("gemm_tc_kernel", args.n_layer), "peak_source": which + " (dense bf16 cuBLAS, sustained)",
+                    "kernel": "gemm_tc_kernel on ffn.key [%d x %d] x batch %d" % (4 * args.n_embd, args.n_embd, B),
+                    "algorithmic_flops_per_launch": gm["flops"], "us_per_launch": gm["us"],
+                    "whole_step": {"matrix_tflops": flops_step / (ms_step * 1e-3) / 1e12,
+                                   "hbm_gbs": ab["total"] / (ms_step * 1e-3) / 1e9, "algorithmic_bytes": ab,
+                                   "algorithmic_flops": flops_step}}
+    status = _lib.device_status()
     out = {
         "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
         "ms_per_step": ms_step, "ms_per_step_p10": float(np.percentile(per_step, 10)),
         "ms_per_step_p50": float(np.percentile(per_step, 50)),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "int8 weights (dp4a, exact int32 sums), fp16 activations, fp32 WKV state" if wl["quant"] == "int8"
-        else "nvfp4 weights, fp16 activations, fp32 accumulate and WKV state",
+        else "nvfp4 weights de-quantised to fp16 in registers, fp16 activations, fp32 accumulate and WKV state",
         "data": "synthetic (seeded random weights in the reference checkpoint schema, random token ids)",
         "config": {"workload": a.workload, "model": a.model, "batch_per_gpu": B, "n_layer": args.n_layer,
                    "n_embd": args.n_embd, "vocab": V, "sharding": "independent sequences per GPU, no collective in the step",
@@ -215,12 +274,7 @@ def run_ours(a, rank, world, dev):
         "e2e": {"value": e2e_val, "unit": "tokens/s", "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 2 * B * V,
                 "ms_per_step": e2e_ms / a.steps},
         "gpu_launches": launches_per_step * a.steps,
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s", "frac": achieved / hbm,
-                     "traffic": None, "peak_source": which,
-                     "kernel": "gemv_stream_kernel (%d of the %d launches of a step; achieved = all algorithmic bytes "
-                               "of the step / step time, so the other launches' time is charged to it)" %
-                               (4 * args.n_layer + 1, launches_per_step),
-                     "algorithmic_bytes_per_step": ab},
+        "roofline": roofline,
         "clocks": clocks, "device_status": status,
     }
     return out
