@@ -88,16 +88,16 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-# DRAM bytes (read + write) of ONE launch from the profiler captures summarised under profiles/ (taken on a model
-# with the same block shapes and fewer blocks; both kernels' traffic is proportional to the blocks processed).
-TRAFFIC = {
-    # kernel: (bytes per block, bytes independent of the block count)
-}
+# DRAM bytes (read + write) of ONE launch, from the profiler captures summarised under profiles/.
+# decode_kernel: captured on a model with the same block shapes and 4 blocks (1139.47 MB of traffic for 1136.80 MB of
+# algorithmic bytes); the kernel walks the same phase list per block, so the ratio carries over to 32 blocks.
+# gemm_tc_kernel: captured on the very shape bench times alone (NVFP4 [16384 x 4096], batch 320).
+DECODE_TRAFFIC_PER_ALGORITHMIC_BYTE = 1139.47 / 1136.80
+GEMM_TRAFFIC = {("nvfp4", 16384, 4096, 320): 40.46e6 + 0.11e6}
 
 
-def traffic_per_launch(kernel: str, n_layer: int):
-    t = TRAFFIC.get(kernel)
-    return None if t is None else t[0] * n_layer + t[1]
+def decode_traffic(algorithmic_total: int, quant: str, n_embd: int):
+    return algorithmic_total * DECODE_TRAFFIC_PER_ALGORITHMIC_BYTE if (quant, n_embd) == ("int8", 4096) else None
 
 
 def time_gemm_alone(model, B: int, dev: int, steps: int) -> dict:
@@ -245,7 +245,7 @@ def run_ours(a, rank, world, dev):
         achieved = ab["total"] / (ms_step * 1e-3) / 1e9
         kernel = "decode_kernel (one launch per token)" if model.decode_mode == "persistent" else "gemv_stream_kernel"
         roofline = {"bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s", "frac": achieved / hbm,
-                    "traffic": traffic_per_launch("decode_kernel", args.n_layer) if model.decode_mode == "persistent" else None,
+                    "traffic": decode_traffic(ab["total"], wl["quant"], args.n_embd) if model.decode_mode == "persistent" else None,
                     "peak_source": which, "kernel": kernel, "algorithmic_bytes_per_launch": ab}
     else:
         # The tensor-core products take the largest share of the step; the largest of them (channel-mix key,
@@ -253,7 +253,7 @@ def run_ours(a, rank, world, dev):
         gm = time_gemm_alone(model, B, dev, a.steps)
         flops_step = 2.0 * B * model.matrix_params()
         roofline = {"bound": "tensor", "achieved": gm["tflops"], "peak": tf, "unit": "TFLOP/s", "frac": gm["tflops"] / tf,
-                    "traffic": traffic_per_launch("gemm_tc_kernel", args.n_layer), "peak_source": which + " (dense bf16 cuBLAS, sustained)",
+                    "traffic": GEMM_TRAFFIC.get((wl["quant"], 4 * args.n_embd, args.n_embd, B)), "peak_source": which + " (dense bf16 cuBLAS, sustained)",
                     "kernel": "gemm_tc_kernel on ffn.key [%d x %d] x batch %d" % (4 * args.n_embd, args.n_embd, B),
                     "algorithmic_flops_per_launch": gm["flops"], "us_per_launch": gm["us"],
                     "whole_step": {"matrix_tflops": flops_step / (ms_step * 1e-3) / 1e12,
