@@ -211,10 +211,11 @@ class RWKV_x070:
 
     # ---- state ------------------------------------------------------------------------------
     def new_state(self, batch: Optional[int] = None) -> List[torch.Tensor]:
-        """Zero state in the reference's layout (reference/rwkv7.py:100-105, :120-125)."""
+        """Zero state in the reference's layout (reference/rwkv7.py:100-105, :120-125); a pipeline stage holds
+        the entries of its own blocks only."""
         args, lead = self.args, (() if batch is None else (batch,))
         st: List[torch.Tensor] = []
-        for _ in range(args.n_layer):  # state: 0=att_x_prev 1=att_kv 2=ffn_x_prev
+        for _ in range(self.n_layer):  # state: 0=att_x_prev 1=att_kv 2=ffn_x_prev
             st.append(torch.zeros(lead + (args.n_embd,), dtype=DTYPE, device=self.device))
             st.append(torch.zeros(lead + (args.n_embd // args.head_size, args.head_size, args.head_size),
                                   dtype=torch.float, device=self.device))

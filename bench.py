@@ -33,6 +33,7 @@ sys.path.insert(0, ROOT)
 WORKLOADS = {
     "decode_bsz1_int8": dict(batch=1, quant="int8"),
     "decode_bsz320_nvfp4": dict(batch=320, quant="nvfp4"),
+    "pipeline_bsz320_nvfp4": dict(batch=320, quant="nvfp4"),   # layer pipeline: one stage per rank (torchrun, N >= 2)
     "gemv_int8": dict(batch=1, quant="int8"),
     "gemv_nvfp4": dict(batch=1, quant="nvfp4"),
     "gemm_int8": dict(batch=320, quant="int8"),
@@ -281,6 +282,76 @@ def run_ours(a, rank, world, dev):
 
 
 # ----------------------------------------------------------------------------------------------
+# layer pipeline: rank s holds blocks [s*L/S, (s+1)*L/S); x and v_first ([b, D] fp16) cross each boundary
+# ----------------------------------------------------------------------------------------------
+def run_pipeline(a, rank, world, dev):
+    from albatross_b200 import RWKV_x070, synth, dist as adist
+    import torch.distributed as td
+    wl = WORKLOADS[a.workload]
+    B, M = a.batch or wl["batch"], a.micro
+    assert world >= 2 and B % M == 0, "the pipeline workload needs torchrun with >= 2 ranks and batch % micro == 0"
+    b = B // M
+    args = synth.make_args(a.model)
+    D, V = args.n_embd, args.vocab_size
+    lo, hi = adist.stage_layers(args.n_layer, world, rank)
+    device = f"cuda:{dev}"
+    model = RWKV_x070(args, quant=wl["quant"], state_dict=synth.iter_checkpoint(a.model, seed=0, device=device),
+                      device=device, layer_range=(lo, hi))
+    states = [model.new_state(b) for _ in range(M)]
+    xout = [torch.empty(b, D, dtype=torch.float16, device=device) for _ in range(M)]
+    vbuf = [torch.empty(b, D, dtype=torch.float16, device=device) for _ in range(M)]
+    rbuf = [[torch.empty(b, D, dtype=torch.float16, device=device) for _ in range(2)] for _ in range(M)]
+    turn = [0] * M
+
+    def make_buffer(mb):   # called twice per micro-batch and step: x_in, then v_first
+        t = rbuf[mb][turn[mb] & 1]
+        turn[mb] += 1
+        return t
+
+    def stage_fn(mb, inp, v_first):
+        if model.is_first:
+            model.forward_stage(states[mb], vbuf[mb], tokens=inp.to(torch.int32), x_out=xout[mb])
+            return xout[mb], vbuf[mb]
+        if model.is_last:
+            return model.forward_stage(states[mb], v_first, x_in=inp).argmax(-1)
+        model.forward_stage(states[mb], v_first, x_in=inp, x_out=xout[mb])
+        return xout[mb], v_first
+
+    dec = adist.PipelineDecoder(stage_fn, M, make_buffer, lambda mb: torch.empty(b, dtype=torch.int64, device=device))
+    g = torch.Generator().manual_seed(7)
+    tokens = [torch.randint(0, V, (b,), generator=g).to(device) for _ in range(M)] if model.is_first else None
+
+    def sync_all():
+        torch.cuda.synchronize(); td.barrier(); torch.cuda.synchronize()
+
+    for _ in range(a.warmup):
+        tokens = dec.step(tokens)
+    sync_all()
+    sampler = ClockSampler(dev)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(a.steps):
+        tokens = dec.step(tokens)
+    e1.record()
+    sync_all()
+    clocks = sampler.stop()
+    t = torch.tensor([e0.elapsed_time(e1)], device=device)
+    td.all_reduce(t, op=td.ReduceOp.MAX)
+    total_ms = float(t.item())
+    from albatross_b200 import _lib
+    return {"metric": METRIC, "value": B * a.steps / (total_ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": a.steps,
+            "warmup": a.warmup, "ms_per_step": total_ms / a.steps, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "nvfp4 weights de-quantised to fp16 in registers, fp16 activations, fp32 accumulate and WKV state",
+            "data": "synthetic (seeded random weights in the reference checkpoint schema, random token ids)",
+            "config": {"workload": a.workload, "model": a.model, "global_batch": B, "micro_batches": M, "stages": world,
+                       "blocks_per_stage": hi - lo, "exchange": "x and v_first, [%d, %d] fp16 each, NCCL send/recv per micro-batch and stage boundary; "
+                       "token ids int64 [%d] back to stage 0" % (b, D, b)},
+            "e2e": None, "gpu_launches": (8 * (hi - lo) + 2) * M * a.steps, "roofline": None, "clocks": clocks,
+            "device_status": _lib.device_status()}
+
+
+# ----------------------------------------------------------------------------------------------
 # single-kernel workload: one quantised matrix-vector product (baseline config 1 and its larger shapes)
 # ----------------------------------------------------------------------------------------------
 def run_gemv(a, dev):
@@ -418,6 +489,7 @@ def main():
     ap.add_argument("--model", default="7.2b")
     ap.add_argument("--batch", type=int, default=0)
     ap.add_argument("--stages", type=int, default=0)
+    ap.add_argument("--micro", type=int, default=4, help="pipeline workload: micro-batches in flight")
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host (profiling)")
     ap.add_argument("--decode-mode", default=None, choices=["persistent", "graph", "eager"])
@@ -456,9 +528,9 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         torch.cuda.set_device(local)
         torch.distributed.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
-    out = run_ours(a, rank, world, local)
+    out = run_pipeline(a, rank, world, local) if a.workload.startswith("pipeline_") else run_ours(a, rank, world, local)
     if rank == 0:
-        if world == 1 and not a.no_cpu_baseline:
+        if world == 1 and not a.no_cpu_baseline and not a.workload.startswith("pipeline_"):
             out["cpu_baseline"] = run_cpu(a)
         print(json.dumps(out))
     if world > 1:

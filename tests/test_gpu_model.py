@@ -94,6 +94,27 @@ def test_wide_batch_decode_uses_the_persistent_head_kernel():
         assert rel_err(state[3 * i + 1].cpu().numpy(), st_ref[3 * i + 1].numpy()) <= LOGIT_REL_TOL
 
 
+def test_pipeline_stages_chain_to_the_full_model():
+    """Two stage models (blocks [0,1) and [1,2)) on one device, chained by x and v_first, equal the whole model."""
+    from albatross_b200 import RWKV_x070, synth
+    full, args = model_for("tiny", "int8")
+    sd = dict(synth.iter_checkpoint("tiny", seed=0))
+    stages = [RWKV_x070(args, quant="int8", state_dict=sd, layer_range=r) for r in ((0, 1), (1, 2))]
+    B, D = 5, args.n_embd
+    toks = torch.tensor(seeded_tokens(args.vocab_size, B, seed=3), dtype=torch.int32, device="cuda")
+    st_full = full.new_state(B)
+    st = [m.new_state(B) for m in stages]
+    for step in range(3):
+        want, st_full = full.forward_batch([[int(t)] for t in toks], st_full)
+        x = torch.empty(B, D, dtype=torch.float16, device="cuda")
+        vf = torch.empty(B, D, dtype=torch.float16, device="cuda")
+        assert stages[0].forward_stage(st[0], vf, tokens=toks, x_out=x) is None
+        got = stages[1].forward_stage(st[1], vf, x_in=x)
+        assert torch.equal(got, want)
+        toks = want.argmax(-1).to(torch.int32)
+    assert torch.equal(st[0][1], st_full[1]) and torch.equal(st[1][1], st_full[4]) and len(st[0]) == 3
+
+
 def test_state_is_updated_in_place_and_forkable():
     model, args = model_for("tiny", "int8")
     state = model.new_state()
