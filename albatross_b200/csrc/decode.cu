@@ -116,7 +116,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) decode_kernel(const DecodePro
             const bool pre = j >= 0 && prog->smem_prefetch;
             gemv_consume(ph.g, plans[i & 3], m, tid, bid, i, pre_phase, pre ? &phs[j & 3].g : nullptr,
                          pre ? &plans[j & 3] : nullptr, j,
-                         (prog->timeline && bid == 0) ? prog->timeline + 2 * n_phases + 4 * i : nullptr);
+                         (prog->timeline && bid == 0) ? prog->timeline + 2 * n_phases + 4 * i : nullptr, prog->early_slice != 0);
         } else {
             const HeadParams& hp = ph.h;
             for (int h = bid; h < hp.H; h += nb) {   // block-uniform

@@ -23,7 +23,7 @@ struct DecodeProgram {
     int n_blocks;
     int l2_prefetch_bytes;   // per block: how much of its share of the next matrix-vector phase is pulled into L2 early
     int smem_prefetch;       // warps start the copy of their first slice of the next phase before the barrier
-    int pad0;
+    int early_slice;         // warps request the first slice of their first item right behind the input loads
     const BlockPlan* plans;  // [n_phases][n_blocks], computed on the host (device copy follows the phases)
     unsigned* barrier;       // points at barrier_word of the device copy
     unsigned long long* timeline;  // optional: block 0 stores %globaltimer at [2i] phase start, [2i+1] phase end

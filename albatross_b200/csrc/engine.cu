@@ -61,6 +61,7 @@ struct ab_model {
     int timeline = 0;    // persistent decode kernel records per-phase timestamps
     int l2_prefetch_kb = 0;   // persistent decode kernel: L2 prefetch of the next phase, per block
     int smem_prefetch = 0;
+    int early_slice = 0;   // measured slower: any weight traffic in flight delays the loads of the input vector
     int merge_ups = 0;   // persistent decode kernel: block h computes the adapter outputs of head h and runs it without a grid barrier
 };
 
@@ -224,6 +225,7 @@ int build_decode_program(ab_model* m, const int32_t* token, void* const* state, 
     prog->first_gemv = 0;
     prog->l2_prefetch_bytes = m->l2_prefetch_kb * 1024;
     prog->smem_prefetch = m->smem_prefetch;
+    prog->early_slice = m->early_slice;
     prog->barrier = const_cast<unsigned*>(&dev_addr->barrier_word);
     prog->timeline = m->timeline ? (unsigned long long*)((unsigned char*)dev_addr +
                                                           decode_timeline_offset(n_phases, m->n_sm)) : nullptr;
@@ -553,6 +555,7 @@ int ab_model_set_option(ab_model* m, const char* name, int value) {
     else if (!strcmp(name, "l2_prefetch_kb")) m->l2_prefetch_kb = value < 0 ? 0 : value;
     else if (!strcmp(name, "smem_prefetch")) m->smem_prefetch = value != 0;
     else if (!strcmp(name, "merge_ups")) m->merge_ups = value != 0;
+    else if (!strcmp(name, "early_slice")) m->early_slice = value != 0;
     else if (!strcmp(name, "layer_offset")) { AB_CHECK_ARG(value >= 0, "layer_offset must be >= 0"); m->layer_offset = value; }
     else { set_error("unknown option %s", name); return ERR_BAD_ARG; }
     return OK;

@@ -484,7 +484,8 @@ __device__ __forceinline__ void prep_x(const GemvSeg& sg, const GemvSmem& m, int
 //             first item of that launch into its slot when it runs out of items here
 __device__ __forceinline__ void gemv_consume(const GemvParams& p, const BlockPlan& bp, const GemvSmem& m, int tid,
                                              int bid, int phase_idx, int& pre_phase, const GemvParams* np,
-                                             const BlockPlan* nbp, int next_phase_idx, unsigned long long* tl = nullptr) {
+                                             const BlockPlan* nbp, int next_phase_idx, unsigned long long* tl = nullptr,
+                                             bool early = false) {
     auto stamp = [&](int k) {
         if (tl && tid == 0) {
             unsigned long long t;
@@ -495,6 +496,16 @@ __device__ __forceinline__ void gemv_consume(const GemvParams& p, const BlockPla
     const int warp = tid >> 5, lane = tid & 31;
     __half* xn = m.xn;
     __half* dx = m.dx;
+    // `early`: the first slice of the warp's first item is requested (cp.async into the warp's slot) right behind
+    // the input vector's loads, so that it is there when the inputs have been prepared. Asked for any earlier, the
+    // weight traffic would sit in front of the input loads in the memory pipeline and delay them.
+    bool early_issued = false;
+    auto issue_early = [&]() {
+        if (early && !early_issued && pre_phase != phase_idx && warp < bp.n_items) {
+            prefetch_item(make_item(p, bp, warp), lane, m.pref + warp * (GEMV_ROWS * GEMV_SLICE_BYTES));
+            early_issued = true;
+        }
+    };
 
     if (p.copy_src && bid == 0)
         for (int i = tid; i < p.copy_n / 8; i += NT_CONS)
@@ -540,6 +551,7 @@ __device__ __forceinline__ void gemv_consume(const GemvParams& p, const BlockPla
                 if (any_mix) pv = ld_act16(reinterpret_cast<const uint4*>(p.x_prev) + i);
                 if (p.x_copy && bid == 0) reinterpret_cast<uint4*>(p.x_copy)[i] = v;
             }
+            issue_early();
             const __half2* h = reinterpret_cast<const __half2*>(&v);
             if (K / 8 <= NT_CONS) {
                 // single pass: statistics over the whole vector are available after one block reduction
@@ -627,6 +639,7 @@ __device__ __forceinline__ void gemv_consume(const GemvParams& p, const BlockPla
         cons_sync();
     }
     stamp(0);
+    issue_early();
 
     // ---- prepared inputs of every segment this block touches
     for (int s = 0; s < bp.nseg; ++s)
@@ -639,7 +652,7 @@ __device__ __forceinline__ void gemv_consume(const GemvParams& p, const BlockPla
         unsigned char* slot = m.pref + warp * (GEMV_ROWS * GEMV_SLICE_BYTES);
         Item cur = make_item(p, bp, warp);
         ItemBuf cb;
-        if (pre_phase == phase_idx) take_prefetched(cur, lane, slot, cb);   // the slot holds slice 0 of item `warp`
+        if (pre_phase == phase_idx || early_issued) take_prefetched(cur, lane, slot, cb);   // the slot holds slice 0 of item `warp`
         else if (item_full(cur)) load_item<true>(cur, 0, lane, cb);
         else load_item<false>(cur, 0, lane, cb);
         int i = warp;
