@@ -7,7 +7,7 @@
 //   D[128 weight rows, N batch rows] (fp32, TMEM) += A[128, 64] (weights, fp16) * B[N, 64]^T (activations, fp16)
 //
 // The weights are the M side of the MMA so that every weight byte is read from HBM exactly once per
-// N tile; the batch (up to 320 rows per block: two MMAs of N = 160) is the N side.
+// N tile; the batch (up to 320 rows per block: an MMA of N = 192 and one for the rest) is the N side.
 //   producer groups (G_NG groups of 4 warps; thread = one of the block's 128 weight rows): group g owns
 //               k-steps g, g + G_NG, ... It brings the row's 64 inputs of a k-step in (cp.async ring of raw
 //               quantised bytes; fp16 rows go straight to registers), de-quantises in registers (int8 ->
@@ -62,7 +62,8 @@ struct GemmGroup {
     int n_prob;
     int rows;       // batch rows (B*T)
     int n_tile;     // batch rows per block tile
-    int n_inst;     // MMAs per k-substep (1, or 2 when n_tile > 256)
+    int n_first;    // batch rows of the first MMA of a k-substep (n_tile, or 192 when a second MMA takes the rest)
+    int tma_rows;   // batch rows per TMA box
     int tmem_cols;
     unsigned* counters;
     float* partials;
@@ -281,7 +282,6 @@ __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ 
     unsigned char* smA = base;                                  // G_STAGES x 16 KB
     unsigned char* smB = base + G_STAGES * G_A_BYTES;           // G_STAGES x n_tile x 128 B
     unsigned char* smRaw = smB + G_STAGES * b_bytes;            // raw weight ring
-    const int n_inst_cols = g.n_tile / g.n_inst;
 
     if (tid == 0) {
         for (int s = 0; s < G_STAGES; ++s) {
@@ -527,9 +527,8 @@ __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ 
                 const int s = ks % G_STAGES, f = ks / G_STAGES;
                 if (f > 0) wait_ok(&empty[s], (f - 1) & 1);
                 mbar_expect_tx(&full[s], (uint32_t)b_bytes);
-                for (int j = 0; j < g.n_inst; ++j)
-                    tma_load_2d(smB + s * b_bytes + j * n_inst_cols * 128, map, kstep_of(ks) * G_BK, n0 + j * n_inst_cols,
-                                &full[s]);
+                for (int r = 0; r < g.n_tile; r += g.tma_rows)
+                    tma_load_2d(smB + s * b_bytes + r * 128, map, kstep_of(ks) * G_BK, n0 + r, &full[s]);
             }
         }
     } else {
@@ -537,12 +536,14 @@ __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ 
         if (lane == 0) {
             // One thread feeds the tensor core, so its instruction stream is kept short: descriptors are built
             // once, a stage or a 16-input step further is an add to the (address >> 4) field.
-            const uint32_t idesc = umma_idesc_f16(n_inst_cols);
+            // An MMA is at most 256 batch rows wide and runs in steps of 64 of them: a 320-row tile is issued as
+            // 192 + 128 on separate TMEM columns (160 + 160 would cost as much as 192 + 192).
+            const bool two = g.n_first < g.n_tile;
+            const uint32_t idesc = umma_idesc_f16(g.n_first), idesc1 = umma_idesc_f16(two ? g.n_tile - g.n_first : 16);
             const uint64_t da0 = umma_desc_sw128(smA), db0 = umma_desc_sw128(smB);
             const uint64_t a_stage = (uint64_t)(G_A_BYTES >> 4), b_stage = (uint64_t)(b_bytes >> 4);
-            const uint64_t b_half = (uint64_t)((n_inst_cols * 128) >> 4);
-            const uint32_t d1 = tmem_base + (uint32_t)n_inst_cols;
-            const bool two = g.n_inst == 2;
+            const uint64_t b_half = (uint64_t)((g.n_first * 128) >> 4);
+            const uint32_t d1 = tmem_base + (uint32_t)g.n_first;
             int s = 0;
             uint32_t parity = 0;
             uint64_t da = da0, db = db0;
@@ -552,11 +553,11 @@ __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ 
                 const uint32_t acc0 = ks > 0 ? 1u : 0u;
                 // advancing 16 inputs = 32 bytes inside the swizzle row: +2 in the (address >> 4) field
                 tc_mma_f16(tmem_base, da, db, idesc, acc0);
-                if (two) tc_mma_f16(d1, da, db + b_half, idesc, acc0);
+                if (two) tc_mma_f16(d1, da, db + b_half, idesc1, acc0);
 #pragma unroll
                 for (int k4 = 1; k4 < G_BK / 16; ++k4) {
                     tc_mma_f16(tmem_base, da + (uint64_t)(2 * k4), db + (uint64_t)(2 * k4), idesc, 1u);
-                    if (two) tc_mma_f16(d1, da + (uint64_t)(2 * k4), db + b_half + (uint64_t)(2 * k4), idesc, 1u);
+                    if (two) tc_mma_f16(d1, da + (uint64_t)(2 * k4), db + b_half + (uint64_t)(2 * k4), idesc1, 1u);
                 }
                 tc_commit(&empty[s]);   // the stage may be refilled once these MMAs have read it
                 da += a_stage;
@@ -631,7 +632,7 @@ int check_mat(const ab_mat& m, const char* what) {
 namespace {
 
 struct GroupShape {
-    int n_tile, n_inst, tmem_cols, n_tiles_y;
+    int n_tile, n_first, tma_rows, tmem_cols, n_tiles_y;
     int ksplit[G_MAX_OPS];
     int grid_x;
     long long part_floats;
@@ -640,9 +641,9 @@ struct GroupShape {
 
 GroupShape group_shape(const GemmOp* ops, int n, int rows) {
     GroupShape gs = {};
-    if (rows <= 256) { gs.n_tile = (rows + 15) & ~15; gs.n_inst = 1; }
-    else if (rows <= 320) { gs.n_tile = (rows + 31) & ~31; gs.n_inst = 2; }
-    else { gs.n_tile = 256; gs.n_inst = 1; }
+    if (rows <= 256) { gs.n_tile = (rows + 15) & ~15; gs.n_first = gs.tma_rows = gs.n_tile; }
+    else if (rows <= 320) { gs.n_tile = (rows + 31) & ~31; gs.n_first = 192; gs.tma_rows = gs.n_tile % 64 ? 32 : 64; }
+    else { gs.n_tile = gs.n_first = gs.tma_rows = 256; }
     gs.tmem_cols = 32;
     while (gs.tmem_cols < gs.n_tile) gs.tmem_cols *= 2;
     gs.n_tiles_y = (rows + gs.n_tile - 1) / gs.n_tile;
@@ -702,10 +703,9 @@ int gemm_group_launch(const GemmOp* ops, int n, int rows, void* scratch, cudaStr
 
     GemmGroup g = {};
     GemmMaps maps;
-    g.n_prob = n; g.rows = rows; g.n_tile = gs.n_tile; g.n_inst = gs.n_inst; g.tmem_cols = gs.tmem_cols;
+    g.n_prob = n; g.rows = rows; g.n_tile = gs.n_tile; g.n_first = gs.n_first; g.tma_rows = gs.tma_rows; g.tmem_cols = gs.tmem_cols;
     g.counters = reinterpret_cast<unsigned*>(scratch);
     g.partials = scratch ? reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(scratch) + (size_t)G_COUNTERS * 4) : nullptr;
-    const int n_inst_cols = gs.n_tile / gs.n_inst;
     int cta = 0, tile = 0;
     long long part = 0;
     for (int i = 0; i < n; ++i) {
@@ -729,7 +729,7 @@ int gemm_group_launch(const GemmOp* ops, int n, int rows, void* scratch, cudaStr
         }
         const cuuint64_t gdim[2] = {(cuuint64_t)m.k, (cuuint64_t)rows};
         const cuuint64_t gstride[1] = {(cuuint64_t)m.k * 2};
-        const cuuint32_t box[2] = {(cuuint32_t)G_BK, (cuuint32_t)n_inst_cols};
+        const cuuint32_t box[2] = {(cuuint32_t)G_BK, (cuuint32_t)gs.tma_rows};
         const cuuint32_t estr[2] = {1, 1};
         const CUresult cr = encode(&maps.m[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(op.x), gdim, gstride, box,
                                    estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
