@@ -146,16 +146,24 @@ __global__ void __launch_bounds__(HT) head_fused_kernel(const __grid_constant__ 
 // The state (16 KiB per item, read once and written once per token) is all of the traffic, so the kernel is built
 // around keeping it moving, and nothing on an item's critical path waits for a global load:
 //   * warps 0-7 (256 threads) run the recurrence. The item's state arrives as ONE 16 KiB bulk copy into a ring of
-//     HB_STAGES shared-memory stages (mbarrier, byte-counted), up to HB_STAGES-1 items ahead of the one being worked on;
-//     the updated state goes straight from registers to global memory.
+//     HB_STAGES shared-memory stages (mbarrier, byte-counted) ahead of the item being worked on; the updated state
+//     is written back into its stage and leaves as ONE 16 KiB bulk copy as well, so no warp ever waits for the
+//     memory system to accept a store (register -> global stores made the step itself take 2.6 us per item).
 //   * warp 8 ("pre") turns the projections of item n+1 into the vectors of the recurrence (k normalisation and
 //     modulation, v residual gate, decay) while warps 0-7 are on item n; its inputs were fetched an item earlier.
-//     Its lane 0 issues the bulk copies.
+//     Its lane 0 issues the first bulk copies; thread 0 issues the write-backs and the later loads.
 //   * warp 9 ("post") turns the read-out of item n into the block output (group norm, bonus, gate).
 // Thread (i = tid/4, q = tid%4) owns, of state row i, the four 16-byte chunks {4m + q, m = 0..3} and visits them in
 // the order m = (e + i) % 4: a quarter-warp then reads eight different bank groups of the stage (no conflicts).
 // Helper lanes own channels 2*lane and 2*lane+1 (one 32-bit load per vector).
-constexpr int HB_STAGES = 4;
+#ifndef HB_STAGES_
+#define HB_STAGES_ 4
+#endif
+#ifndef HB_BLOCKS_
+#define HB_BLOCKS_ 3
+#endif
+constexpr int HB_STAGES = HB_STAGES_;
+constexpr int HB_BLOCKS = HB_BLOCKS_;   // resident blocks per SM
 constexpr int HB_THREADS = HT + 64;
 constexpr int HB_STATE_BYTES = 64 * 64 * 4;
 
@@ -170,14 +178,19 @@ struct HeadPost {   // what the output stage needs from the input stage
 
 __device__ __forceinline__ void bar_sync_id(int id, int n) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n) : "memory"); }
 __device__ __forceinline__ void bar_arrive_id(int id, int n) { asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(n) : "memory"); }
-__device__ __forceinline__ void st_cs16(float* p, float4 v) {
-    asm volatile("st.global.cs.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+__device__ __forceinline__ void bulk_s2g(void* dst, const void* src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;\n cp.async.bulk.commit_group;" ::"l"(dst),
+                 "r"(smem_u32(src)), "r"(bytes)
+                 : "memory");
 }
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 // two adjacent fp16 channels; activations bypass L1 (written by another SM in an earlier kernel)
 __device__ __forceinline__ float2 ld2a(const __half* p) { return __half22float2(__ldcg(reinterpret_cast<const __half2*>(p))); }
 __device__ __forceinline__ float2 ld2p(const __half* p) { return __half22float2(__ldg(reinterpret_cast<const __half2*>(p))); }
 
-__global__ void __launch_bounds__(HB_THREADS, 3) head_batch_kernel(const __grid_constant__ HeadParams p, int n_items) {
+__global__ void __launch_bounds__(HB_THREADS, HB_BLOCKS) head_batch_kernel(const __grid_constant__ HeadParams p, int n_items) {
     extern __shared__ __align__(128) unsigned char dsm[];   // HB_STAGES x 16 KiB
     __shared__ __align__(16) HeadVec vec[2];
     __shared__ __align__(16) HeadPost post[3];
@@ -199,6 +212,7 @@ __global__ void __launch_bounds__(HB_THREADS, 3) head_batch_kernel(const __grid_
     __syncthreads();
     // Named barriers. 1, 2: the vectors of an even / odd item are ready (pre arrives, warps 0-7 wait).
     // 3, 4: the recurrence of an even / odd item is done (warps 0-7 arrive, pre and post wait).
+    // 5: warps 0-7 have written an item's new state into its stage.
     constexpr int N_VEC = HT + 32, N_DONE = HT + 64;
     if (warp == 8) {
         auto load_state_of = [&](int n) {
@@ -281,8 +295,7 @@ __global__ void __launch_bounds__(HB_THREADS, 3) head_batch_kernel(const __grid_
             // cur = inputs of item n+1 (fetched an iteration ago); start on those of item n+2
             if (n + 2 < n_mine) fetch(n + 2, nxt);
             if (n > 0) {
-                bar_sync_id(3 + ((n - 1) & 1), N_DONE);   // item n-1 is through: its vectors and its stage are free
-                if (lane == 0 && n - 1 + HB_STAGES < n_mine) load_state_of(n - 1 + HB_STAGES);
+                bar_sync_id(3 + ((n - 1) & 1), N_DONE);   // item n-1 is through: its vectors are free
             }
             glue(n + 1, cur, vec[(n + 1) & 1], post[(n + 1) % 3]);
             bar_arrive_id(1 + ((n + 1) & 1), N_VEC);
@@ -323,7 +336,7 @@ __global__ void __launch_bounds__(HB_THREADS, 3) head_batch_kernel(const __grid_
                 *reinterpret_cast<volatile int*>(&s_failed) = 1;
                 atomicOr(&g_device_status, DEV_WAIT_HEAD);
             }
-            const float* srow = reinterpret_cast<const float*>(dsm + s * HB_STATE_BYTES) + i * 64;
+            float* srow = reinterpret_cast<float*>(dsm + s * HB_STATE_BYTES) + i * 64;
             float4 st[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) st[e] = *reinterpret_cast<const float4*>(srow + 16 * ((e + i) & 3) + 4 * q);
@@ -340,7 +353,6 @@ __global__ void __launch_bounds__(HB_THREADS, 3) head_batch_kernel(const __grid_
             sa += __shfl_xor_sync(0xffffffffu, sa, 2);
             const float v_i = cv.v[i];
             float y = 0.f;
-            float* gout = p.state + (size_t)item_of(n) * 4096 + i * 64;
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int c0 = 16 * ((e + i) & 3) + 4 * q;
@@ -351,13 +363,27 @@ __global__ void __launch_bounds__(HB_THREADS, 3) head_batch_kernel(const __grid_
                 o.y = fmaf(st[e].y, w4.y, fmaf(k4.y, v_i, sa * b4.y)); y = fmaf(o.y, r4.y, y);
                 o.z = fmaf(st[e].z, w4.z, fmaf(k4.z, v_i, sa * b4.z)); y = fmaf(o.z, r4.z, y);
                 o.w = fmaf(st[e].w, w4.w, fmaf(k4.w, v_i, sa * b4.w)); y = fmaf(o.w, r4.w, y);
-                st_cs16(gout + c0, o);
+                *reinterpret_cast<float4*>(srow + c0) = o;   // same chunk this thread read: nobody else touches it
             }
             y += __shfl_xor_sync(0xffffffffu, y, 1);
             y += __shfl_xor_sync(0xffffffffu, y, 2);
             if (q == 0) sy[n & 3][i] = rh(y);
             bar_arrive_id(3 + (n & 1), N_DONE);
+            fence_proxy_async();   // the stage is about to be read by the bulk-copy unit
+            bar_sync_id(5, HT);
+            if (tid == 0) {
+                bulk_s2g(p.state + (size_t)item_of(n) * 4096, dsm + s * HB_STATE_BYTES, HB_STATE_BYTES);
+                // all write-backs but the newest have left shared memory: the previous item's stage can be refilled
+                bulk_wait_read<1>();
+                const int m = n - 1 + HB_STAGES;
+                if (n >= 1 && m < n_mine) {
+                    const int sm = m % HB_STAGES;
+                    mbar_expect_tx(&full[sm], HB_STATE_BYTES);
+                    bulk_g2s(dsm + sm * HB_STATE_BYTES, p.state + (size_t)item_of(m) * 4096, HB_STATE_BYTES, &full[sm]);
+                }
+            }
         }
+        if (tid == 0) bulk_wait_all();   // every write-back has reached global memory before the block ends
     }
 }
 
@@ -382,7 +408,7 @@ int head_launch(const HeadParams& p, cudaStream_t stream) {
         AB_CHECK_ARG(((uintptr_t)p.state & 15) == 0, "head: state must be 16-byte aligned");
         const int n_items = p.B * p.H;
         cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3((unsigned)min(n_items, 3 * n_sm));
+        cfg.gridDim = dim3((unsigned)min(n_items, HB_BLOCKS * n_sm));
         cfg.blockDim = dim3(HB_THREADS);
         cfg.dynamicSmemBytes = HB_STAGES * HB_STATE_BYTES;
         cfg.stream = stream;
