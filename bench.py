@@ -42,11 +42,14 @@ WORKLOADS = {
 METRIC = "rwkv7_decode_tokens_per_s"
 
 
-def measured_peaks():
+def measured_peaks(burst: bool = False):
+    """(HBM GB/s, dense bf16 TFLOP/s, source). The tensor figure is the burst one for a kernel timed alone and the
+    sustained one for a kernel timed inside a long step."""
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
         d = json.load(open(p))
-        return float(d["hbm_gbs"]), float(d.get("bf16_tflops_sustained", d.get("bf16_tflops", 1590.0))), "measured"
+        tf = d.get("bf16_tflops") if burst else d.get("bf16_tflops_sustained", d.get("bf16_tflops"))
+        return float(d["hbm_gbs"]), float(tf or 1590.0), "measured"
     return 6650.0, 1590.0, "fallback"
 
 
@@ -253,8 +256,11 @@ def run_ours(a, rank, world, dev):
         # n_out = 4 * n_embd) is timed alone, live, on the model's own packed weights of every block in turn.
         gm = time_gemm_alone(model, B, dev, a.steps)
         flops_step = 2.0 * B * model.matrix_params()
-        roofline = {"bound": "tensor", "achieved": gm["tflops"], "peak": tf, "unit": "TFLOP/s", "frac": gm["tflops"] / tf,
-                    "traffic": GEMM_TRAFFIC.get((wl["quant"], 4 * args.n_embd, args.n_embd, B)), "peak_source": which + " (dense bf16 cuBLAS, sustained)",
+        _, tf_burst, _ = measured_peaks(burst=True)
+        roofline = {"bound": "tensor", "achieved": gm["tflops"], "peak": tf_burst, "unit": "TFLOP/s", "frac": gm["tflops"] / tf_burst,
+                    "frac_of_sustained_peak": gm["tflops"] / tf,
+                    "traffic": GEMM_TRAFFIC.get((wl["quant"], 4 * args.n_embd, args.n_embd, B)),
+                    "peak_source": which + " (dense bf16 cuBLAS; burst figure, the kernel is timed alone)",
                     "kernel": "gemm_tc_kernel on ffn.key [%d x %d] x batch %d" % (4 * args.n_embd, args.n_embd, B),
                     "algorithmic_flops_per_launch": gm["flops"], "us_per_launch": gm["us"],
                     "whole_step": {"matrix_tflops": flops_step / (ms_step * 1e-3) / 1e12,
@@ -430,7 +436,7 @@ def run_gemm(a, dev):
     clocks = sampler.stop()
     ms = e0.elapsed_time(e1) / a.steps
     flops = 2.0 * rows * n * k
-    _, tf, which = measured_peaks()
+    _, tf, which = measured_peaks(burst=True)
     tfs = flops / (ms * 1e-3) / 1e12
     return {"metric": "gemm_tflops", "value": tfs, "unit": "TFLOP/s", "n_gpus": 1, "steps": a.steps, "warmup": a.warmup,
             "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -438,7 +444,7 @@ def run_gemm(a, dev):
             "data": "synthetic", "config": {"workload": a.workload, "n_out": n, "k": k, "batch": rows, "matrices_cycled": n_mats},
             "gpu_launches": a.steps,
             "roofline": {"bound": "tensor", "achieved": tfs, "peak": tf, "unit": "TFLOP/s", "frac": tfs / tf, "traffic": None,
-                         "peak_source": which + " (dense bf16 cuBLAS, sustained)", "kernel": "gemm_tc_kernel",
+                         "peak_source": which + " (dense bf16 cuBLAS; burst figure, the kernel is timed alone)", "kernel": "gemm_tc_kernel",
                          "algorithmic_flops_per_launch": flops},
             "clocks": clocks, "device_status": _lib.device_status()}
 
