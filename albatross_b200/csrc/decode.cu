@@ -33,13 +33,18 @@ __device__ __forceinline__ void red_release_add(unsigned* p, unsigned v) {
 }
 
 // Barrier among all blocks. `failed` becomes (and stays) true once a wait has run out.
-__device__ __forceinline__ void grid_barrier(unsigned* counter, unsigned target, int tid, bool& failed) {
+// `while_waiting` runs in every thread after the block has announced its arrival and before thread 0 starts to
+// poll: work that does not depend on other blocks (requests for the next phase's first weights) goes there, so that
+// it neither delays the arrival nor shares the memory pipeline with the loads that follow the barrier.
+template <class F>
+__device__ __forceinline__ void grid_barrier(unsigned* counter, unsigned target, int tid, bool& failed, F while_waiting) {
     __shared__ int s_ok;
     cons_sync();   // every thread of the block has issued its writes of this phase
+    if (tid == 0 && !failed) red_release_add(counter, 1u);
+    while_waiting();
     if (tid == 0) {
         int ok = 1;
         if (!failed) {
-            red_release_add(counter, 1u);
             uint32_t it = 0;
             while (ld_acquire_u32(counter) < target) {
                 if (++it > (1u << 23)) {
@@ -135,8 +140,22 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) decode_kernel(const DecodePro
         }
         if (prog->timeline && bid == 0 && tid == 0) prog->timeline[2 * i + 1] = global_ns();
         if (i + 1 < n_phases) {
-            if (ph.no_barrier) cons_sync();   // same block produces and consumes: a block barrier orders the global writes
-            else grid_barrier(prog->barrier, (unsigned)(++n_barriers) * nb, tid, failed);
+            if (ph.no_barrier) {
+                cons_sync();   // same block produces and consumes: a block barrier orders the global writes
+            } else {
+                const int j = ph.type == PHASE_GEMV ? ph.next_gemv : -1;
+                grid_barrier(prog->barrier, (unsigned)(++n_barriers) * nb, tid, failed, [&]() {
+                    // the warp's first work item of the next matrix-vector phase starts its way into shared memory
+                    if (prog->barrier_prefetch && j >= 0 && pre_phase != j) {
+                        const GemvParams& q = phs[j & 3].g;
+                        const BlockPlan& np_ = plans[j & 3];
+                        const int w = tid >> 5;
+                        if (w < np_.n_items)
+                            prefetch_item(make_item(q, np_, w), tid & 31, m.pref + w * (GEMV_ROWS * GEMV_SLICE_BYTES));
+                        pre_phase = j;
+                    }
+                });
+            }
         }
     }
 }

@@ -62,6 +62,7 @@ struct ab_model {
     int l2_prefetch_kb = 0;   // persistent decode kernel: L2 prefetch of the next phase, per block
     int smem_prefetch = 0;
     int early_slice = 0;   // measured slower: any weight traffic in flight delays the loads of the input vector
+    int barrier_prefetch = 0;   // measured slower: the polls of the barrier queue behind the prefetch traffic
     int merge_ups = 0;   // persistent decode kernel: block h computes the adapter outputs of head h and runs it without a grid barrier
 };
 
@@ -226,6 +227,7 @@ int build_decode_program(ab_model* m, const int32_t* token, void* const* state, 
     prog->l2_prefetch_bytes = m->l2_prefetch_kb * 1024;
     prog->smem_prefetch = m->smem_prefetch;
     prog->early_slice = m->early_slice;
+    prog->barrier_prefetch = m->barrier_prefetch;
     prog->barrier = const_cast<unsigned*>(&dev_addr->barrier_word);
     prog->timeline = m->timeline ? (unsigned long long*)((unsigned char*)dev_addr +
                                                           decode_timeline_offset(n_phases, m->n_sm)) : nullptr;
@@ -556,6 +558,7 @@ int ab_model_set_option(ab_model* m, const char* name, int value) {
     else if (!strcmp(name, "smem_prefetch")) m->smem_prefetch = value != 0;
     else if (!strcmp(name, "merge_ups")) m->merge_ups = value != 0;
     else if (!strcmp(name, "early_slice")) m->early_slice = value != 0;
+    else if (!strcmp(name, "barrier_prefetch")) m->barrier_prefetch = value != 0;
     else if (!strcmp(name, "layer_offset")) { AB_CHECK_ARG(value >= 0, "layer_offset must be >= 0"); m->layer_offset = value; }
     else { set_error("unknown option %s", name); return ERR_BAD_ARG; }
     return OK;
