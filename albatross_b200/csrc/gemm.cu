@@ -147,6 +147,11 @@ __device__ __forceinline__ void cp_async_4(void* dst, const void* src, bool ok) 
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ unsigned ld_acquire_gpu(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
 __device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, %0;" ::"n"(G_PROD) : "memory"); }
 
 // K-major operand tile, 128-byte swizzle: rows of 128 bytes, groups of 8 rows 1024 bytes apart.
@@ -447,12 +452,20 @@ __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ 
             else emit32(ci, v);
         };
         // residual tiles on their way in (only blocks that will write the output need them)
+        // Split K ends in one of two ways. Few slices (the long products launched alone, whose blocks all finish
+        // together): the last block to arrive sums the tile, the others leave at once. Many slices (the fp16 adapter
+        // products of a grouped launch, whose blocks are done long before the rest of the grid): every block of the
+        // tile takes the chunks ci = z, z + ksplit, ... once all partial sums are there.
+        const bool shared_sum = pb.ksplit >= 6;
+        auto my_chunk = [&](int ci) { return !shared_sum || ci % pb.ksplit == z; };
         auto fetch_resid = [&]() {
             if (!(staged && epi == EPI_RESID)) return;
             if (tid == 0) {
-                mbar_expect_tx(&resid_bar, (uint32_t)(n_chunks * 32 * G_BM * 2));
+                int n_mine = 0;
+                for (int ci = 0; ci < n_chunks; ++ci) n_mine += my_chunk(ci) ? 1 : 0;
+                mbar_expect_tx(&resid_bar, (uint32_t)(n_mine * 32 * G_BM * 2));
                 for (int ci = 0; ci < n_chunks; ++ci)
-                    tma_load_2d(stg + (size_t)ci * 32 * G_BM, &maps.r[pi], m0, n0 + ci * 32, &resid_bar);
+                    if (my_chunk(ci)) tma_load_2d(stg + (size_t)ci * 32 * G_BM, &maps.r[pi], m0, n0 + ci * 32, &resid_bar);
             }
             wait_ok(&resid_bar, 0);
         };
@@ -461,7 +474,8 @@ __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ 
             fence_proxy_async();
             epi_sync();
             if (tid == 0) {
-                for (int ci = 0; ci < n_chunks; ++ci) tma_store_2d(&maps.y[pi], m0, n0 + ci * 32, stg + (size_t)ci * 32 * G_BM);
+                for (int ci = 0; ci < n_chunks; ++ci)
+                    if (my_chunk(ci)) tma_store_2d(&maps.y[pi], m0, n0 + ci * 32, stg + (size_t)ci * 32 * G_BM);
                 bulk_commit_and_drain_reads();   // the shared memory must outlive the unit's reads
             }
         };
@@ -478,7 +492,10 @@ __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ 
             }
             flush();
         } else {
-            // split K: park this block's fp32 tile, the last block to arrive sums all of them in a fixed order
+            // Split K: every block of the tile parks its fp32 partial sums; they are summed in a fixed order
+            // (deterministic). Where the blocks of a tile wait for one another it is safe because a split grid never
+            // has more blocks than the GPU has SMs and every block holds a whole SM: all of them are resident. The
+            // wait is bounded all the same.
             const int tile = pb.tile_base + m_tile * gridDim.y + blockIdx.y;
             const size_t tile_floats = (size_t)g.n_tile * G_BM;
             float* tile0 = g.partials + pb.part_base + ((size_t)(m_tile * gridDim.y + blockIdx.y) * pb.ksplit) * tile_floats;
@@ -494,15 +511,28 @@ __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ 
             epi_sync();
             if (tid == 0) {
                 const unsigned old = atomicAdd(&g.counters[tile], 1u);
-                const int last = old == (unsigned)pb.ksplit - 1;
-                if (last) g.counters[tile] = 0;   // leave the counter ready for the next launch
-                s_last = last;
-                __threadfence();
+                int go;
+                if (shared_sum) {
+                    go = 1;
+                    uint32_t it = 0;
+                    while (ld_acquire_gpu(&g.counters[tile]) < (unsigned)pb.ksplit) {
+                        if (++it > (1u << 21)) {
+                            go = 0;
+                            atomicOr(&g_device_status, DEV_WAIT_GEMM);
+                            break;
+                        }
+                    }
+                } else {
+                    go = old == (unsigned)pb.ksplit - 1;
+                    if (go) g.counters[tile] = 0;   // leave the counter ready for the next launch
+                    __threadfence();
+                }
+                s_last = go;
             }
             epi_sync();
             if (s_last) {
                 fetch_resid();
-                for (int ci = grp; ci < n_chunks; ci += G_NG) {
+                auto sum_chunk = [&](int ci) {
                     float v[32];
 #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] = 0.f;
@@ -513,8 +543,20 @@ __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ 
                             if (ci * 32 + i < g.n_tile) v[i] += __ldcg(src + (size_t)(ci * 32 + i) * G_BM + r_local);
                     }
                     emit(ci, v);
+                };
+                if (shared_sum) {
+                    int k = 0;
+                    for (int ci = z; ci < n_chunks; ci += pb.ksplit, ++k)
+                        if (k % G_NG == grp) sum_chunk(ci);
+                } else {
+                    for (int ci = grp; ci < n_chunks; ci += G_NG) sum_chunk(ci);
                 }
                 flush();
+            }
+            // shared sum: the last block to leave puts the counter back to zero for the next launch
+            if (shared_sum && tid == 0) {
+                const unsigned old = atomicAdd(&g.counters[tile], 1u);
+                if (old == 2u * (unsigned)pb.ksplit - 1u) g.counters[tile] = 0;
             }
         }
         tc_fence_before();
@@ -696,6 +738,17 @@ int gemm_group_launch(const GemmOp* ops, int n, int rows, void* scratch, cudaStr
     AB_CHECK_ARG(ops && n >= 1 && n <= G_MAX_OPS && rows > 0, "gemm: bad group (n=%d rows=%d)", n, rows);
     const GroupShape gs = group_shape(ops, n, rows);
     AB_CHECK_ARG(gs.n_split_tiles <= G_COUNTERS, "gemm: too many split-K tiles");
+    if (gs.n_split_tiles > 0) {
+        // the blocks of a split tile wait for one another: all of them must be resident (one block per SM)
+        static int n_sm = 0;
+        if (!n_sm) {
+            int dev = 0, v = 0;
+            AB_CUDA(cudaGetDevice(&dev));
+            AB_CUDA(cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev));
+            n_sm = v;
+        }
+        AB_CHECK_ARG(gs.grid_x * gs.n_tiles_y <= n_sm, "gemm: a split-K grid of %d blocks does not fit %d SMs", gs.grid_x * gs.n_tiles_y, n_sm);
+    }
     AB_CHECK_ARG(gs.part_floats == 0 || (scratch && ((uintptr_t)scratch & 15) == 0), "gemm: split-K needs a 16-byte aligned scratch area");
     EncodeTiledFn encode;
     int st = get_encode_fn(&encode);
