@@ -124,12 +124,17 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) decode_kernel(const DecodePro
                          (prog->timeline && bid == 0) ? prog->timeline + 2 * n_phases + 4 * i : nullptr, prog->early_slice != 0);
         } else {
             const HeadParams& hp = ph.h;
+            // adapter up-projections inside the phase: block h needs only the 64 channels of head h, so the
+            // matrix-vector phase (and the grid barrier) that would produce them for everybody is not needed
+            const bool ups = hp.w2 != nullptr;
             for (int h = bid; h < hp.H; h += nb) {   // block-uniform
                 if (tid < HT) {
+                    if (ups) head_ups_stage(hp, h, tid, smem);   // the matrix-vector buffers are idle in this phase
                     float* sbase = hp.state + (size_t)h * 4096;
                     StateRow st;
                     load_state(st, sbase, tid >> 2, tid & 3);
-                    head_steps(hp, 0, h, tid, st, hsh, false, SyncNamed256());
+                    if (ups) head_ups_compute(hp, tid, smem, hsh, SyncNamed256());
+                    head_steps(hp, 0, h, tid, st, hsh, ups, SyncNamed256());
                     store_state(st, sbase, tid >> 2, tid & 3);
                     if (hp.copy_src && tid < 32)
                         reinterpret_cast<__half2*>(hp.copy_dst + h * 64)[tid] =

@@ -17,13 +17,6 @@ namespace ab {
 
 namespace {
 
-__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_wait_all() {
-    asm volatile("cp.async.commit_group;\n cp.async.wait_group 0;" ::: "memory");
-}
-
 // ---------------------------------------------------------------------------------------------
 // Operator-ABI kernel
 // ---------------------------------------------------------------------------------------------
@@ -64,30 +57,13 @@ __global__ void __launch_bounds__(HT) wkv7_kernel(int T, int C, int H, float* __
 __global__ void __launch_bounds__(HT) head_fused_kernel(const __grid_constant__ HeadParams p) {
     extern __shared__ __align__(128) unsigned char dsm[];
     __shared__ HeadShared sh;
-    float (*up)[64] = sh.up;
     const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;
-    const int tid = threadIdx.x, i = tid >> 2, q = tid & 3, lane = tid & 31, warp = tid >> 5;
-    const int D = p.D;
+    const int tid = threadIdx.x, i = tid >> 2, q = tid & 3;
     const bool ups = p.w2 != nullptr;
-    const int rtot = p.rw + p.ra + p.rv + p.rg;
 
     // ---- batch-1 path: pull this head's slices of the four up-projection matrices into smem.
     // They are weights, so this runs before the wait on the previous kernel.
-    __half* w2s = reinterpret_cast<__half*>(dsm);             // [rtot][64]
-    float* hvec = reinterpret_cast<float*>(dsm + (size_t)rtot * 128);  // [rtot]
-    float* part = hvec + ((rtot + 3) & ~3);                   // [8][4][64]
-    if (ups) {
-        for (int pc = tid; pc < rtot * 8; pc += HT) {
-            int row = pc >> 3;
-            const int seg8 = pc & 7;
-            const __half* m;
-            if (row < p.rw) m = p.w2;
-            else if ((row -= p.rw) < p.ra) m = p.a2;
-            else if ((row -= p.ra) < p.rv) m = p.v2;
-            else { row -= p.rv; m = p.g2; }
-            cp_async16(w2s + (size_t)(pc >> 3) * 64 + seg8 * 8, m + (size_t)row * D + h * 64 + seg8 * 8);
-        }
-    }
+    if (ups) head_ups_stage(p, h, tid, dsm);
     if (p.use_pdl) {
         pdl_wait();
         pdl_launch_dependents();
@@ -98,38 +74,7 @@ __global__ void __launch_bounds__(HT) head_fused_kernel(const __grid_constant__ 
     load_state(st, sbase, i, q);
 
     if (ups) {
-        for (int j = tid; j < rtot; j += HT) {
-            int row = j;
-            const __half* hv;
-            if (row < p.rw) hv = p.hw;
-            else if ((row -= p.rw) < p.ra) hv = p.ha;
-            else if ((row -= p.ra) < p.rv) hv = p.hv;
-            else { row -= p.rv; hv = p.hg; }
-            hvec[j] = __half2float(hv[row]);
-        }
-        cp_async_wait_all();
-        __syncthreads();
-        // warp `warp` takes rows j = warp (mod 8); lane covers channels 2*lane, 2*lane+1
-        const int bounds[5] = {0, p.rw, p.rw + p.ra, p.rw + p.ra + p.rv, rtot};
-#pragma unroll
-        for (int m = 0; m < 4; ++m) {
-            float s0 = 0.f, s1 = 0.f;
-            for (int j = bounds[m] + warp; j < bounds[m + 1]; j += 8) {
-                const float2 wv = __half22float2(reinterpret_cast<const __half2*>(w2s + (size_t)j * 64)[lane]);
-                s0 = fmaf(hvec[j], wv.x, s0);
-                s1 = fmaf(hvec[j], wv.y, s1);
-            }
-            part[(warp * 4 + m) * 64 + 2 * lane] = s0;
-            part[(warp * 4 + m) * 64 + 2 * lane + 1] = s1;
-        }
-        __syncthreads();
-        {
-            const int m = tid >> 6, c = tid & 63;
-            float s = 0.f;
-#pragma unroll
-            for (int wq = 0; wq < 8; ++wq) s += part[(wq * 4 + m) * 64 + c];
-            up[m][c] = rh(s);
-        }
+        head_ups_compute(p, tid, dsm, sh, SyncBlock());
         if (p.copy_src && tid < 32)
             reinterpret_cast<__half2*>(p.copy_dst + h * 64)[tid] = reinterpret_cast<const __half2*>(p.copy_src + h * 64)[tid];
         __syncthreads();
@@ -422,8 +367,7 @@ int head_launch(const HeadParams& p, cudaStream_t stream) {
     }
     size_t smem = 0;
     if (ups) {
-        const int rtot = p.rw + p.ra + p.rv + p.rg;
-        smem = (size_t)rtot * 128 + (size_t)((rtot + 3) & ~3) * 4 + 8 * 4 * 64 * 4;
+        smem = head_ups_smem(p.rw + p.ra + p.rv + p.rg);
     }
     static size_t max_smem = 0;
     if (!max_smem) {

@@ -38,6 +38,76 @@ __device__ __forceinline__ void store_state(const StateRow& st, float* base, int
     for (int e = 0; e < 4; ++e) dst[e] = make_float4(st.s[4 * e], st.s[4 * e + 1], st.s[4 * e + 2], st.s[4 * e + 3]);
 }
 
+__device__ __forceinline__ void head_cp_async16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void head_cp_async_wait_all() {
+    asm volatile("cp.async.commit_group;\n cp.async.wait_group 0;" ::: "memory");
+}
+// Bytes of scratch shared memory the in-kernel adapter up-projections of one head need.
+__host__ __device__ inline size_t head_ups_smem(int rtot) {
+    return (size_t)rtot * 128 + (size_t)((rtot + 3) & ~3) * 4 + 8 * 4 * 64 * 4;
+}
+
+// Batch-1 adapter up-projections of head h, part 1: start copying this head's 64-channel slices of the four
+// up-projection matrices ([rank, D] each) into scratch shared memory. They are weights: no dependency on activations.
+__device__ __forceinline__ void head_ups_stage(const HeadParams& p, int h, int tid, unsigned char* dsm) {
+    __half* w2s = reinterpret_cast<__half*>(dsm);   // [rtot][64]
+    const int rtot = p.rw + p.ra + p.rv + p.rg;
+    for (int pc = tid; pc < rtot * 8; pc += HT) {
+        int row = pc >> 3;
+        const int seg8 = pc & 7;
+        const __half* m;
+        if (row < p.rw) m = p.w2;
+        else if ((row -= p.rw) < p.ra) m = p.a2;
+        else if ((row -= p.ra) < p.rv) m = p.v2;
+        else { row -= p.rv; m = p.g2; }
+        head_cp_async16(w2s + (size_t)(pc >> 3) * 64 + seg8 * 8, m + (size_t)row * p.D + h * 64 + seg8 * 8);
+    }
+}
+// Part 2: sh.up[m][c] = sum_j hidden_m[j] * W2_m[j, h*64 + c] for the four adapters m (w, a, v-gate, g).
+template <class Sync>
+__device__ __forceinline__ void head_ups_compute(const HeadParams& p, int tid, unsigned char* dsm, HeadShared& sh, Sync sync) {
+    const int rtot = p.rw + p.ra + p.rv + p.rg;
+    const int lane = tid & 31, warp = tid >> 5;
+    const __half* w2s = reinterpret_cast<const __half*>(dsm);
+    float* hvec = reinterpret_cast<float*>(dsm + (size_t)rtot * 128);   // [rtot]
+    float* part = hvec + ((rtot + 3) & ~3);                             // [8][4][64]
+    for (int j = tid; j < rtot; j += HT) {
+        int row = j;
+        const __half* hv;
+        if (row < p.rw) hv = p.hw;
+        else if ((row -= p.rw) < p.ra) hv = p.ha;
+        else if ((row -= p.ra) < p.rv) hv = p.hv;
+        else { row -= p.rv; hv = p.hg; }
+        hvec[j] = lda(hv + row);
+    }
+    head_cp_async_wait_all();
+    sync();
+    // warp `warp` takes rows j = warp (mod 8); lane covers channels 2*lane, 2*lane+1
+    const int bounds[5] = {0, p.rw, p.rw + p.ra, p.rw + p.ra + p.rv, rtot};
+#pragma unroll
+    for (int m = 0; m < 4; ++m) {
+        float s0 = 0.f, s1 = 0.f;
+        for (int j = bounds[m] + warp; j < bounds[m + 1]; j += 8) {
+            const float2 wv = __half22float2(reinterpret_cast<const __half2*>(w2s + (size_t)j * 64)[lane]);
+            s0 = fmaf(hvec[j], wv.x, s0);
+            s1 = fmaf(hvec[j], wv.y, s1);
+        }
+        part[(warp * 4 + m) * 64 + 2 * lane] = s0;
+        part[(warp * 4 + m) * 64 + 2 * lane + 1] = s1;
+    }
+    sync();
+    {
+        const int m = tid >> 6, c = tid & 63;
+        float s = 0.f;
+#pragma unroll
+        for (int wq = 0; wq < 8; ++wq) s += part[(wq * 4 + m) * 64 + c];
+        sh.up[m][c] = rh(s);
+    }
+    sync();
+}
+
 // One recurrence step for this thread's 16 columns. Vectors are indexed by key column j.
 // Returns y_i (valid in all four lanes of the row).
 __device__ __forceinline__ float wkv_step(StateRow& st, const float* w, const float* k, const float* a,

@@ -130,6 +130,7 @@ class RWKV_x070:
         self._ws: Dict[Tuple[int, int], torch.Tensor] = {}
         self._graphs: Dict[tuple, tuple] = {}
         self._programs: Dict[tuple, tuple] = {}
+        self._options: Dict[str, int] = {}
         # token ids travel host -> device from a ring of pinned slots; a slot is reused only after the
         # asynchronous copy that read it has completed, so callers need not synchronise between steps
         self._tok_ring = torch.empty(64, dtype=torch.int32).pin_memory()
@@ -206,6 +207,7 @@ class RWKV_x070:
 
     def set_option(self, name: str, value: int) -> None:
         _lib.check(_lib.lib.ab_model_set_option(self._handle, name.encode(), int(value)), "ab_model_set_option")
+        self._options[name] = int(value)
         self._graphs.clear()
         self._programs.clear()
 
@@ -323,7 +325,8 @@ class RWKV_x070:
         """Per-phase (start, end) timestamps in ns of the last persistent decode step on `state`, as seen by
         block 0; needs set_option("timeline", 1) before the program for `state` was built."""
         prog, prog_ptr, _, _ = self._program_for(state)
-        n = 6 * self.n_layer + 1
+        per_block = 5 if self._options.get("merge_ups", 0) and self.n_head <= 148 else 6
+        n = per_block * self.n_layer + 1
         hdr = _lib.lib.ab_decode_timeline_offset(self._handle)
         off = (prog_ptr - prog.data_ptr()) + hdr
         torch.cuda.synchronize()

@@ -153,7 +153,16 @@ size_t ab_decode_timeline_offset(const ab_model* m);
 int ab_decode_program_build(ab_model* m, const int32_t* token, void* const* state, void* workspace, void* logits,
                             void* program, void* stream);
 int ab_decode_run(ab_model* m, void* program, void* stream);
-/* Tuning knobs: pipeline depth of the streaming kernels and programmatic dependent launch (default on). */
+/* Options (set before ab_decode_program_build for those of the persistent kernel):
+ *   "pdl" (1)             programmatic dependent launch between the kernels of a step
+ *   "debug_sync" (0)      synchronise and check after every launch
+ *   "timeline" (0)        persistent kernel records per-phase timestamps (ab_decode_timeline_offset)
+ *   "layer_offset" (0)    index of this model's first block in the whole network (pipeline stages)
+ *   "merge_ups" (0)       persistent kernel: adapter up-projections inside the per-head phase
+ *   "l2_prefetch_kb" (0), "smem_prefetch" (0), "early_slice" (0), "barrier_prefetch" (0)
+ *                         persistent kernel: ways of requesting the next phase's weights early; all measured
+ *                         slower than not doing it (they delay the loads of the phase's input vector)
+ *   "stages"              accepted and ignored */
 int ab_model_set_option(ab_model* m, const char* name, int value);
 
 #ifdef __cplusplus

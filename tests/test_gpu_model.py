@@ -115,6 +115,30 @@ def test_pipeline_stages_chain_to_the_full_model():
     assert torch.equal(st[0][1], st_full[1]) and torch.equal(st[1][1], st_full[4]) and len(st[0]) == 3
 
 
+@pytest.mark.parametrize("option", ["merge_ups", "l2_prefetch_kb", "smem_prefetch", "early_slice", "barrier_prefetch"])
+def test_persistent_kernel_options_do_not_change_results(option):
+    """The scheduling options of the persistent kernel move work between phases; logits stay the same
+    (bit for bit for the prefetch options, within fp32 summation order for the merged adapter phase)."""
+    model, args = model_for("0.1b", "int8")
+    toks = seeded_tokens(args.vocab_size, 6, seed=9)
+
+    def run(value):
+        model.set_option(option, value)
+        st, outs = None, []
+        for t in toks:
+            logits, st = model.forward(t, st)
+            outs.append(logits.float().clone())
+        return torch.stack(outs)
+
+    base = run(0)
+    alt = run(64 if option == "l2_prefetch_kb" else 1)
+    model.set_option(option, 0)
+    if option == "merge_ups":
+        assert rel_err(alt.cpu().numpy(), base.cpu().numpy()) < 2e-3
+    else:
+        assert torch.equal(alt, base)
+
+
 def test_state_is_updated_in_place_and_forkable():
     model, args = model_for("tiny", "int8")
     state = model.new_state()
