@@ -117,8 +117,9 @@ def test_pipeline_stages_chain_to_the_full_model():
 
 @pytest.mark.parametrize("option", ["merge_ups", "l2_prefetch_kb", "smem_prefetch", "early_slice", "barrier_prefetch"])
 def test_persistent_kernel_options_do_not_change_results(option):
-    """The scheduling options of the persistent kernel move work between phases; logits stay the same
-    (bit for bit for the prefetch options, within fp32 summation order for the merged adapter phase)."""
+    """The scheduling options of the persistent kernel move work between phases; logits stay the same: bit for bit
+    for the prefetch options. The merged adapter phase sums the up-projections in another order (fp32), which can
+    move an fp16 rounding; a randomly initialised network amplifies that with depth, so it gets the logit tolerance."""
     model, args = model_for("0.1b", "int8")
     toks = seeded_tokens(args.vocab_size, 6, seed=9)
 
@@ -134,7 +135,8 @@ def test_persistent_kernel_options_do_not_change_results(option):
     alt = run(64 if option == "l2_prefetch_kb" else 1)
     model.set_option(option, 0)
     if option == "merge_ups":
-        assert rel_err(alt.cpu().numpy(), base.cpu().numpy()) < 2e-3
+        err = rel_err(alt.cpu().numpy(), base.cpu().numpy())
+        assert err <= LOGIT_REL_TOL, err
     else:
         assert torch.equal(alt, base)
 
