@@ -158,7 +158,9 @@ int ab_decode_run(ab_model* m, void* program, void* stream);
  *   "debug_sync" (0)      synchronise and check after every launch
  *   "timeline" (0)        persistent kernel records per-phase timestamps (ab_decode_timeline_offset)
  *   "layer_offset" (0)    index of this model's first block in the whole network (pipeline stages)
- *   "merge_ups" (0)       persistent kernel: adapter up-projections inside the per-head phase
+ *   "merge_ups" (0)       persistent kernel: adapter up-projections inside the per-head phase instead of a phase
+ *                         of matrix-vector rows of their own (bit-identical to ab_forward at B = T = 1, 3 % slower;
+ *                         switches "smem_prefetch" and "barrier_prefetch" off)
  *   "l2_prefetch_kb" (0), "smem_prefetch" (0), "early_slice" (0), "barrier_prefetch" (0)
  *                         persistent kernel: ways of requesting the next phase's weights early; all measured
  *                         slower than not doing it (they delay the loads of the phase's input vector)

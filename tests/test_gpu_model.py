@@ -181,3 +181,19 @@ def test_config2_int8_decode_teacher_forced():
     assert worst <= LOGIT_REL_TOL, worst
     assert agree / (n_decode + 1) >= ARGMAX_AGREE, (agree, raw)
     assert raw / (n_decode + 1) >= 0.9, raw
+
+
+def test_batch1_modes_give_identical_logits():
+    """CUDA-graph replay and per-phase launches are the same kernels; the persistent kernel runs the same arithmetic
+    when its adapter up-projections are computed inside the head phase (option "merge_ups")."""
+    outs = []
+    for mode in ("persistent", "graph", "eager"):
+        model, args = model_for("0.1b", "int8", decode_mode=mode, use_graph=(mode != "eager"))
+        if mode == "persistent":
+            model.set_option("merge_ups", 1)
+        st, seq = None, []
+        for t in seeded_tokens(args.vocab_size, 5, seed=4):
+            logits, st = model.forward(t, st)
+            seq.append(logits.clone())
+        outs.append(torch.stack(seq))
+    assert torch.equal(outs[0], outs[2]) and torch.equal(outs[1], outs[2])
