@@ -452,7 +452,7 @@ def run_gemm(a, dev):
 # ----------------------------------------------------------------------------------------------
 # CPU arm: the oracle's restatement of the reference's PyTorch path on the host cores
 # ----------------------------------------------------------------------------------------------
-def run_cpu(a, n_layers_sample: int = 2, steps: int = 6):
+def run_cpu(a, n_layers_sample: int = 4, steps: int = 0):
     """Times the single-token path (the only one that is pure torch in the reference) in fp32.
 
     A 7.2B fp32 checkpoint is 28 GB, so the sample is `n_layers_sample` blocks plus the vocabulary head
@@ -461,6 +461,7 @@ def run_cpu(a, n_layers_sample: int = 2, steps: int = 6):
     from oracle.rwkv7_oracle import Oracle, new_state, prepare
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
+    steps = steps or max(6, min(a.steps, 32))
     L, D, V, ranks = synth.CONFIGS[a.model]
     Ls = min(L, n_layers_sample)
     raw = synth.make_checkpoint((Ls, D, V, ranks), seed=0)
