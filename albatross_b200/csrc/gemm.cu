@@ -15,10 +15,13 @@
 //               128-byte swizzle the MMA expects. One warp per scheduler cannot hide the latencies of this
 //               serial instruction stream; several groups on different k-steps can. Afterwards all groups
 //               run the epilogue: tcgen05.ld of 32 columns of their 32 TMEM lanes, row / tensor scale,
-//               activation or residual, fp16 stores (a warp writes 32 consecutive output features);
+//               activation or residual; the fp16 tile is laid out in shared memory and leaves through TMA stores
+//               (a residual tile comes in through TMA loads); products with a ragged row pitch store directly;
 //   next warp : one thread issues the TMA loads of the activation tile (tensor map over X, 128B swizzle);
 //   last warp : allocates TMEM; one thread issues tcgen05.mma (kind::f16) and commits to mbarriers.
-// Three-stage operand ring, all mbarrier waits bounded (status word on expiry), TMEM freed on every path.
+// Three-stage operand ring, all waits bounded (status word on expiry), TMEM freed on every path. Short grids with
+// long K loops are split along K (fp32 partial tiles in a scratch area, summed in a fixed order). Launched with
+// programmatic stream serialisation the kernel starts its weight stream before it waits for its predecessor.
 #include <cuda.h>
 
 #include <type_traits>
@@ -112,15 +115,6 @@ __device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uin
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
         : "memory");
 }
-__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t* v) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-        : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* v) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
