@@ -38,26 +38,29 @@ __device__ __forceinline__ void red_release_add(unsigned* p, unsigned v) {
 // it neither delays the arrival nor shares the memory pipeline with the loads that follow the barrier.
 template <class F>
 __device__ __forceinline__ void grid_barrier(unsigned* counter, unsigned target, int tid, bool& failed, F while_waiting) {
-    __shared__ int s_ok;
+    __shared__ volatile int s_done, s_ok;
     cons_sync();   // every thread of the block has issued its writes of this phase
-    if (tid == 0 && !failed) red_release_add(counter, 1u);
-    while_waiting();
     if (tid == 0) {
-        int ok = 1;
-        if (!failed) {
-            uint32_t it = 0;
-            while (ld_acquire_u32(counter) < target) {
-                if (++it > (1u << 23)) {
-                    ok = 0;
-                    atomicOr(&g_device_status, DEV_WAIT_HEAD);
-                    break;
-                }
+        s_done = 0;
+        s_ok = failed ? 0 : 1;
+        if (!failed) red_release_add(counter, 1u);
+    }
+    while_waiting();
+    // Four pollers (lane 0 of warps 0-3), a fifth of a round trip apart: the block notices the last arrival a
+    // fraction of an L2 round trip after it happened instead of up to a whole one.
+    cons_sync();
+    if ((tid & 31) == 0 && tid < 128 && !failed) {
+        if (tid) __nanosleep((unsigned)(tid >> 5) * 160u);
+        uint32_t it = 0;
+        while (!s_done) {
+            if (ld_acquire_u32(counter) >= target) break;
+            if (++it > (1u << 23)) {
+                s_ok = 0;
+                atomicOr(&g_device_status, DEV_WAIT_HEAD);
+                break;
             }
-            __threadfence();
-        } else {
-            ok = 0;
         }
-        s_ok = ok;
+        s_done = 1;
     }
     cons_sync();
     if (!s_ok) failed = true;
