@@ -53,8 +53,14 @@ __host__ __device__ inline int gemv_groups_of(int n_rows) { return (n_rows + GEM
 // Relative cost of one row group: blocks get equal cost, not equal bytes, because NVFP4 rows take more
 // instructions per byte than int8 rows. fp16 rows cost what int8 rows cost per byte (measured per work item in
 // the r/k/v + adapter phase of the persistent kernel: 0.24 us vs 0.23 us per 8 KiB item).
+// Rows shorter than a slice (the adapter up-projections, K = rank) cost in proportion to their bytes, with a floor
+// for the fixed work per item.
 __host__ __device__ inline int gemv_group_cost(int fmt, int K) {
-    return gemv_slices(fmt, K) * (fmt == FMT_FP4 ? 4 : 2);
+    const int per_slice = fmt == FMT_FP4 ? 32 : 16;
+    const int rb = gemv_row_bytes(fmt, K);
+    if (rb >= GEMV_SLICE_BYTES) return gemv_slices(fmt, K) * per_slice;
+    const int c = (per_slice * rb + GEMV_SLICE_BYTES - 1) / GEMV_SLICE_BYTES;
+    return c < per_slice / 4 ? per_slice / 4 : c;
 }
 // Shared-memory bytes of one segment's prepared input (int8: high + low bytes; otherwise fp16).
 __host__ __device__ inline int gemv_xq_bytes(int K) { return 2 * ((K + 511) & ~511); }
