@@ -6,7 +6,7 @@ Importing the model needs the built library (python -m albatross_b200.build).
 """
 import importlib
 
-__all__ = ["RWKV_x070", "RWKV7_OP", "RWKV7_BATCH_OP"]
+__all__ = ["RWKV_x070", "RWKV7_OP", "RWKV7_BATCH_OP", "sampler_simple_batch"]
 
 
 def __getattr__(name):

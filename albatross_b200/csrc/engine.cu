@@ -486,6 +486,10 @@ int ab_gemm(const ab_mat* m, int rows, const void* x, void* y, int epi, const vo
     return gemm_launch(*m, rows, (const __half*)x, (__half*)y, epi, (const __half*)resid, scratch, (cudaStream_t)stream);
 }
 
+int ab_sample_rows(const void* logits, int rows, int vocab, float noise, uint32_t seed, int32_t* out, void* stream) {
+    return sample_rows((const __half*)logits, rows, vocab, noise, seed, out, (cudaStream_t)stream);
+}
+
 int ab_dequant(const ab_mat* m, float* out, void* stream) {
     AB_CHECK_ARG(m, "ab_dequant: null pointer");
     return dequant_launch(*m, out, (cudaStream_t)stream);

@@ -142,6 +142,53 @@ __global__ void __launch_bounds__(RT) ln_mix_rows_kernel(const __half* __restric
     }
 }
 
+// Greedy / noisy-greedy sampling of one token per row: argmax over the row of logit + U(0, noise)
+// (reference/utils.py:43-45 adds uniform noise and takes the first entry of a descending argsort). Ties go to the
+// lowest index. The noise is a counter-based hash of (seed, row, column): reproducible, not torch's generator.
+__device__ __forceinline__ float sample_noise(uint32_t seed, uint32_t row, uint32_t col) {
+    uint32_t x = seed ^ (row * 0x9E3779B9u) ^ (col * 0x85EBCA6Bu);
+    x ^= x >> 16; x *= 0x7FEB352Du; x ^= x >> 15; x *= 0x846CA68Bu; x ^= x >> 16;
+    return (float)(x >> 8) * (1.0f / 16777216.0f);   // [0, 1)
+}
+__global__ void __launch_bounds__(RT) sample_rows_kernel(const __half* __restrict__ logits, int V, float noise, uint32_t seed,
+                                                         int* __restrict__ out) {
+    __shared__ float bv[RT / 32];
+    __shared__ int bi[RT / 32];
+    const size_t row = blockIdx.x;
+    const __half* lr = logits + row * V;
+    float best = -INFINITY;
+    int idx = 0x7fffffff;
+    auto take = [&](float v, int i) {
+        if (noise > 0.f) v += noise * sample_noise(seed, (uint32_t)row, (uint32_t)i);
+        if (v > best || (v == best && i < idx)) { best = v; idx = i; }
+    };
+    const int nv = (V % 8 == 0 && ((uintptr_t)lr & 15) == 0) ? V / 8 : 0;
+    for (int c = threadIdx.x; c < nv; c += RT) {
+        const uint4 q = reinterpret_cast<const uint4*>(lr)[c];
+        const __half2* h = reinterpret_cast<const __half2*>(&q);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = __half22float2(h[e]);
+            take(f.x, c * 8 + 2 * e);
+            take(f.y, c * 8 + 2 * e + 1);
+        }
+    }
+    for (int i = nv * 8 + threadIdx.x; i < V; i += RT) take(__half2float(lr[i]), i);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { bv[threadIdx.x >> 5] = best; bi[threadIdx.x >> 5] = idx; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < RT / 32; ++w)
+            if (bv[w] > best || (bv[w] == best && bi[w] < idx)) { best = bv[w]; idx = bi[w]; }
+        out[row] = idx;
+    }
+}
+
 // x_prev[b] = xn[b, T-1]
 __global__ void __launch_bounds__(RT) last_rows_kernel(const __half* __restrict__ xn, int T, int D, __half* __restrict__ x_prev) {
     const size_t b = blockIdx.x;
@@ -169,6 +216,12 @@ bool ln_mix_rows_ok(const MixParams& p) { return p.T == 1 && p.D % 8 == 0 && p.D
 int ln_mix_rows(const __half* x, const __half* w, const __half* b, const MixParams& p, cudaStream_t s) {
     AB_CHECK_ARG(x && w && b && p.x_prev && p.n_mix >= 1 && p.n_mix <= 6 && p.B > 0 && ln_mix_rows_ok(p), "ln_mix_rows: bad argument");
     ln_mix_rows_kernel<<<p.B, RT, 0, s>>>(x, w, b, p);
+    AB_CUDA(cudaGetLastError());
+    return OK;
+}
+int sample_rows(const __half* logits, int rows, int V, float noise, uint32_t seed, int* out, cudaStream_t s) {
+    AB_CHECK_ARG(logits && out && rows > 0 && V > 0 && noise >= 0.f, "sample_rows: bad argument");
+    sample_rows_kernel<<<rows, RT, 0, s>>>(logits, V, noise, seed, out);
     AB_CUDA(cudaGetLastError());
     return OK;
 }

@@ -65,6 +65,16 @@ def RWKV7_BATCH_OP(state, r, w, k, v, a, b):
     return _wkv(B, T, C_, state, r, w, k, v, a, b)
 
 
+def sampler_simple_batch(logits: torch.Tensor, noise: float = 1.0, seed: int = 0) -> torch.Tensor:
+    """Next-token ids [B, 1] (int64) from fp16 logits [B, V] on the device: argmax of logits + U(0, noise), as
+    reference/utils.py:43-45 computes with an argsort. `seed` selects the noise (vary it per step)."""
+    assert logits.dim() == 2 and logits.dtype == DTYPE and logits.is_cuda and logits.is_contiguous()
+    out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
+    _lib.check(_lib.lib.ab_sample_rows(logits.data_ptr(), logits.shape[0], logits.shape[1], float(noise), int(seed) & 0xFFFFFFFF,
+                                       out.data_ptr(), torch.cuda.current_stream().cuda_stream), "ab_sample_rows")
+    return out.to(torch.int64).unsqueeze(1)
+
+
 # --------------------------------------------------------------------------------------------
 # Model
 # --------------------------------------------------------------------------------------------

@@ -117,6 +117,13 @@ int ab_gemm(const ab_mat* m, int rows, const void* x, void* y, int epi, const vo
 #define AB_GEMM_STATIC_SCRATCH_BYTES (8u * 1024u * 1024u)
 int ab_gemm_static(const ab_mat* m, int rows, const void* x, void* y, int epi, const void* resid, void* stream);
 
+/* ---- token sampling on the device -----------------------------------------------------------
+ * Replaces sampler_simple_batch (reference/utils.py:43-45: uniform noise in [0, noise) added to the logits, then
+ * the first column of a descending argsort) without sorting and without leaving the device: out[r] = argmax over
+ * the row of logits[r, :] + U(0, noise), ties to the lowest index. logits fp16 [rows, vocab], out int32 [rows].
+ * noise == 0 is plain greedy decoding. The noise is a hash of (seed, row, column), not torch's generator. */
+int ab_sample_rows(const void* logits, int rows, int vocab, float noise, uint32_t seed, int32_t* out, void* stream);
+
 /* ---- de-quantisation dump (parity checks) ---------------------------------------------------
  * Writes the kernels' in-register de-quantised weights as fp32 [n_out,k] (tensor/row/column scales applied). */
 int ab_dequant(const ab_mat* m, float* out, void* stream);

@@ -178,3 +178,27 @@ def test_batched_product_small_k_and_epilogues():
                     (_lib.EPI_RELU2, lambda v: np.maximum(v, 0) ** 2), (_lib.EPI_RESID, lambda v: v + resid.double().numpy())):
         got = _gemm(pm, x.cuda(), epi, resid.cuda() if epi == _lib.EPI_RESID else None).float().cpu().numpy()
         assert rel_err(got, fn(base)) < 4e-3
+
+
+def test_device_sampler_matches_argsort():
+    """ab_sample_rows: noise 0 is the arg-max the reference takes from a descending argsort; with noise the chosen
+    logit is within `noise` of the row maximum and the draw is reproducible per seed."""
+    from albatross_b200 import sampler_simple_batch
+    torch.manual_seed(2)
+    for rows, V in ((1, 65536), (320, 65536), (7, 1000), (3, 37)):
+        logits = (torch.randn(rows, V, device="cuda") * 3).half()
+        logits[0, min(V - 1, 11)] = logits[0].max() + 1                       # a clear winner in row 0
+        got = sampler_simple_batch(logits, noise=0.0)
+        want = torch.argsort(logits.float(), dim=-1, descending=True, stable=True)[:, :1]
+        assert got.shape == (rows, 1) and got.dtype == torch.int64
+        assert torch.equal(got, want)
+        a = sampler_simple_batch(logits, noise=1.0, seed=5)
+        b = sampler_simple_batch(logits, noise=1.0, seed=5)
+        c = sampler_simple_batch(logits, noise=1.0, seed=6)
+        assert torch.equal(a, b)
+        picked = logits.float().gather(1, a)
+        assert (picked >= logits.float().max(dim=1, keepdim=True).values - 1.0).all()
+        if rows * V > 100000:
+            assert not torch.equal(a, c)
+    ties = torch.zeros(2, 64, device="cuda").half()
+    assert sampler_simple_batch(ties, noise=0.0).flatten().tolist() == [0, 0]  # ties go to the lowest index
