@@ -9,8 +9,8 @@ state update between them and the vocabulary head) for the workload's batch. Wei
 (seeded, reference checkpoint schema), since trained checkpoints are not available offline.
 
 Prints ONE JSON line. `value` is device-timed (CUDA events, inputs resident in HBM, CUDA-graph
-replay of the library's launches); `e2e` goes through the public `RWKV_x070.forward[_batch]` call with
-host token ids (pinned host -> device) and reads the logits back to the host every step.
+replay of the library's launches); `e2e` is a decode loop through the public calls: `RWKV_x070.forward[_batch]`
+on host token ids (pinned host -> device), greedy sampling on the device, next ids read back to the host, every step.
 `--impl reference` times the CPU restatement of the reference's PyTorch path (oracle/) on the host
 cores on a bounded sample of the same workload.
 """
@@ -179,17 +179,20 @@ def run_ours(a, rank, world, dev):
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
         return float(t.item())
 
-    # ---- e2e: the public call, host token ids in, logits back on the host, every step
-    pinned_logits = torch.empty((B, V) if B > 1 else (V,), dtype=torch.float16).pin_memory()
+    # ---- e2e: the public calls of a decode loop, every step: host token ids in (pinned -> device), forward, greedy
+    # sampling on the device (the library's replacement for the reference's argsort sampler), ids back on the host
+    from albatross_b200 import sampler_simple_batch
+    pinned_ids = torch.empty((B, 1), dtype=torch.int64).pin_memory()
     state = model.new_state(B if B > 1 else None)
 
     def e2e_step(i):
         nonlocal state
         if B == 1:
             logits, state = model.forward(int(toks[i, 0]), state)
+            logits = logits.unsqueeze(0)
         else:
             logits, state = model.forward_batch([[int(t)] for t in toks[i]], state)
-        pinned_logits.copy_(logits, non_blocking=True)
+        pinned_ids.copy_(sampler_simple_batch(logits, noise=0.0), non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
     for i in range(a.warmup):
@@ -278,8 +281,9 @@ def run_ours(a, rank, world, dev):
         "config": {"workload": a.workload, "model": a.model, "batch_per_gpu": B, "n_layer": args.n_layer,
                    "n_embd": args.n_embd, "vocab": V, "sharding": "independent sequences per GPU, no collective in the step",
                    "l2": "inputs larger than L2: %.2f GB of weights streamed per step" % (ab["weights"] / 1e9)},
-        "e2e": {"value": e2e_val, "unit": "tokens/s", "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 2 * B * V,
-                "ms_per_step": e2e_ms / a.steps},
+        "e2e": {"value": e2e_val, "unit": "tokens/s", "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 8 * B,
+                "ms_per_step": e2e_ms / a.steps,
+                "what": "RWKV_x070.forward[_batch] on host token ids + sampler_simple_batch on the device + ids to the host"},
         "gpu_launches": launches_per_step * a.steps,
         "roofline": roofline,
         "clocks": clocks, "device_status": status,
