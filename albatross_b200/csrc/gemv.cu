@@ -3,6 +3,9 @@
 // Replaces the reference's fp16 `x @ W` GEMV call sites at batch 1
 // (reference/rwkv7.py:230-235, :240, :250 time-mix; :308-309 channel-mix; :156 vocabulary head).
 // The device code lives in gemv_body.cuh; this file holds the stand-alone kernel and its launcher.
+#include <algorithm>
+#include <vector>
+
 #include "gemv_body.cuh"
 
 namespace ab {
@@ -130,3 +133,53 @@ int gemv_launch(const GemvParams& p_in, cudaStream_t stream) {
 }
 
 }  // namespace ab
+
+// Host-side self-check of the block partition (no GPU needed): every row group of every segment is owned by exactly
+// one block, a block's share of a segment is one contiguous run, and the per-block counts stay inside the kernel's
+// limits. Returns OK or ERR_BAD_ARG with a message; `max_items` / `max_cost_spread_pct` (optional) report the largest
+// item count of a block and how far the most loaded block is above the mean cost, in percent.
+extern "C" int ab_gemv_plan_selftest(const int32_t* fmt, const int32_t* n_rows, const int32_t* k, int nseg, int n_blocks,
+                                     int32_t* max_items, int32_t* max_cost_spread_pct) {
+    using namespace ab;
+    AB_CHECK_ARG(fmt && n_rows && k && nseg >= 1 && nseg <= GEMV_MAX_SEG && n_blocks >= 1, "plan selftest: bad argument");
+    GemvParams p = {};
+    p.nseg = nseg;
+    for (int s = 0; s < nseg; ++s) {
+        AB_CHECK_ARG(n_rows[s] > 0 && k[s] > 0 && fmt[s] >= FMT_F16 && fmt[s] <= FMT_FP4, "plan selftest: bad segment %d", s);
+        p.seg[s].fmt = fmt[s]; p.seg[s].n_rows = n_rows[s]; p.seg[s].K = k[s];
+    }
+    std::vector<int> next(nseg, 0);
+    long long total_cost = 0, worst = 0;
+    int items_max = 0;
+    for (int b = 0; b < n_blocks; ++b) {
+        BlockPlan bp;
+        compute_plan(p, b, n_blocks, bp);
+        long long cost = 0;
+        int items = 0, rows = 0;
+        for (int s = 0; s < nseg; ++s) {
+            const SegPlan& q = bp.sp[s];
+            AB_CHECK_ARG(q.n_groups >= 0, "plan selftest: negative share (block %d segment %d)", b, s);
+            if (q.n_groups > 0)
+                AB_CHECK_ARG(q.lo == next[s], "plan selftest: block %d segment %d starts at group %d, expected %d", b, s, q.lo, next[s]);
+            if (q.n_groups > 0) next[s] = q.lo + q.n_groups;
+            AB_CHECK_ARG(q.npc * q.chunk == q.nks && q.item_base == items && q.row_base == rows,
+                         "plan selftest: inconsistent item layout (block %d segment %d)", b, s);
+            items += q.n_groups * q.npc;
+            rows += q.n_groups * GEMV_ROWS;
+            cost += (long long)q.n_groups * gemv_group_cost(fmt[s], k[s]);
+        }
+        AB_CHECK_ARG(items == bp.n_items && rows == bp.n_rows, "plan selftest: totals of block %d do not add up", b);
+        items_max = std::max(items_max, items);
+        worst = std::max(worst, cost);
+        total_cost += cost;
+    }
+    for (int s = 0; s < nseg; ++s)
+        AB_CHECK_ARG(next[s] == gemv_groups_of(n_rows[s]), "plan selftest: segment %d covered up to group %d of %d", s, next[s],
+                     gemv_groups_of(n_rows[s]));
+    if (max_items) *max_items = items_max;
+    if (max_cost_spread_pct) {
+        const double mean = (double)total_cost / n_blocks;
+        *max_cost_spread_pct = mean > 0 ? (int)((worst / mean - 1.0) * 100.0 + 0.5) : 0;
+    }
+    return OK;
+}

@@ -86,6 +86,12 @@ int ab_wkv7_fwd(int B, int T, int C, int H, float* state, const void* r, const v
  * with de-quantisation fused into the product. x fp16 [k], y fp16 [n_out]. */
 int ab_gemv(const ab_mat* m, const void* x, void* y, void* stream);
 
+/* Host-only self-check of how ab_gemv and the persistent kernel split a list of matrices between `n_blocks` blocks
+ * (all arrays are HOST arrays of `nseg` entries: weight format, output rows, input length): every group of four
+ * rows is owned by exactly one block and a block's share of a matrix is contiguous. Runs without a GPU. */
+int ab_gemv_plan_selftest(const int32_t* fmt, const int32_t* n_rows, const int32_t* k, int nseg, int n_blocks,
+                          int32_t* max_items, int32_t* max_cost_spread_pct);
+
 /* ---- batched matrix products (tensor cores) -----------------------------------------------
  * Replace the `[B,T,D] @ W` call sites of the batch path (reference/rwkv7.py:283,285,286,300,322,323,220).
  * x fp16 [rows, k] row-major, y fp16 [rows, n_out]; epi is one of AB_EPI_*; resid (fp16 [rows,n_out])
