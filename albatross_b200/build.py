@@ -50,5 +50,27 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+def resource_usage(log_path: str = os.path.join(OUT_DIR, "build.log")) -> dict:
+    """Per kernel: registers and spill bytes as ptxas reported them in the last build (kernel name -> dict).
+
+    The streaming kernels sit at their register cap (128 registers x 512 threads); a spill in them costs tens of
+    percent of decode throughput, so the tests keep an eye on this."""
+    import re
+    out, name = {}, None
+    for line in open(log_path):
+        m = re.search(r"Compiling entry function '(\S+)'", line)
+        if m:
+            name = m.group(1)
+            continue
+        m = re.search(r"(\d+) bytes stack frame, (\d+) bytes spill stores, (\d+) bytes spill loads", line)
+        if m and name:
+            out.setdefault(name, {})["spill_bytes"] = int(m.group(2)) + int(m.group(3))
+            continue
+        m = re.search(r"Used (\d+) registers", line)
+        if m and name:
+            out.setdefault(name, {})["registers"] = int(m.group(1))
+    return out
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))

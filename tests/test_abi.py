@@ -40,3 +40,15 @@ def test_python_struct_layout_matches_header():
     from albatross_b200 import _lib
     assert ctypes.sizeof(_lib.Mat) == 48
     assert ctypes.sizeof(_lib.Layer) == 19 * 8 + 10 * 48 + 4 * 8 + 4 * 48
+
+
+def test_streaming_kernels_do_not_spill():
+    """The batch-1 kernels run at their register cap; a spill in them (easily introduced by code added to the
+    persistent kernel) slows every matrix-vector phase, so the build's ptxas report is checked."""
+    from albatross_b200 import build
+    build.build(force=True)
+    usage = build.resource_usage()
+    hot = {k: v for k, v in usage.items() if "decode_kernel" in k or "gemv_stream_kernel" in k or "head_batch_kernel" in k}
+    assert len(hot) == 3, sorted(usage)
+    for name, u in hot.items():
+        assert u["spill_bytes"] == 0, (name, u)
