@@ -278,7 +278,7 @@ def run_ours(a, rank, world, dev):
         "dtype": "int8 weights (dp4a, exact int32 sums), fp16 activations, fp32 WKV state" if wl["quant"] == "int8"
         else "nvfp4 weights de-quantised to fp16 in registers, fp16 activations, fp32 accumulate and WKV state",
         "data": "synthetic (seeded random weights in the reference checkpoint schema, random token ids)",
-        "config": {"workload": a.workload, "model": a.model, "batch_per_gpu": B, "n_layer": args.n_layer,
+        "config": {"workload": a.workload, "shapes": a.model, "batch_per_gpu": B, "n_layer": args.n_layer,
                    "n_embd": args.n_embd, "vocab": V, "sharding": "independent sequences per GPU, no collective in the step",
                    "l2": "inputs larger than L2: %.2f GB of weights streamed per step" % (ab["weights"] / 1e9)},
         "e2e": {"value": e2e_val, "unit": "tokens/s", "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 8 * B,
@@ -354,7 +354,7 @@ def run_pipeline(a, rank, world, dev):
             "warmup": a.warmup, "ms_per_step": total_ms / a.steps, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "nvfp4 weights de-quantised to fp16 in registers, fp16 activations, fp32 accumulate and WKV state",
             "data": "synthetic (seeded random weights in the reference checkpoint schema, random token ids)",
-            "config": {"workload": a.workload, "model": a.model, "global_batch": B, "micro_batches": M, "stages": world,
+            "config": {"workload": a.workload, "shapes": a.model, "global_batch": B, "micro_batches": M, "stages": world,
                        "blocks_per_stage": hi - lo, "exchange": "x and v_first, [%d, %d] fp16 each, NCCL send/recv per micro-batch and stage boundary; "
                        "token ids int64 [%d] back to stage 0" % (b, D, b)},
             "e2e": None, "gpu_launches": (8 * (hi - lo) + 2) * M * a.steps, "roofline": None, "clocks": clocks,
@@ -522,7 +522,7 @@ def main():
             "impl": "reference", "metric": METRIC, "value": cb["value"], "unit": "tokens/s", "n_gpus": a.gpus,
             "steps": a.steps, "warmup": a.warmup, "ms_per_step": 1e3 / cb["value"], "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "fp32 (CPU)", "data": "synthetic",
-            "config": {"workload": a.workload, "model": a.model, "batch_per_gpu": B},
+            "config": {"workload": a.workload, "shapes": a.model, "batch_per_gpu": B},
             "cpu_baseline": cb,
             "e2e": {"value": cb["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
         return
