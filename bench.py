@@ -2,7 +2,8 @@
 """Decode benchmark for the RWKV-7 quantised-weight hot path.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload decode_bsz1_int8|decode_bsz320_nvfp4] [--model 7.2b|0.1b|tiny]
+                    [--workload decode_bsz1_int8|decode_bsz320_nvfp4|decode_bsz1_nvfp4|pipeline_bsz320_nvfp4|gemv_*|gemm_*]
+                    [--model 7.2b|0.1b|tiny]
 
 One "step" is one decode step of the whole model (every matrix product of the 32 blocks, the WKV-7
 state update between them and the vocabulary head) for the workload's batch. Weights are random
@@ -33,6 +34,7 @@ sys.path.insert(0, ROOT)
 WORKLOADS = {
     "decode_bsz1_int8": dict(batch=1, quant="int8"),
     "decode_bsz320_nvfp4": dict(batch=320, quant="nvfp4"),
+    "decode_bsz1_nvfp4": dict(batch=1, quant="nvfp4"),
     "pipeline_bsz320_nvfp4": dict(batch=320, quant="nvfp4"),   # layer pipeline: one stage per rank (torchrun, N >= 2)
     "gemv_int8": dict(batch=1, quant="int8"),
     "gemv_nvfp4": dict(batch=1, quant="nvfp4"),
