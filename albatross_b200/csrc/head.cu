@@ -112,9 +112,18 @@ constexpr int HB_BLOCKS = HB_BLOCKS_;   // resident blocks per SM
 constexpr int HB_THREADS = HT + 64;
 constexpr int HB_STATE_BYTES = 64 * 64 * 4;
 
+// Vectors of one recurrence step. r, k, a, b are fp16 values anyway (each is the result of an fp16-rounded op), so
+// they are kept as fp16: every thread reads 16 elements of each per item, and the shared-memory pipe, not HBM, paces
+// the step; 8-byte instead of 16-byte reads take half the wavefronts. The decay w is fp32.
 struct HeadVec {
-    float r[64], w[64], k[64], a[64], b[64], v[64];
+    float w[64], v[64];
+    __half r[64], k[64], a[64], b[64];
 };
+__device__ __forceinline__ float4 ld_h4(const __half* p) {   // four consecutive fp16 -> float4
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&u.x)), hi = __half22float2(*reinterpret_cast<const __half2*>(&u.y));
+    return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
 struct HeadPost {   // what the output stage needs from the input stage
     float v[64];
     float rkr;
@@ -212,7 +221,7 @@ __global__ void __launch_bounds__(HB_THREADS, HB_BLOCKS) head_batch_kernel(const
                 const float k2 = rh(kr[e] * rh(1.f + rh(rh(aa - 1.f) * ka_[e])));
                 // decay in fp32 as on the reference's single-token path (reference/rwkv7.py:241)
                 const float wd = __expf(-0.606531f * sigmoidf_(rh(w0_[e] + w_raw[e])));
-                o.r[c] = rr[e]; o.w[c] = wd; o.k[c] = k2; o.v[c] = vv[e];
+                o.r[c] = __float2half_rn(rr[e]); o.w[c] = wd; o.k[c] = __float2half_rn(k2); o.v[c] = vv[e];
                 po.v[c] = vv[e];
                 av[e] = aa;
                 rkr += rh(rh(rr[e] * k2) * rk_[e]);
@@ -223,8 +232,8 @@ __global__ void __launch_bounds__(HB_THREADS, HB_BLOCKS) head_batch_kernel(const
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const float kk = rh(kk0[e] / nrm);
-                o.a[2 * lane + e] = -kk;
-                o.b[2 * lane + e] = rh(kk * av[e]);
+                o.a[2 * lane + e] = __float2half_rn(-kk);
+                o.b[2 * lane + e] = __float2half_rn(kk * av[e]);
             }
             if (lane == 0) po.rkr = rkr;
         };
@@ -290,7 +299,7 @@ __global__ void __launch_bounds__(HB_THREADS, HB_BLOCKS) head_batch_kernel(const
             float sa = 0.f;
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const float4 a4 = *reinterpret_cast<const float4*>(cv.a + 16 * ((e + i) & 3) + 4 * q);
+                const float4 a4 = ld_h4(cv.a + 16 * ((e + i) & 3) + 4 * q);
                 sa = fmaf(a4.x, st[e].x, sa); sa = fmaf(a4.y, st[e].y, sa);
                 sa = fmaf(a4.z, st[e].z, sa); sa = fmaf(a4.w, st[e].w, sa);
             }
@@ -301,8 +310,8 @@ __global__ void __launch_bounds__(HB_THREADS, HB_BLOCKS) head_batch_kernel(const
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int c0 = 16 * ((e + i) & 3) + 4 * q;
-                const float4 w4 = *reinterpret_cast<const float4*>(cv.w + c0), k4 = *reinterpret_cast<const float4*>(cv.k + c0);
-                const float4 b4 = *reinterpret_cast<const float4*>(cv.b + c0), r4 = *reinterpret_cast<const float4*>(cv.r + c0);
+                const float4 w4 = *reinterpret_cast<const float4*>(cv.w + c0), k4 = ld_h4(cv.k + c0);
+                const float4 b4 = ld_h4(cv.b + c0), r4 = ld_h4(cv.r + c0);
                 float4 o;
                 o.x = fmaf(st[e].x, w4.x, fmaf(k4.x, v_i, sa * b4.x)); y = fmaf(o.x, r4.x, y);
                 o.y = fmaf(st[e].y, w4.y, fmaf(k4.y, v_i, sa * b4.y)); y = fmaf(o.y, r4.y, y);
