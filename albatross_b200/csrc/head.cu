@@ -181,29 +181,37 @@ __global__ void __launch_bounds__(HB_THREADS, HB_BLOCKS) head_batch_kernel(const
             pdl_wait();
             pdl_launch_dependents();
         }
-        struct Act { float2 r, k, v, w_raw, a_raw, vg_raw, vf; };
+        // Everything the input stage reads from global memory, activations and per-channel parameters alike, is
+        // requested one item ahead and kept packed (two fp16 per register): the stage is on the critical path of the
+        // block (item n+1 cannot start before it is done), so it must not wait for a load.
+        struct Act { __half2 r, k, v, w_raw, a_raw, vg_raw, vf, a0, k_k, k_a, w0, r_k, v0; };
+        auto ldh2a = [](const __half* q) { return __ldcg(reinterpret_cast<const __half2*>(q)); };
+        auto ldh2p = [](const __half* q) { return __ldg(reinterpret_cast<const __half2*>(q)); };
         auto fetch = [&](int n, Act& a) {
             const size_t o = off_of(n) + 2 * lane;
-            a.r = ld2a(p.r + o); a.k = ld2a(p.k + o); a.v = ld2a(p.v + o);
-            a.w_raw = ld2a(p.w_raw + o); a.a_raw = ld2a(p.a_raw + o);
-            if (!p.layer0) { a.vg_raw = ld2a(p.vg_raw + o); a.vf = ld2a(p.v_first + o); }
+            const int gc = (item_of(n) % p.H) * 64 + 2 * lane;
+            a.r = ldh2a(p.r + o); a.k = ldh2a(p.k + o); a.v = ldh2a(p.v + o);
+            a.w_raw = ldh2a(p.w_raw + o); a.a_raw = ldh2a(p.a_raw + o);
+            a.a0 = ldh2p(p.a0 + gc); a.k_k = ldh2p(p.k_k + gc); a.k_a = ldh2p(p.k_a + gc);
+            a.w0 = ldh2p(p.w0 + gc); a.r_k = ldh2p(p.r_k + gc);
+            if (!p.layer0) { a.vg_raw = ldh2a(p.vg_raw + o); a.vf = ldh2a(p.v_first + o); a.v0 = ldh2p(p.v0 + gc); }
         };
         // reference/rwkv7.py:284-297 for one (sequence, head)
         auto glue = [&](int n, const Act& a, HeadVec& o, HeadPost& po) {
-            const int it = item_of(n), h = it % p.H;
-            const int gc = h * 64 + 2 * lane;
-            const float2 a0 = ld2p(p.a0 + gc), k_k = ld2p(p.k_k + gc), k_a = ld2p(p.k_a + gc);
-            const float2 w0 = ld2p(p.w0 + gc), r_k = ld2p(p.r_k + gc);
-            const float rr[2] = {a.r.x, a.r.y}, kr[2] = {a.k.x, a.k.y};
-            float vv[2] = {a.v.x, a.v.y};
-            const float a_raw[2] = {a.a_raw.x, a.a_raw.y}, w_raw[2] = {a.w_raw.x, a.w_raw.y};
+            const float2 fr = __half22float2(a.r), fk = __half22float2(a.k), fv = __half22float2(a.v);
+            const float2 fwr = __half22float2(a.w_raw), far = __half22float2(a.a_raw);
+            const float2 a0 = __half22float2(a.a0), k_k = __half22float2(a.k_k), k_a = __half22float2(a.k_a);
+            const float2 w0 = __half22float2(a.w0), r_k = __half22float2(a.r_k);
+            const float rr[2] = {fr.x, fr.y}, kr[2] = {fk.x, fk.y};
+            float vv[2] = {fv.x, fv.y};
+            const float a_raw[2] = {far.x, far.y}, w_raw[2] = {fwr.x, fwr.y};
             const float a0_[2] = {a0.x, a0.y}, kk_[2] = {k_k.x, k_k.y}, ka_[2] = {k_a.x, k_a.y};
             const float w0_[2] = {w0.x, w0.y}, rk_[2] = {r_k.x, r_k.y};
             if (p.layer0) {
                 *reinterpret_cast<__half2*>(p.v_first + off_of(n) + 2 * lane) = __floats2half2_rn(vv[0], vv[1]);
             } else {
-                const float2 v0 = ld2p(p.v0 + gc);
-                const float v0_[2] = {v0.x, v0.y}, vg_raw[2] = {a.vg_raw.x, a.vg_raw.y}, vf[2] = {a.vf.x, a.vf.y};
+                const float2 v0 = __half22float2(a.v0), fvg = __half22float2(a.vg_raw), fvf = __half22float2(a.vf);
+                const float v0_[2] = {v0.x, v0.y}, vg_raw[2] = {fvg.x, fvg.y}, vf[2] = {fvf.x, fvf.y};
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                     const float vg = rh(sigmoidf_(rh(v0_[e] + vg_raw[e])));
