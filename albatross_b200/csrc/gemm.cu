@@ -580,29 +580,26 @@ __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ 
             const uint64_t a_stage = (uint64_t)(G_A_BYTES >> 4), b_stage = (uint64_t)(b_bytes >> 4);
             const uint64_t b_half = (uint64_t)((g.n_first * 128) >> 4);
             const uint32_t d1 = tmem_base + (uint32_t)g.n_first;
-            int s = 0;
+            // unrolled over the stages: stage index, descriptors and barrier addresses are compile-time offsets
             uint32_t parity = 0;
-            uint64_t da = da0, db = db0;
-            for (int ks = 0; ks < n_ksteps; ++ks) {
-                wait_ok(&full[s], parity);
-                tc_fence_after();
-                const uint32_t acc0 = ks > 0 ? 1u : 0u;
-                // advancing 16 inputs = 32 bytes inside the swizzle row: +2 in the (address >> 4) field
-                tc_mma_f16(tmem_base, da, db, idesc, acc0);
-                if (two) tc_mma_f16(d1, da, db + b_half, idesc1, acc0);
+            for (int ks0 = 0; ks0 < n_ksteps; ks0 += G_STAGES, parity ^= 1u) {
 #pragma unroll
-                for (int k4 = 1; k4 < G_BK / 16; ++k4) {
-                    tc_mma_f16(tmem_base, da + (uint64_t)(2 * k4), db + (uint64_t)(2 * k4), idesc, 1u);
-                    if (two) tc_mma_f16(d1, da + (uint64_t)(2 * k4), db + b_half + (uint64_t)(2 * k4), idesc1, 1u);
-                }
-                tc_commit(&empty[s]);   // the stage may be refilled once these MMAs have read it
-                da += a_stage;
-                db += b_stage;
-                if (++s == G_STAGES) {
-                    s = 0;
-                    parity ^= 1u;
-                    da = da0;
-                    db = db0;
+                for (int s = 0; s < G_STAGES; ++s) {
+                    const int ks = ks0 + s;
+                    if (ks >= n_ksteps) break;
+                    const uint64_t da = da0 + (uint64_t)s * a_stage, db = db0 + (uint64_t)s * b_stage;
+                    wait_ok(&full[s], parity);
+                    tc_fence_after();
+                    const uint32_t acc0 = ks > 0 ? 1u : 0u;
+                    // advancing 16 inputs = 32 bytes inside the swizzle row: +2 in the (address >> 4) field
+                    tc_mma_f16(tmem_base, da, db, idesc, acc0);
+                    if (two) tc_mma_f16(d1, da, db + b_half, idesc1, acc0);
+#pragma unroll
+                    for (int k4 = 1; k4 < G_BK / 16; ++k4) {
+                        tc_mma_f16(tmem_base, da + (uint64_t)(2 * k4), db + (uint64_t)(2 * k4), idesc, 1u);
+                        if (two) tc_mma_f16(d1, da + (uint64_t)(2 * k4), db + b_half + (uint64_t)(2 * k4), idesc1, 1u);
+                    }
+                    tc_commit(&empty[s]);   // the stage may be refilled once these MMAs have read it
                 }
             }
             tc_commit(&accum_bar);
