@@ -530,11 +530,21 @@ __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ 
                     float v[32];
 #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] = 0.f;
-                    for (int zz = 0; zz < pb.ksplit; ++zz) {
-                        const float* src = tile0 + (size_t)zz * tile_floats;
+                    // two slices per round: 64 loads in flight, summed in slice order
+                    for (int zz = 0; zz < pb.ksplit; zz += 2) {
+                        const float* s0 = tile0 + (size_t)zz * tile_floats;
+                        const bool two_ok = zz + 1 < pb.ksplit;
+                        const float* s1 = s0 + (two_ok ? tile_floats : 0);
+                        float t0[32], t1[32];
 #pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            if (ci * 32 + i < g.n_tile) v[i] += __ldcg(src + (size_t)(ci * 32 + i) * G_BM + r_local);
+                        for (int i = 0; i < 32; ++i) {
+                            const bool ok = ci * 32 + i < g.n_tile;
+                            const size_t o = (size_t)(ci * 32 + i) * G_BM + r_local;
+                            t0[i] = ok ? __ldcg(s0 + o) : 0.f;
+                            t1[i] = ok && two_ok ? __ldcg(s1 + o) : 0.f;
+                        }
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = (v[i] + t0[i]) + t1[i];
                     }
                     emit(ci, v);
                 };
