@@ -75,14 +75,21 @@ __global__ void __launch_bounds__(RT) ln_mix_rows_kernel(const __half* __restric
     const size_t m = blockIdx.x;
     const int nv = p.D / 8;
     const uint4* xr = reinterpret_cast<const uint4*>(x + m * p.D);
-    uint4 raw[LM_MAXV], prv[LM_MAXV];
+    uint4 raw[LM_MAXV], prv[LM_MAXV], wv_[LM_MAXV], bv_[LM_MAXV];
     float s = 0.f;
+    // everything that does not depend on the row statistics is requested up front (norm weights into registers, the
+    // lerp vectors into L1), so that the two block reductions are the only waits after the first load
 #pragma unroll
     for (int v = 0; v < LM_MAXV; ++v) {
         const int i = threadIdx.x + v * RT;
         if (i < nv) {
             raw[v] = xr[i];
             prv[v] = reinterpret_cast<const uint4*>(p.x_prev + m * p.D)[i];
+            wv_[v] = reinterpret_cast<const uint4*>(w)[i];
+            bv_[v] = reinterpret_cast<const uint4*>(b)[i];
+#pragma unroll
+            for (int j = 0; j < 6; ++j)
+                if (j < p.n_mix) asm volatile("prefetch.global.L1 [%0];" ::"l"(reinterpret_cast<const uint4*>(p.mix[j]) + i));
             const __half2* h = reinterpret_cast<const __half2*>(&raw[v]);
 #pragma unroll
             for (int e = 0; e < 4; ++e) { const float2 f = __half22float2(h[e]); s += f.x + f.y; }
@@ -106,7 +113,7 @@ __global__ void __launch_bounds__(RT) ln_mix_rows_kernel(const __half* __restric
     for (int v = 0; v < LM_MAXV; ++v) {
         const int i = threadIdx.x + v * RT;
         if (i < nv) {
-            const uint4 wv = reinterpret_cast<const uint4*>(w)[i], bv = reinterpret_cast<const uint4*>(b)[i];
+            const uint4 wv = wv_[v], bv = bv_[v];
             const __half2* h = reinterpret_cast<const __half2*>(&raw[v]);
             const __half2* wh = reinterpret_cast<const __half2*>(&wv);
             const __half2* bh = reinterpret_cast<const __half2*>(&bv);
