@@ -1,15 +1,16 @@
 // Device-side body of the weight-streaming matrix-vector product, shared by the stand-alone kernel
 // (gemv.cu) and the persistent batch-1 decode kernel (decode.cu).
 //
-// Weights go HBM -> registers with 128-bit non-allocating loads (8 in flight per thread, 1024 threads
+// Weights go HBM -> registers with 128-bit non-allocating loads (16 in flight per thread, 512 threads
 // per SM). The activation vector of every matrix a block touches is prepared once in shared memory (int8
 // high/low bytes of a 16-bit fixed-point value with one scale per 512 inputs, or fp16) and is shared by
-// the four rows a warp works on. Work items are (4 rows x 1 KB of each row); one flat item list covers all
-// matrices of a launch, so a launch has one prologue, one streaming loop and one epilogue. Per-item
+// the four rows a warp works on. Work items are (4 rows x 2 KB slices of each row); one flat item list covers
+// all matrices of a launch, so a launch has one prologue, one streaming loop and one epilogue. Per-item
 // partial sums land in shared memory; a row-parallel epilogue sums the K slices in a fixed order, applies
-// the row / tensor scale and the fused activation or residual, and stores fp16. A warp's first item of
-// the NEXT launch phase is copied ahead of time into shared memory with cp.async, so HBM keeps streaming
-// while the block finishes its epilogue, waits at the grid barrier and runs the next prologue.
+// the row / tensor scale and the fused activation or residual, and stores fp16. Optionally a warp's first
+// item of the NEXT phase is copied ahead of time into shared memory with cp.async; every variant of that
+// measured slower than not doing it (the copies delay the loads of the next phase's input vector), so the
+// persistent kernel leaves it off by default.
 #pragma once
 #include "gemv.cuh"
 
