@@ -5,10 +5,10 @@
 //   * every warp runs the phases (matrix-vector products with fused prologue / epilogue, and the
 //     per-head WKV-7 step); weights stream HBM -> registers with 128-bit loads;
 //   * blocks meet at a grid-wide barrier between phases: a monotonically increasing counter in
-//     global memory, arrive = release-add, wait = bounded acquire spin;
-//   * before a block goes to the barrier, each of its warps starts a cp.async copy of its first work
-//     item of the next matrix-vector phase into shared memory (weights do not depend on activations),
-//     so HBM keeps streaming through the barrier and the next prologue.
+//     global memory, arrive = release-add, wait = four staggered pollers with bounded acquire spins;
+//   * requesting the next phase's weights early (L2 prefetch, cp.async of each warp's first slice before or while
+//     the block waits at the barrier) exists as options and is off: all of it measured slower, because the requests
+//     sit in front of the small loads of the next phase's input vector, which are the critical path.
 // Every wait is bounded; on expiry the block sets the device status word and stops waiting.
 #include "decode.cuh"
 #include "gemv_body.cuh"
