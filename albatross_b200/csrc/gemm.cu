@@ -59,6 +59,7 @@ struct GemmProb {
     int tile_base;    // first split-K tile id (counter / partial index)
     long long part_base;   // float offset of its split-K partial sums in the scratch area
     int tma_out;      // output (and residual) tiles go through shared memory and the TMA unit
+    int recv_slots;   // split K: own chunks whose slices fit the receive area at a time
 };
 struct GemmGroup {
     GemmProb pr[G_MAX_OPS];
@@ -70,6 +71,7 @@ struct GemmGroup {
     int tmem_cols;
     unsigned* counters;
     float* partials;
+    int recv_off;   // split K: byte offset of the area the partial sums are fetched to, in the block's shared memory
 };
 struct GemmMaps {
     CUtensorMap m[G_MAX_OPS];   // activations X
@@ -147,6 +149,7 @@ __device__ __forceinline__ unsigned ld_acquire_gpu(const unsigned* p) {
     return v;
 }
 __device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, %0;" ::"n"(G_PROD) : "memory"); }
+constexpr int G_CHUNK_F32 = 32 * G_BM * 4;   // fp32 partial sums of 32 batch rows x 128 features
 
 // K-major operand tile, 128-byte swizzle: rows of 128 bytes, groups of 8 rows 1024 bytes apart.
 __device__ __forceinline__ uint64_t umma_desc_sw128(const void* smem) {
@@ -251,14 +254,15 @@ __device__ __forceinline__ float apply_epi(int epi, float o) {
     }
 }
 
+// SPLIT: some product of the launch is split along K (the lean instance is compiled without that ending).
+template <bool SPLIT>
 __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ GemmMaps maps,
                                                         const __grid_constant__ GemmGroup g) {
     extern __shared__ __align__(1024) unsigned char gsm[];
-    __shared__ uint64_t full[G_STAGES], empty[G_STAGES], accum_bar, resid_bar;
+    __shared__ uint64_t full[G_STAGES], empty[G_STAGES], accum_bar, resid_bar, recv_bar;
     __shared__ uint32_t tmem_base_s;
-    __shared__ int s_failed, s_last;
+    __shared__ int s_failed;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-
     // ---- which product, which tile, which K split
     int pi = 0;
     while (pi + 1 < g.n_prob && (int)blockIdx.x >= g.pr[pi + 1].cta_base) ++pi;
@@ -289,9 +293,9 @@ __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ 
         }
         mbar_init(&accum_bar, 1);
         mbar_init(&resid_bar, 1);
+        mbar_init(&recv_bar, 1);
         fence_mbar_init();
         s_failed = 0;
-        s_last = 0;
     }
     if (warp == 4 * G_NG + 1) tmem_alloc(&tmem_base_s, (uint32_t)g.tmem_cols);
     tc_fence_before();
@@ -445,14 +449,10 @@ __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ 
             if (staged) stage32(ci, v);
             else emit32(ci, v);
         };
-        // residual tiles on their way in (only blocks that will write the output need them)
-        // Split K ends in one of two ways. Few slices (the long products launched alone, whose blocks all finish
-        // together): the last block to arrive sums the tile, the others leave at once. Many slices (the fp16 adapter
-        // products of a grouped launch, whose blocks are done long before the rest of the grid): every block of the
-        // tile takes the chunks ci = z, z + ksplit, ... once all partial sums are there.
-        const bool shared_sum = pb.ksplit >= 6;
-        auto my_chunk = [&](int ci) { return !shared_sum || ci % pb.ksplit == z; };
-        auto fetch_resid = [&]() {
+        // With split K every block of a tile finishes the chunks ci = z, z + ksplit, ... of it.
+        auto my_chunk = [&](int ci) { return pb.ksplit == 1 || ci % pb.ksplit == z; };
+        // residual tiles on their way in
+        auto fetch_resid = [&](bool wait = true) {
             if (!(staged && epi == EPI_RESID)) return;
             if (tid == 0) {
                 int n_mine = 0;
@@ -461,7 +461,7 @@ __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ 
                 for (int ci = 0; ci < n_chunks; ++ci)
                     if (my_chunk(ci)) tma_load_2d(stg + (size_t)ci * 32 * G_BM, &maps.r[pi], m0, n0 + ci * 32, &resid_bar);
             }
-            wait_ok(&resid_bar, 0);
+            if (wait) wait_ok(&resid_bar, 0);
         };
         auto flush = [&]() {
             if (!staged) return;
@@ -474,7 +474,7 @@ __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ 
             }
         };
 
-        if (pb.ksplit == 1) {
+        if (!SPLIT || pb.ksplit == 1) {
             fetch_resid();
             for (int ci = grp; ci < n_chunks; ci += G_NG) {
                 uint32_t raw[32];
@@ -486,15 +486,20 @@ __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ 
             }
             flush();
         } else {
-            // Split K: every block of the tile parks its fp32 partial sums; they are summed in a fixed order
-            // (deterministic). Where the blocks of a tile wait for one another it is safe because a split grid never
-            // has more blocks than the GPU has SMs and every block holds a whole SM: all of them are resident. The
-            // wait is bounded all the same.
+            // Split K: chunk ci of the tile is finished by block ci % ksplit. Every block parks the partial sums of
+            // the other blocks' chunks in the scratch area; once all blocks of the tile have done so, each fetches
+            // the slices of its own chunks with bulk copies (all in flight at once) into the idle operand stages and
+            // sums them in slice order (deterministic), its own slice coming from TMEM. The blocks of a tile wait
+            // for one another: a split grid never has more blocks than the GPU has SMs and every block holds a
+            // whole SM, so all of them are resident. The wait is bounded all the same.
+            const int nz = pb.ksplit;
             const int tile = pb.tile_base + m_tile * gridDim.y + blockIdx.y;
             const size_t tile_floats = (size_t)g.n_tile * G_BM;
-            float* tile0 = g.partials + pb.part_base + ((size_t)(m_tile * gridDim.y + blockIdx.y) * pb.ksplit) * tile_floats;
+            float* tile0 = g.partials + pb.part_base + ((size_t)(m_tile * gridDim.y + blockIdx.y) * nz) * tile_floats;
             float* mine = tile0 + (size_t)z * tile_floats;
+            fetch_resid(false);
             for (int ci = grp; ci < n_chunks; ci += G_NG) {
+                if (ci % nz == z) continue;
                 uint32_t raw[32];
                 tc_ld32(lane_addr + (uint32_t)(ci * 32), raw);
 #pragma unroll
@@ -503,64 +508,69 @@ __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ 
             }
             __threadfence();
             epi_sync();
+            bool ok = true;
             if (tid == 0) {
-                const unsigned old = atomicAdd(&g.counters[tile], 1u);
-                int go;
-                if (shared_sum) {
-                    go = 1;
-                    uint32_t it = 0;
-                    while (ld_acquire_gpu(&g.counters[tile]) < (unsigned)pb.ksplit) {
-                        if (++it > (1u << 21)) {
-                            go = 0;
-                            atomicOr(&g_device_status, DEV_WAIT_GEMM);
-                            break;
+                atomicAdd(&g.counters[tile], 1u);
+                uint32_t it = 0;
+                while (ld_acquire_gpu(&g.counters[tile]) < (unsigned)nz) {
+                    if (++it > (1u << 21)) {
+                        ok = false;
+                        atomicOr(&g_device_status, DEV_WAIT_GEMM);
+                        break;
+                    }
+                }
+                // the partial sums were written by ordinary stores of other blocks; the bulk copies read them
+                asm volatile("fence.proxy.async;" ::: "memory");
+            }
+            if (staged && epi == EPI_RESID) wait_ok(&resid_bar, 0);
+            unsigned char* recv = base + g.recv_off;
+            const int n_own = z < n_chunks ? (n_chunks - z + nz - 1) / nz : 0;   // chunks z, z + nz, ...
+            const int per_round = pb.recv_slots;   // own chunks whose slices fit the receive area at a time
+            for (int k0 = 0, round = 0; k0 < n_own; k0 += per_round, ++round) {
+                const int k1 = min(k0 + per_round, n_own);
+                if (round > 0) epi_sync();   // everybody has read the slices of the round before
+                if (tid == 0) {
+                    uint32_t total = 0;
+                    for (int kk = k0; kk < k1; ++kk)
+                        total += (uint32_t)(nz - 1) * (uint32_t)(min(32, g.n_tile - (z + kk * nz) * 32) * G_BM * 4);
+                    mbar_expect_tx(&recv_bar, ok ? total : 0u);
+                    for (int kk = k0; ok && kk < k1; ++kk) {
+                        const int ci = z + kk * nz;
+                        const uint32_t bytes = (uint32_t)(min(32, g.n_tile - ci * 32) * G_BM * 4);
+                        for (int zz = 0; zz < nz; ++zz) {
+                            if (zz == z) continue;
+                            bulk_g2s(recv + (size_t)((kk - k0) * (nz - 1) + (zz < z ? zz : zz - 1)) * G_CHUNK_F32,
+                                     tile0 + (size_t)zz * tile_floats + (size_t)ci * 32 * G_BM, bytes, &recv_bar);
                         }
                     }
-                } else {
-                    go = old == (unsigned)pb.ksplit - 1;
-                    if (go) g.counters[tile] = 0;   // leave the counter ready for the next launch
-                    __threadfence();
                 }
-                s_last = go;
-            }
-            epi_sync();
-            if (s_last) {
-                fetch_resid();
-                auto sum_chunk = [&](int ci) {
+                wait_ok(&recv_bar, (uint32_t)(round & 1));
+                for (int kk = k0; kk < k1; ++kk) {
+                    if (kk % G_NG != grp) continue;
+                    const int ci = z + kk * nz;
+                    uint32_t raw[32];
+                    tc_ld32(lane_addr + (uint32_t)(ci * 32), raw);
                     float v[32];
 #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] = 0.f;
-                    // two slices per round: 64 loads in flight, summed in slice order
-                    for (int zz = 0; zz < pb.ksplit; zz += 2) {
-                        const float* s0 = tile0 + (size_t)zz * tile_floats;
-                        const bool two_ok = zz + 1 < pb.ksplit;
-                        const float* s1 = s0 + (two_ok ? tile_floats : 0);
-                        float t0[32], t1[32];
+                    for (int zz = 0; zz < nz; ++zz) {
+                        if (zz == z) {
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            const bool ok = ci * 32 + i < g.n_tile;
-                            const size_t o = (size_t)(ci * 32 + i) * G_BM + r_local;
-                            t0[i] = ok ? __ldcg(s0 + o) : 0.f;
-                            t1[i] = ok && two_ok ? __ldcg(s1 + o) : 0.f;
+                            for (int i = 0; i < 32; ++i) v[i] += __uint_as_float(raw[i]);
+                        } else {
+                            const float* src = reinterpret_cast<const float*>(recv + (size_t)((kk - k0) * (nz - 1) + (zz < z ? zz : zz - 1)) * G_CHUNK_F32) + r_local;
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) v[i] += src[i * G_BM];
                         }
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) v[i] = (v[i] + t0[i]) + t1[i];
                     }
                     emit(ci, v);
-                };
-                if (shared_sum) {
-                    int k = 0;
-                    for (int ci = z; ci < n_chunks; ci += pb.ksplit, ++k)
-                        if (k % G_NG == grp) sum_chunk(ci);
-                } else {
-                    for (int ci = grp; ci < n_chunks; ci += G_NG) sum_chunk(ci);
                 }
-                flush();
             }
-            // shared sum: the last block to leave puts the counter back to zero for the next launch
-            if (shared_sum && tid == 0) {
+            flush();
+            // the last block to leave puts the counter back to zero for the next launch
+            if (tid == 0) {
                 const unsigned old = atomicAdd(&g.counters[tile], 1u);
-                if (old == 2u * (unsigned)pb.ksplit - 1u) g.counters[tile] = 0;
+                if (old == 2u * (unsigned)nz - 1u) g.counters[tile] = 0;
             }
         }
         tc_fence_before();
@@ -682,6 +692,19 @@ struct GroupShape {
     int n_split_tiles;
 };
 
+// Shared memory of a block (beyond the 1 KB alignment slack): operand stages + raw weight rings.
+size_t block_smem(int n_tile) { return (size_t)G_STAGES * (G_A_BYTES + (size_t)n_tile * 128) + G_RAW_BYTES; }
+// Split K: how many of its own chunks a block can fetch the other blocks' partial sums for at a time. They land
+// in the operand stages behind the output staging area.
+int split_recv_slots(int n_tile, int ks) {
+    const int n_chunks = (n_tile + 31) / 32;
+    const size_t stage_bytes = (size_t)n_chunks * 32 * G_BM * 2;
+    const size_t avail = block_smem(n_tile) - stage_bytes;
+    const int own_max = (n_chunks + ks - 1) / ks;
+    const int fit = (int)(avail / ((size_t)(ks - 1) * G_CHUNK_F32));
+    return fit < own_max ? fit : own_max;
+}
+
 GroupShape group_shape(const GemmOp* ops, int n, int rows) {
     GroupShape gs = {};
     if (rows <= 256) { gs.n_tile = (rows + 15) & ~15; gs.n_first = gs.tma_rows = gs.n_tile; }
@@ -712,6 +735,7 @@ GroupShape group_shape(const GemmOp* ops, int n, int rows) {
             if (ks > ksteps / 8) ks = ksteps / 8;
             if (ks < 1) ks = 1;
         }
+        while (ks > 1 && split_recv_slots(gs.n_tile, ks) < 1) --ks;   // the slices of one chunk must fit the receive area
         gs.ksplit[i] = ks;
         const int m_tiles = (ops[i].w.n_out + G_BM - 1) / G_BM;
         gs.grid_x += m_tiles * ks;
@@ -758,6 +782,7 @@ int gemm_group_launch(const GemmOp* ops, int n, int rows, void* scratch, cudaStr
     GemmGroup g = {};
     GemmMaps maps;
     g.n_prob = n; g.rows = rows; g.n_tile = gs.n_tile; g.n_first = gs.n_first; g.tma_rows = gs.tma_rows; g.tmem_cols = gs.tmem_cols;
+    g.recv_off = (gs.n_tile + 31) / 32 * 32 * G_BM * 2;
     g.counters = reinterpret_cast<unsigned*>(scratch);
     g.partials = scratch ? reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(scratch) + (size_t)G_COUNTERS * 4) : nullptr;
     int cta = 0, tile = 0;
@@ -775,6 +800,7 @@ int gemm_group_launch(const GemmOp* ops, int n, int rows, void* scratch, cudaStr
         GemmProb& pb = g.pr[i];
         pb.w = m; pb.resid = op.resid; pb.y = op.y; pb.epi = op.epi;
         pb.cta_base = cta; pb.ksplit = gs.ksplit[i]; pb.tile_base = tile; pb.part_base = part;
+        pb.recv_slots = pb.ksplit > 1 ? split_recv_slots(gs.n_tile, pb.ksplit) : 0;
         const int m_tiles = (m.n_out + G_BM - 1) / G_BM;
         cta += m_tiles * pb.ksplit;
         if (pb.ksplit > 1) {
@@ -816,10 +842,11 @@ int gemm_group_launch(const GemmOp* ops, int n, int rows, void* scratch, cudaStr
     }
     for (int i = n; i < G_MAX_OPS; ++i) { maps.m[i] = maps.m[0]; maps.y[i] = maps.m[0]; maps.r[i] = maps.m[0]; }
 
-    const size_t smem = 1024 + (size_t)G_STAGES * (G_A_BYTES + (size_t)gs.n_tile * 128) + G_RAW_BYTES;
+    const size_t smem = 1024 + block_smem(gs.n_tile);
     static size_t smem_set = 0;
     if (smem > smem_set) {
-        AB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        AB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        AB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         smem_set = smem;
     }
     cudaLaunchConfig_t cfg = {};
@@ -827,12 +854,17 @@ int gemm_group_launch(const GemmOp* ops, int n, int rows, void* scratch, cudaStr
     cfg.blockDim = dim3(GT);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    int n_attr = 0;
+    if (pdl) {
+        attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+        ++n_attr;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = pdl ? 1 : 0;
-    AB_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_kernel, maps, g));
+    cfg.numAttrs = n_attr;
+    if (gs.n_split_tiles > 0) AB_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_kernel<true>, maps, g));
+    else AB_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_kernel<false>, maps, g));
     return OK;
 }
 
@@ -908,3 +940,4 @@ extern "C" int ab_gemm_static(const ab_mat* m, int rows, const void* x, void* y,
     if (st != OK) return st;
     return gemm_launch(*m, rows, (const __half*)x, (__half*)y, epi, (const __half*)resid, scratch, (cudaStream_t)stream);
 }
+
