@@ -94,9 +94,8 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int 
                  "r"(smem_u32(src))
                  : "memory");
 }
-__device__ __forceinline__ void bulk_commit_and_drain_reads() {
-    asm volatile("cp.async.bulk.commit_group;\n cp.async.bulk.wait_group.read 0;" ::: "memory");
-}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_drain_reads() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols)
                  : "memory");
@@ -149,6 +148,7 @@ __device__ __forceinline__ unsigned ld_acquire_gpu(const unsigned* p) {
     return v;
 }
 __device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, %0;" ::"n"(G_PROD) : "memory"); }
+__device__ __forceinline__ void group_sync(int grp) { asm volatile("bar.sync %0, 128;" ::"r"(2 + grp) : "memory"); }   // one producer group
 constexpr int G_CHUNK_F32 = 32 * G_BM * 4;   // fp32 partial sums of 32 batch rows x 128 features
 
 // K-major operand tile, 128-byte swizzle: rows of 128 bytes, groups of 8 rows 1024 bytes apart.
@@ -445,9 +445,17 @@ __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ 
                 default: body(std::integral_constant<int, EPI_NONE>()); break;
             }
         };
+        // A staged chunk leaves at once, while the group works on its next chunk: the group's first thread hands it
+        // to the TMA unit as soon as all four warps have written their part.
         auto emit = [&](int ci, const float* v) {
-            if (staged) stage32(ci, v);
-            else emit32(ci, v);
+            if (!staged) { emit32(ci, v); return; }
+            stage32(ci, v);
+            fence_proxy_async();
+            group_sync(grp);
+            if (r_local == 0) {
+                tma_store_2d(&maps.y[pi], m0, n0 + ci * 32, stg + (size_t)ci * 32 * G_BM);
+                bulk_commit();
+            }
         };
         // With split K every block of a tile finishes the chunks ci = z, z + ksplit, ... of it.
         auto my_chunk = [&](int ci) { return pb.ksplit == 1 || ci % pb.ksplit == z; };
@@ -464,14 +472,7 @@ __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ 
             if (wait) wait_ok(&resid_bar, 0);
         };
         auto flush = [&]() {
-            if (!staged) return;
-            fence_proxy_async();
-            epi_sync();
-            if (tid == 0) {
-                for (int ci = 0; ci < n_chunks; ++ci)
-                    if (my_chunk(ci)) tma_store_2d(&maps.y[pi], m0, n0 + ci * 32, stg + (size_t)ci * 32 * G_BM);
-                bulk_commit_and_drain_reads();   // the shared memory must outlive the unit's reads
-            }
+            if (staged && r_local == 0) bulk_drain_reads();   // the shared memory must outlive the unit's reads
         };
 
         if (!SPLIT || pb.ksplit == 1) {
