@@ -20,7 +20,8 @@
 //   next warp : one thread issues the TMA loads of the activation tile (tensor map over X, 128B swizzle);
 //   last warp : allocates TMEM; one thread issues tcgen05.mma (kind::f16) and commits to mbarriers.
 // Three-stage operand ring, all waits bounded (status word on expiry), TMEM freed on every path. Short grids with
-// long K loops are split along K (fp32 partial tiles in a scratch area, summed in a fixed order). Launched with
+// long K loops are split along K: every block of a tile finishes a share of its 32-row chunks, fetching the other
+// blocks' fp32 partial sums of them from a scratch area with bulk copies and adding them in a fixed order. Launched with
 // programmatic stream serialisation the kernel starts its weight stream before it waits for its predecessor.
 #include <cuda.h>
 
