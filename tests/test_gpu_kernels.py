@@ -159,6 +159,27 @@ def test_batched_product_against_oracle(fmt, rows, n, k):
     assert rel_err(got, want) < 3e-3
 
 
+@pytest.mark.parametrize("rows", [16, 32, 48, 80, 100, 130, 200, 256])
+def test_batched_product_split_k_batch_sizes(rows):
+    """Few output tiles and a long K loop: split K. The batch size sets how much shared memory a block has for the
+    other blocks' partial sums (for some sizes the split is narrowed to make one chunk's slices fit), whether the
+    last 32-row chunk is ragged, and how many chunks each block of a tile finishes. With and without the residual
+    epilogue; a second call must reproduce the first bit for bit (fixed summation order)."""
+    from albatross_b200 import _lib, quant
+    torch.manual_seed(rows)
+    n, k = 256, 4096
+    w = torch.randn(n, k) * 0.02
+    x = torch.randn(rows, k).half()
+    resid = torch.randn(rows, n).half()
+    pm = quant.quantize(w.cuda(), "nvfp4")
+    base = x.double().numpy() @ qo.fake_quantize(w.numpy(), "nvfp4").astype(np.float64).T
+    for epi, want in ((_lib.EPI_NONE, base), (_lib.EPI_RESID, base + resid.double().numpy())):
+        r = resid.cuda() if epi == _lib.EPI_RESID else None
+        got = _gemm(pm, x.cuda(), epi, r)
+        assert rel_err(got.float().cpu().numpy(), want) < 3e-3
+        assert torch.equal(_gemm(pm, x.cuda(), epi, r), got)
+
+
 def test_batched_product_small_k_and_epilogues():
     """Adapter-sized products (K = 16 ... 480, not multiples of the 64-input k-step) and the fused epilogues."""
     from albatross_b200 import _lib, quant
