@@ -395,7 +395,7 @@ int forward_rows(ab_model* m, int B, int T, const int32_t* tokens, void* const* 
         const void* mv[6] = {L.x_r, L.x_k, L.x_v, L.x_w, L.x_a, L.x_g};
         for (int j = 0; j < 6; ++j) { mp.mix[j] = (const __half*)mv[j]; mp.out[j] = ws.mix[j]; }
         if (ln_mix_rows_ok(mp)) {
-            AB_TRY(ln_mix_rows(ws.x, (const __half*)L.ln1_w, (const __half*)L.ln1_b, mp, st));
+            AB_TRY(ln_mix_rows(ws.x, (const __half*)L.ln1_w, (const __half*)L.ln1_b, mp, st, m->use_pdl));
         } else {
             AB_TRY(ln_rows(ws.x, (const __half*)L.ln1_w, (const __half*)L.ln1_b, M, D, 1, 0, ws.xn, st));
             AB_TRY(mix_rows(mp, st));
@@ -426,7 +426,7 @@ int forward_rows(ab_model* m, int B, int T, const int32_t* tokens, void* const* 
         fp.xn = ws.xn; fp.x_prev = (__half*)state[3 * i + 2]; fp.B = B; fp.T = T; fp.D = D; fp.n_mix = 1;
         fp.mix[0] = (const __half*)L.ffn_x_k; fp.out[0] = ws.mix[0];
         if (ln_mix_rows_ok(fp)) {
-            AB_TRY(ln_mix_rows(ws.x, (const __half*)L.ln2_w, (const __half*)L.ln2_b, fp, st));
+            AB_TRY(ln_mix_rows(ws.x, (const __half*)L.ln2_w, (const __half*)L.ln2_b, fp, st, m->use_pdl));
         } else {
             AB_TRY(ln_rows(ws.x, (const __half*)L.ln2_w, (const __half*)L.ln2_b, M, D, 1, 0, ws.xn, st));
             AB_TRY(mix_rows(fp, st));

@@ -70,7 +70,8 @@ __global__ void __launch_bounds__(RT) mix_rows_kernel(MixParams p) {
 // stores), the normalised row becomes the new token-shift state. Same rounding points as ln_rows + mix_rows.
 constexpr int LM_MAXV = 4;   // 16-byte chunks per thread: D <= 8 * RT * LM_MAXV
 __global__ void __launch_bounds__(RT) ln_mix_rows_kernel(const __half* __restrict__ x, const __half* __restrict__ w,
-                                                         const __half* __restrict__ b, const __grid_constant__ MixParams p) {
+                                                         const __half* __restrict__ b, const __grid_constant__ MixParams p,
+                                                         int use_pdl) {
     __shared__ float red[RT / 32];
     const size_t m = blockIdx.x;
     const int nv = p.D / 8;
@@ -78,18 +79,32 @@ __global__ void __launch_bounds__(RT) ln_mix_rows_kernel(const __half* __restric
     uint4 raw[LM_MAXV], prv[LM_MAXV], wv_[LM_MAXV], bv_[LM_MAXV];
     float s = 0.f;
     // everything that does not depend on the row statistics is requested up front (norm weights into registers, the
-    // lerp vectors into L1), so that the two block reductions are the only waits after the first load
+    // lerp vectors into L1), so that the two block reductions are the only waits after the first load. Under
+    // programmatic stream serialisation the parameters are requested while the preceding kernel still runs, and the
+    // next kernel (a product, which starts with its weight stream) may start at once.
+    if (use_pdl) pdl_launch_dependents();
 #pragma unroll
     for (int v = 0; v < LM_MAXV; ++v) {
         const int i = threadIdx.x + v * RT;
         if (i < nv) {
-            raw[v] = xr[i];
-            prv[v] = reinterpret_cast<const uint4*>(p.x_prev + m * p.D)[i];
             wv_[v] = reinterpret_cast<const uint4*>(w)[i];
             bv_[v] = reinterpret_cast<const uint4*>(b)[i];
 #pragma unroll
             for (int j = 0; j < 6; ++j)
                 if (j < p.n_mix) asm volatile("prefetch.global.L1 [%0];" ::"l"(reinterpret_cast<const uint4*>(p.mix[j]) + i));
+        }
+    }
+    if (use_pdl) pdl_wait();
+#pragma unroll
+    for (int v = 0; v < LM_MAXV; ++v) {
+        const int i = threadIdx.x + v * RT;
+        if (i < nv) {
+            // an ordinary (coherent) load that stays behind the wait above: the row was written by the preceding kernel
+            asm volatile("ld.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(raw[v].x), "=r"(raw[v].y), "=r"(raw[v].z), "=r"(raw[v].w)
+                         : "l"(xr + i)
+                         : "memory");
+            prv[v] = reinterpret_cast<const uint4*>(p.x_prev + m * p.D)[i];
             const __half2* h = reinterpret_cast<const __half2*>(&raw[v]);
 #pragma unroll
             for (int e = 0; e < 4; ++e) { const float2 f = __half22float2(h[e]); s += f.x + f.y; }
@@ -220,10 +235,18 @@ int ln_rows(const __half* x, const __half* w, const __half* b, int rows, int D, 
     return OK;
 }
 bool ln_mix_rows_ok(const MixParams& p) { return p.T == 1 && p.D % 8 == 0 && p.D <= 8 * RT * LM_MAXV; }
-int ln_mix_rows(const __half* x, const __half* w, const __half* b, const MixParams& p, cudaStream_t s) {
+int ln_mix_rows(const __half* x, const __half* w, const __half* b, const MixParams& p, cudaStream_t s, bool pdl) {
     AB_CHECK_ARG(x && w && b && p.x_prev && p.n_mix >= 1 && p.n_mix <= 6 && p.B > 0 && ln_mix_rows_ok(p), "ln_mix_rows: bad argument");
-    ln_mix_rows_kernel<<<p.B, RT, 0, s>>>(x, w, b, p);
-    AB_CUDA(cudaGetLastError());
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.B);
+    cfg.blockDim = dim3(RT);
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    AB_CUDA(cudaLaunchKernelEx(&cfg, ln_mix_rows_kernel, x, w, b, p, pdl ? 1 : 0));
     return OK;
 }
 int sample_rows(const __half* logits, int rows, int V, float noise, uint32_t seed, int* out, cudaStream_t s) {
