@@ -35,7 +35,7 @@ namespace ab {
 namespace {
 
 #ifndef G_NG_
-#define G_NG_ 2
+#define G_NG_ 3
 #endif
 constexpr int G_NG = G_NG_;      // producer groups
 constexpr int G_PROD = 128 * G_NG;
