@@ -172,25 +172,6 @@ __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
     return *reinterpret_cast<const uint32_t*>(&h);
 }
 
-// Raw bytes of one weight row per k-step (64 inputs), and 16-byte chunks in them.
-__device__ __forceinline__ int raw_row_bytes(int fmt) { return fmt == FMT_I8 ? 64 : (fmt == FMT_F16 ? 128 : 32); }
-
-// Start copying the raw weights of k-step `ks` of row `row` into a ring slot (chunk-major: chunk q of row r at
-// q * 2048 + r * 16, so that the owner's read-back is conflict free); NVFP4 block scales (4 bytes) follow.
-__device__ __forceinline__ void raw_issue(const ab_mat& w, int row, int r_local, int ks, unsigned char* slot) {
-    const int K = w.k, k0 = ks * G_BK;
-    const int rb = raw_row_bytes(w.fmt), nq = rb / 16;
-    const bool row_ok = row < w.n_out;
-    const unsigned char* src = reinterpret_cast<const unsigned char*>(w.w) +
-                               (row_ok ? ((size_t)row * K + k0) * rb / 64 : 0);
-    const int epc = 16 * 64 / rb;   // inputs per 16-byte chunk
-    for (int q = 0; q < nq; ++q) cp_async_16(slot + q * 2048 + r_local * 16, src + q * 16, row_ok && k0 + q * epc < K);
-    if (w.fmt == FMT_FP4) {
-        const unsigned char* ssrc = reinterpret_cast<const unsigned char*>(w.scale) + (row_ok ? ((size_t)row * K + k0) / 16 : 0);
-        cp_async_4(slot + nq * 2048 + r_local * 4, ssrc, row_ok && k0 < K);
-    }
-}
-
 // De-quantise the 64 inputs of this thread's row from a landed ring slot into eight 16-byte chunks of fp16
 // (chunk c = inputs 8c..8c+7). Invalid rows / inputs were zero-filled by the copy.
 __device__ __forceinline__ void raw_dequant(int fmt, int r_local, const unsigned char* slot, uint4* out) {
@@ -326,8 +307,10 @@ __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ 
         const bool row_ok = row < n_out;
 
         // de-quantised k-step -> operand stage (swizzled), then tell the MMA warp
-        auto put_stage = [&](int ks, const uint4* cur) {
-            const int s = ks % G_STAGES, f = ks / G_STAGES;
+        // (j = how many k-steps this group has done before; with as many groups as stages a group always fills the
+        // same stage)
+        auto put_stage = [&](int ks, int j, const uint4* cur) {
+            const int s = G_NG == G_STAGES ? grp : ks % G_STAGES, f = G_NG == G_STAGES ? j : ks / G_STAGES;
             if (f > 0) wait_ok(&empty[s], (f - 1) & 1);
             unsigned char* dst = smA + s * G_A_BYTES + r_local * 128;
 #pragma unroll
@@ -349,42 +332,57 @@ __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ 
             uint4 nxt[8];
             if (grp < n_ksteps) fetch(grp, nxt);
             pdl_wait();
-            for (int ks = grp; ks < n_ksteps; ks += G_NG) {
+            int j = 0;
+            for (int ks = grp; ks < n_ksteps; ks += G_NG, ++j) {
                 uint4 cur[8];
 #pragma unroll
                 for (int c = 0; c < 8; ++c) cur[c] = nxt[c];
                 if (ks + G_NG < n_ksteps) fetch(ks + G_NG, nxt);
-                put_stage(ks, cur);
+                put_stage(ks, j, cur);
             }
         } else {
-            unsigned char* ring = smRaw + grp * G_RAW_GROUP;
-            const int slot_bytes = raw_row_bytes(fmt) * G_BM + (fmt == FMT_FP4 ? G_BM * 4 : 0);
-            int depth = G_RAW_GROUP / slot_bytes;   // own k-steps of raw weights in flight
-            if (depth > 6) depth = 6;
-            for (int j = 0; j < depth - 1; ++j) {
-                const int ks = grp + j * G_NG;
-                if (ks < n_ksteps) raw_issue(pb.w, row, r_local, kstep_of(ks), ring + (j % depth) * slot_bytes);
-                cp_async_commit();
-            }
-            pdl_wait();
-            int j = 0;
-            for (int ks = grp; ks < n_ksteps; ks += G_NG, ++j) {
-                const int ja = j + depth - 1, ks_a = grp + ja * G_NG;
-                if (ks_a < n_ksteps) raw_issue(pb.w, row, r_local, kstep_of(ks_a), ring + (ja % depth) * slot_bytes);
-                cp_async_commit();
-                // all but the newest depth-1 groups have landed: k-step ks is there
-                switch (depth) {
-                    case 6: cp_async_wait<5>(); break;
-                    case 5: cp_async_wait<4>(); break;
-                    case 4: cp_async_wait<3>(); break;
-                    case 3: cp_async_wait<2>(); break;
-                    case 2: cp_async_wait<1>(); break;
-                    default: cp_async_wait<0>(); break;
+            // One instance of the loop per weight format: ring depth, slot size and chunk counts are constants in it,
+            // the ring slots are walked with wrapping counters and the row's base addresses are computed once.
+            auto quant_loop = [&](auto fmt_c) {
+                constexpr int F = decltype(fmt_c)::value;
+                constexpr int rb = F == FMT_I8 ? 64 : 32, nq = rb / 16, epc = 16 * 64 / rb;
+                constexpr int slot_bytes = rb * G_BM + (F == FMT_FP4 ? G_BM * 4 : 0);
+                constexpr int depth = G_RAW_GROUP / slot_bytes > 6 ? 6 : G_RAW_GROUP / slot_bytes;   // own k-steps in flight
+                static_assert(depth >= 1, "raw ring too small");
+                unsigned char* ring = smRaw + grp * G_RAW_GROUP;
+                const int K = pb.w.k;
+                const unsigned char* wrow = reinterpret_cast<const unsigned char*>(pb.w.w) + (row_ok ? (size_t)row * K * rb / 64 : 0);
+                const unsigned char* srow = reinterpret_cast<const unsigned char*>(pb.w.scale) + (row_ok && F == FMT_FP4 ? (size_t)row * K / 16 : 0);
+                // chunk-major slot: chunk q of row r at q * 2048 + r * 16 (conflict-free read-back); NVFP4 block scales follow
+                auto issue = [&](int ks_abs, unsigned char* slot) {
+                    const int k0 = ks_abs * G_BK;
+#pragma unroll
+                    for (int q = 0; q < nq; ++q)
+                        cp_async_16(slot + q * 2048 + r_local * 16, wrow + (size_t)ks_abs * rb + q * 16, row_ok && k0 + q * epc < K);
+                    if (F == FMT_FP4) cp_async_4(slot + nq * 2048 + r_local * 4, srow + (size_t)ks_abs * 4, row_ok && k0 < K);
+                };
+#pragma unroll
+                for (int j = 0; j < depth - 1; ++j) {
+                    const int ks = grp + j * G_NG;
+                    if (ks < n_ksteps) issue(kstep_of(ks), ring + j * slot_bytes);
+                    cp_async_commit();
                 }
-                uint4 cur[8];
-                raw_dequant(fmt, r_local, ring + (j % depth) * slot_bytes, cur);
-                put_stage(ks, cur);
-            }
+                pdl_wait();
+                int j = 0, wslot = depth - 1, rslot = 0;
+                for (int ks = grp; ks < n_ksteps; ks += G_NG, ++j) {
+                    const int ks_a = ks + (depth - 1) * G_NG;
+                    if (ks_a < n_ksteps) issue(kstep_of(ks_a), ring + wslot * slot_bytes);
+                    if (++wslot == depth) wslot = 0;
+                    cp_async_commit();
+                    cp_async_wait<depth - 1>();   // all but the newest depth-1 groups have landed: k-step ks is there
+                    uint4 cur[8];
+                    raw_dequant(F, r_local, ring + rslot * slot_bytes, cur);
+                    if (++rslot == depth) rslot = 0;
+                    put_stage(ks, j, cur);
+                }
+            };
+            if (fmt == FMT_I8) quant_loop(std::integral_constant<int, FMT_I8>());
+            else quant_loop(std::integral_constant<int, FMT_FP4>());
         }
 
         // ===== epilogue: thread = output feature (TMEM lane); groups take turns on chunks of 32 batch rows =====
