@@ -41,6 +41,11 @@ constexpr int G_NG = G_NG_;      // producer groups
 constexpr int G_PROD = 128 * G_NG;
 constexpr int GT = G_PROD + 64;  // threads per block
 constexpr int G_STAGES = 3;
+#ifndef G_A_TMEM_
+#define G_A_TMEM_ 1
+#endif
+constexpr bool G_A_TMEM = G_A_TMEM_ != 0;   // de-quantised weights go to tensor memory instead of shared memory
+constexpr int G_A_COLS = 32;             // TMEM columns of one weight stage: 64 inputs as fp16 pairs
 constexpr int G_BM = 128;        // weight rows per block
 constexpr int G_BK = 64;         // inputs per k-step (128 bytes of fp16 = one swizzle row)
 constexpr int G_A_BYTES = G_BM * G_BK * 2;
@@ -70,6 +75,7 @@ struct GemmGroup {
     int n_first;    // batch rows of the first MMA of a k-substep (n_tile, or 192 when a second MMA takes the rest)
     int tma_rows;   // batch rows per TMA box
     int tmem_cols;
+    int a_col0;     // first TMEM column of the weight stages (behind the accumulators)
     unsigned* counters;
     float* partials;
     int recv_off;   // split K: byte offset of the area the partial sums are fetched to, in the block's shared memory
@@ -116,6 +122,27 @@ __device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uin
         " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}"
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
         : "memory");
+}
+// The same product with the weight operand read from tensor memory (128 lanes = weight rows, 8 columns = 16 inputs
+// as fp16 pairs) instead of shared memory.
+__device__ __forceinline__ void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// 32 registers of each of the warp's 32 lanes -> 32 consecutive TMEM columns of its 32 lanes.
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t* v) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+          "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]),
+          "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]),
+          "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* v) {
     asm volatile(
@@ -312,10 +339,18 @@ __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ 
         auto put_stage = [&](int ks, int j, const uint4* cur) {
             const int s = G_NG == G_STAGES ? grp : ks % G_STAGES, f = G_NG == G_STAGES ? j : ks / G_STAGES;
             if (f > 0) wait_ok(&empty[s], (f - 1) & 1);
-            unsigned char* dst = smA + s * G_A_BYTES + r_local * 128;
+            if (G_A_TMEM) {
+                tc_fence_after();   // the MMAs that read this stage are complete (their commit released it)
+                // this thread's 64 inputs = 32 registers -> 32 columns of its own TMEM lane
+                tc_st32(tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(g.a_col0 + s * G_A_COLS),
+                        reinterpret_cast<const uint32_t*>(cur));
+                tc_fence_before();
+            } else {
+                unsigned char* dst = smA + s * G_A_BYTES + r_local * 128;
 #pragma unroll
-            for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(dst + ((c ^ (r_local & 7)) << 4)) = cur[c];
-            fence_proxy_async();   // generic-proxy stores -> visible to the tensor core's async proxy
+                for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(dst + ((c ^ (r_local & 7)) << 4)) = cur[c];
+                fence_proxy_async();   // generic-proxy stores -> visible to the tensor core's async proxy
+            }
             __syncwarp();
             if (lane == 0) mbar_arrive(&full[s]);   // one arrival per warp of the owning group
         };
@@ -612,12 +647,22 @@ __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ 
                     tc_fence_after();
                     const uint32_t acc0 = ks > 0 ? 1u : 0u;
                     // advancing 16 inputs = 32 bytes inside the swizzle row: +2 in the (address >> 4) field
-                    tc_mma_f16(tmem_base, da, db, idesc, acc0);
-                    if (two) tc_mma_f16(d1, da, db + b_half, idesc1, acc0);
+                    if (G_A_TMEM) {
+                        const uint32_t ta = tmem_base + (uint32_t)(g.a_col0 + s * G_A_COLS);
 #pragma unroll
-                    for (int k4 = 1; k4 < G_BK / 16; ++k4) {
-                        tc_mma_f16(tmem_base, da + (uint64_t)(2 * k4), db + (uint64_t)(2 * k4), idesc, 1u);
-                        if (two) tc_mma_f16(d1, da + (uint64_t)(2 * k4), db + b_half + (uint64_t)(2 * k4), idesc1, 1u);
+                        for (int k4 = 0; k4 < G_BK / 16; ++k4) {   // 16 inputs = 8 columns of the weight stage
+                            const uint32_t acc = k4 ? 1u : acc0;
+                            tc_mma_f16_ts(tmem_base, ta + (uint32_t)(8 * k4), db + (uint64_t)(2 * k4), idesc, acc);
+                            if (two) tc_mma_f16_ts(d1, ta + (uint32_t)(8 * k4), db + b_half + (uint64_t)(2 * k4), idesc1, acc);
+                        }
+                    } else {
+                        tc_mma_f16(tmem_base, da, db, idesc, acc0);
+                        if (two) tc_mma_f16(d1, da, db + b_half, idesc1, acc0);
+#pragma unroll
+                        for (int k4 = 1; k4 < G_BK / 16; ++k4) {
+                            tc_mma_f16(tmem_base, da + (uint64_t)(2 * k4), db + (uint64_t)(2 * k4), idesc, 1u);
+                            if (two) tc_mma_f16(d1, da + (uint64_t)(2 * k4), db + b_half + (uint64_t)(2 * k4), idesc1, 1u);
+                        }
                     }
                     tc_commit(&empty[s]);   // the stage may be refilled once these MMAs have read it
                 }
@@ -711,7 +756,8 @@ GroupShape group_shape(const GemmOp* ops, int n, int rows) {
     else if (rows <= 320) { gs.n_tile = (rows + 31) & ~31; gs.n_first = 192; gs.tma_rows = gs.n_tile % 64 ? 32 : 64; }
     else { gs.n_tile = gs.n_first = gs.tma_rows = 256; }
     gs.tmem_cols = 32;
-    while (gs.tmem_cols < gs.n_tile) gs.tmem_cols *= 2;
+    const int a_cols = G_A_TMEM ? G_STAGES * G_A_COLS : 0;   // weight stages behind the accumulators
+    while (gs.tmem_cols < ((gs.n_tile + 31) & ~31) + a_cols) gs.tmem_cols *= 2;
     gs.n_tiles_y = (rows + gs.n_tile - 1) / gs.n_tile;
     int base_ctas = 0, slow_ctas = 0;
     for (int i = 0; i < n; ++i) {
@@ -782,6 +828,7 @@ int gemm_group_launch(const GemmOp* ops, int n, int rows, void* scratch, cudaStr
     GemmGroup g = {};
     GemmMaps maps;
     g.n_prob = n; g.rows = rows; g.n_tile = gs.n_tile; g.n_first = gs.n_first; g.tma_rows = gs.tma_rows; g.tmem_cols = gs.tmem_cols;
+    g.a_col0 = (gs.n_tile + 31) & ~31;
     g.recv_off = (gs.n_tile + 31) / 32 * 32 * G_BM * 2;
     g.counters = reinterpret_cast<unsigned*>(scratch);
     g.partials = scratch ? reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(scratch) + (size_t)G_COUNTERS * 4) : nullptr;
