@@ -11,15 +11,18 @@
 //   producer groups (G_NG groups of 4 warps; thread = one of the block's 128 weight rows): group g owns
 //               k-steps g, g + G_NG, ... It brings the row's 64 inputs of a k-step in (cp.async ring of raw
 //               quantised bytes; fp16 rows go straight to registers), de-quantises in registers (int8 ->
-//               fp16 exactly; e2m1 x e4m3 block scale -> fp16 exactly) and stores them K-major with the
-//               128-byte swizzle the MMA expects. One warp per scheduler cannot hide the latencies of this
+//               fp16 exactly; e2m1 x e4m3 block scale -> fp16 exactly) and writes them to tensor memory
+//               (tcgen05.st: its 32 registers = 32 columns of its own TMEM lane), from where the MMA reads its
+//               weight operand; shared memory carries only the activation tiles. (Compiled with G_A_TMEM_=0
+//               the weights go to shared memory instead, K-major with the 128-byte swizzle.)
+//               One warp per scheduler cannot hide the latencies of this
 //               serial instruction stream; several groups on different k-steps can. Afterwards all groups
 //               run the epilogue: tcgen05.ld of 32 columns of their 32 TMEM lanes, row / tensor scale,
 //               activation or residual; the fp16 tile is laid out in shared memory and leaves through TMA stores
 //               (a residual tile comes in through TMA loads); products with a ragged row pitch store directly;
 //   next warp : one thread issues the TMA loads of the activation tile (tensor map over X, 128B swizzle);
 //   last warp : allocates TMEM; one thread issues tcgen05.mma (kind::f16) and commits to mbarriers.
-// Three-stage operand ring, all waits bounded (status word on expiry), TMEM freed on every path. Short grids with
+// Four-stage operand ring, all waits bounded (status word on expiry), TMEM freed on every path. Short grids with
 // long K loops are split along K: every block of a tile finishes a share of its 32-row chunks, fetching the other
 // blocks' fp32 partial sums of them from a scratch area with bulk copies and adding them in a fixed order. Launched with
 // programmatic stream serialisation the kernel starts its weight stream before it waits for its predecessor.
@@ -40,10 +43,13 @@ namespace {
 constexpr int G_NG = G_NG_;      // producer groups
 constexpr int G_PROD = 128 * G_NG;
 constexpr int GT = G_PROD + 64;  // threads per block
-constexpr int G_STAGES = 3;
 #ifndef G_A_TMEM_
 #define G_A_TMEM_ 1
 #endif
+#ifndef G_STAGES_
+#define G_STAGES_ 4
+#endif
+constexpr int G_STAGES = G_STAGES_;
 constexpr bool G_A_TMEM = G_A_TMEM_ != 0;   // de-quantised weights go to tensor memory instead of shared memory
 constexpr int G_A_COLS = 32;             // TMEM columns of one weight stage: 64 inputs as fp16 pairs
 constexpr int G_BM = 128;        // weight rows per block
@@ -291,8 +297,8 @@ __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ 
 
     unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)gsm + 1023) & ~(uintptr_t)1023);
     const int b_bytes = g.n_tile * 128;
-    unsigned char* smA = base;                                  // G_STAGES x 16 KB
-    unsigned char* smB = base + G_STAGES * G_A_BYTES;           // G_STAGES x n_tile x 128 B
+    unsigned char* smA = base;                                  // G_STAGES x 16 KB (unused when the weights go to TMEM)
+    unsigned char* smB = base + (G_A_TMEM ? 0 : G_STAGES * G_A_BYTES);   // G_STAGES x n_tile x 128 B
     unsigned char* smRaw = smB + G_STAGES * b_bytes;            // raw weight ring
 
     if (tid == 0) {
@@ -738,7 +744,12 @@ struct GroupShape {
 };
 
 // Shared memory of a block (beyond the 1 KB alignment slack): operand stages + raw weight rings.
-size_t block_smem(int n_tile) { return (size_t)G_STAGES * (G_A_BYTES + (size_t)n_tile * 128) + G_RAW_BYTES; }
+size_t block_smem(int n_tile) {
+    if (!G_A_TMEM) return (size_t)G_STAGES * (G_A_BYTES + (size_t)n_tile * 128) + G_RAW_BYTES;
+    // activation stages + raw rings, and some more for the epilogue (output staging, split-K slices), up to 224 KB
+    const size_t need = (size_t)G_STAGES * n_tile * 128 + G_RAW_BYTES, want = need + 48 * 1024;
+    return want < 224 * 1024 ? want : (need > 224 * 1024 ? need : 224 * 1024);
+}
 // Split K: how many of its own chunks a block can fetch the other blocks' partial sums for at a time. They land
 // in the operand stages behind the output staging area.
 int split_recv_slots(int n_tile, int ks) {
