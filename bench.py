@@ -9,7 +9,10 @@ One "step" is one decode step of the whole model (every matrix product of the 32
 state update between them and the vocabulary head) for the workload's batch. Weights are random
 (seeded, reference checkpoint schema), since trained checkpoints are not available offline.
 
-Prints ONE JSON line. `value` is device-timed (CUDA events, inputs resident in HBM, CUDA-graph
+Prints ONE JSON line. The default workload is the batch-1 int8 decode of the 7.2B shapes; its line also carries,
+under `also`, the second configuration of the metric (NVFP4, 320 sequences per GPU: a full record with its own `e2e`,
+`roofline` and `clocks`) and the single int8 matrix-vector product of baseline config 1 with its HBM GB/s, measured in
+the same process at every N. `value` is device-timed (CUDA events, inputs resident in HBM, CUDA-graph
 replay of the library's launches); `e2e` is a decode loop through the public calls: `RWKV_x070.forward[_batch]`
 on host token ids (pinned host -> device), greedy sampling on the device, next ids read back to the host, every step.
 `--impl reference` times the CPU restatement of the reference's PyTorch path (oracle/) on the host
@@ -94,16 +97,43 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-# DRAM bytes (read + write) of ONE launch, from the profiler captures summarised under profiles/.
-# decode_kernel: captured on a model with the same block shapes and 4 blocks (1139.47 MB of traffic for 1136.80 MB of
-# algorithmic bytes); the kernel walks the same phase list per block, so the ratio carries over to 32 blocks.
-# gemm_tc_kernel: captured on the very shape bench times alone (NVFP4 [16384 x 4096], batch 320).
-DECODE_TRAFFIC_PER_ALGORITHMIC_BYTE = 1139.47 / 1136.80
-GEMM_TRAFFIC = {("nvfp4", 16384, 4096, 320): 40.46e6 + 0.11e6}
+def profiled_traffic() -> dict:
+    """DRAM bytes (read + write) per launch of the profiled kernels, read from the table in
+    profiles/dram_traffic.md (one row per ncu capture: kernel | workload key | DRAM bytes | algorithmic bytes).
+    A kernel whose capture is missing gets `traffic: null`."""
+    out = {}
+    path = os.path.join(ROOT, "profiles", "dram_traffic.md")
+    if not os.path.exists(path):
+        return out
+    for line in open(path):
+        f = [x.strip() for x in line.strip().strip("|").split("|")]
+        if len(f) >= 4 and f[0] and not set(f[0]) <= set("-: ") and f[0] != "kernel":
+            try:
+                out[(f[0], f[1])] = (float(f[2]), float(f[3]))
+            except ValueError:
+                continue
+    return out
 
 
 def decode_traffic(algorithmic_total: int, quant: str, n_embd: int):
-    return algorithmic_total * DECODE_TRAFFIC_PER_ALGORITHMIC_BYTE if (quant, n_embd) == ("int8", 4096) else None
+    """decode_kernel was captured on a model with the same block shapes and 4 blocks; the kernel walks the same
+    phase list per block, so the captured traffic / algorithmic ratio carries over to 32 blocks."""
+    t = profiled_traffic().get(("decode_kernel", f"{quant}_d{n_embd}"))
+    return algorithmic_total * t[0] / t[1] if t else None
+
+
+def gemm_traffic(quant: str, n_out: int, k: int, rows: int):
+    t = profiled_traffic().get(("gemm_tc_kernel", f"{quant}_{n_out}x{k}x{rows}"))
+    return t[0] if t else None
+
+
+def workload_config(a, workload: str, batch: int) -> dict:
+    """The `config` object of a JSON line: a function of the command line only, so both arms print the same one."""
+    from albatross_b200 import synth
+    L, D, V, _ = synth.CONFIGS[a.model]
+    return {"workload": workload, "shapes": a.model, "batch_per_gpu": batch, "n_layer": L, "n_embd": D, "vocab": V,
+            "sharding": "independent sequences per GPU, no collective in the step",
+            "l2": "inputs larger than L2: every step streams all weights of the model (GBs) from HBM"}
 
 
 def time_gemm_alone(model, B: int, dev: int, steps: int) -> dict:
@@ -147,10 +177,11 @@ def algorithmic_bytes(model, batch: int) -> dict:
 # ----------------------------------------------------------------------------------------------
 # our arm
 # ----------------------------------------------------------------------------------------------
-def run_ours(a, rank, world, dev):
+def run_ours(a, rank, world, dev, workload=None, batch=None):
     from albatross_b200 import RWKV_x070, synth
-    wl = WORKLOADS[a.workload]
-    B = a.batch or wl["batch"]
+    workload = workload or a.workload
+    wl = WORKLOADS[workload]
+    B = batch or wl["batch"]
     args = synth.make_args(a.model)
     torch.cuda.set_device(dev)
     model = RWKV_x070(args, quant=wl["quant"], state_dict=synth.iter_checkpoint(a.model, seed=0, device=f"cuda:{dev}"),
@@ -264,7 +295,7 @@ def run_ours(a, rank, world, dev):
         _, tf_burst, _ = measured_peaks(burst=True)
         roofline = {"bound": "tensor", "achieved": gm["tflops"], "peak": tf_burst, "unit": "TFLOP/s", "frac": gm["tflops"] / tf_burst,
                     "frac_of_sustained_peak": gm["tflops"] / tf,
-                    "traffic": GEMM_TRAFFIC.get((wl["quant"], 4 * args.n_embd, args.n_embd, B)),
+                    "traffic": gemm_traffic(wl["quant"], 4 * args.n_embd, args.n_embd, B),
                     "peak_source": which + " (dense bf16 cuBLAS; burst figure, the kernel is timed alone)",
                     "kernel": "gemm_tc_kernel on ffn.key [%d x %d] x batch %d" % (4 * args.n_embd, args.n_embd, B),
                     "algorithmic_flops_per_launch": gm["flops"], "us_per_launch": gm["us"],
@@ -280,9 +311,7 @@ def run_ours(a, rank, world, dev):
         "dtype": "int8 weights (dp4a, exact int32 sums), fp16 activations, fp32 WKV state" if wl["quant"] == "int8"
         else "nvfp4 weights de-quantised to fp16 in registers, fp16 activations, fp32 accumulate and WKV state",
         "data": "synthetic (seeded random weights in the reference checkpoint schema, random token ids)",
-        "config": {"workload": a.workload, "shapes": a.model, "batch_per_gpu": B, "n_layer": args.n_layer,
-                   "n_embd": args.n_embd, "vocab": V, "sharding": "independent sequences per GPU, no collective in the step",
-                   "l2": "inputs larger than L2: %.2f GB of weights streamed per step" % (ab["weights"] / 1e9)},
+        "config": workload_config(a, workload, B),
         "e2e": {"value": e2e_val, "unit": "tokens/s", "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 8 * B,
                 "ms_per_step": e2e_ms / a.steps,
                 "what": "RWKV_x070.forward[_batch] on host token ids + sampler_simple_batch on the device + ids to the host"},
@@ -366,14 +395,15 @@ def run_pipeline(a, rank, world, dev):
 # ----------------------------------------------------------------------------------------------
 # single-kernel workload: one quantised matrix-vector product (baseline config 1 and its larger shapes)
 # ----------------------------------------------------------------------------------------------
-def run_gemv(a, dev):
+def run_gemv(a, dev, workload=None, n=None, k=None):
     """Times ab_gemv alone. Each launch streams a different matrix (enough of them to exceed the L2),
     so every launch reads its weights from HBM."""
     import ctypes as C
     from albatross_b200 import _lib, quant
     torch.cuda.set_device(dev)
-    fmt = "nvfp4" if "nvfp4" in a.workload else "int8"
-    n, k = a.n_out, a.k
+    workload = workload or a.workload
+    fmt = "nvfp4" if "nvfp4" in workload else "int8"
+    n, k = n or a.n_out, k or a.k
     per = n * k * (1.0 if fmt == "int8" else 0.5625)
     n_mats = max(4, int(400e6 // per) + 1)
     torch.manual_seed(0)
@@ -402,7 +432,7 @@ def run_gemv(a, dev):
     return {"metric": "gemv_hbm_gbs", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": a.steps, "warmup": a.warmup,
             "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": fmt + " weights, fp16 activations", "data": "synthetic",
-            "config": {"workload": a.workload, "n_out": n, "k": k, "matrices_cycled": n_mats,
+            "config": {"workload": workload, "n_out": n, "k": k, "matrices_cycled": n_mats,
                        "l2": "each launch reads a different matrix; the set is larger than L2"},
             "gpu_launches": a.steps,
             "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm, "unit": "GB/s", "frac": gbs / hbm, "traffic": None,
@@ -487,7 +517,7 @@ def run_cpu(a, n_layers_sample: int = 4, steps: int = 0):
     t_block = (float(np.percentile(ts_full, 10)) - t_head) / Ls
     t_token = t_block * L + t_head
     B = a.batch or WORKLOADS[a.workload]["batch"]
-    return {"value": 1.0 / t_token, "unit": "tokens/s", "cores": cores, "kind": "port",
+    return {"value": 1.0 / t_token, "unit": "tokens/s", "cores": cores, "kind": "port", "ms_per_token": 1e3 * t_token,
             "sample": f"{Ls} of {L} blocks + head at {a.model} shapes, fp32 torch single-token path, {steps} steps, p10, "
                       f"extrapolated to {L} blocks; bsz {B} on the CPU = this rate (sequences run one after another)"}
 
@@ -507,6 +537,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host (profiling)")
     ap.add_argument("--decode-mode", default=None, choices=["persistent", "graph", "eager"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-also", action="store_true", help="default workload only: skip the bsz-320 NVFP4 and single-product records")
     ap.add_argument("--n-out", type=int, default=4096, help="gemv_* workloads: output rows")
     ap.add_argument("--k", type=int, default=4096, help="gemv_* workloads: input length")
     a = ap.parse_args()
@@ -515,18 +546,25 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
 
+    default_line = a.workload == "decode_bsz1_int8" and not a.batch and not a.no_also
     if a.impl == "reference":
         if rank != 0:
             return
         cb = run_cpu(a)
         B = a.batch or WORKLOADS[a.workload]["batch"]
-        print(json.dumps({
+        line = {
             "impl": "reference", "metric": METRIC, "value": cb["value"], "unit": "tokens/s", "n_gpus": a.gpus,
             "steps": a.steps, "warmup": a.warmup, "ms_per_step": 1e3 / cb["value"], "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "fp32 (CPU)", "data": "synthetic",
-            "config": {"workload": a.workload, "shapes": a.model, "batch_per_gpu": B},
+            "config": workload_config(a, a.workload, B),
             "cpu_baseline": cb,
-            "e2e": {"value": cb["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+            "e2e": {"value": cb["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        if default_line:
+            # the host cores run sequences one after another: 320 resident sequences decode at the single-sequence rate
+            line["also"] = {"decode_bsz320_nvfp4": {"value": cb["value"], "unit": "tokens/s",
+                                                    "config": workload_config(a, "decode_bsz320_nvfp4", 320),
+                                                    "note": "same CPU port; a batch on the host cores is a loop over sequences"}}
+        print(json.dumps(line))
         return
 
     if a.workload.startswith("gemm_"):
@@ -542,6 +580,20 @@ def main():
         torch.cuda.set_device(local)
         torch.distributed.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
     out = run_pipeline(a, rank, world, local) if a.workload.startswith("pipeline_") else run_ours(a, rank, world, local)
+    if default_line:
+        # The metric names two decode configurations and the matrix-vector bandwidth: the second configuration
+        # (7.2B NVFP4, 320 sequences per GPU) and the single int8 product are measured in the same process, at every N.
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        second = run_ours(a, rank, world, local, workload="decode_bsz320_nvfp4")
+        out["also"] = {"decode_bsz320_nvfp4": second}
+        gc.collect()
+        torch.cuda.empty_cache()
+        if rank == 0:
+            gv = run_gemv(a, local, workload="gemv_int8", n=4096, k=4096)
+            out["also"]["gemv_int8_4096x4096"] = {k_: gv[k_] for k_ in ("metric", "value", "unit", "ms_per_step", "config", "roofline")}
+            out["gpu_launches"] += second["gpu_launches"] + gv["gpu_launches"]
     if rank == 0:
         if world == 1 and not a.no_cpu_baseline and not a.workload.startswith("pipeline_"):
             out["cpu_baseline"] = run_cpu(a)
