@@ -5,6 +5,8 @@
 #include <stdint.h>
 #include <stdio.h>
 
+#include <mutex>
+
 namespace ab {
 
 // ---------------------------------------------------------------------------------------------
@@ -35,12 +37,46 @@ int check_cuda(cudaError_t e, const char* what);
         if (_s != ab::OK) return _s;                         \
     } while (0)
 
+// One-time set-up of a launcher (function attributes, device properties) is per DEVICE, not per process: a process
+// may drive several GPUs, and cudaFuncSetAttribute applies to the current one only. `run` executes `f` the first time
+// it is called with a given device current (under a lock: host threads may launch concurrently) and remembers success.
+constexpr int AB_MAX_DEVICES = 64;
+struct DeviceProps {
+    int n_sm = 0;
+    size_t smem_optin = 0;
+};
+struct PerDeviceOnce {
+    std::mutex mu;
+    bool done[AB_MAX_DEVICES] = {};
+    DeviceProps props[AB_MAX_DEVICES];
+    template <class F>
+    int run(const DeviceProps** out, F f) {
+        int dev = 0;
+        AB_CUDA(cudaGetDevice(&dev));
+        AB_CHECK_ARG(dev >= 0 && dev < AB_MAX_DEVICES, "device index %d not supported (at most %d devices per process)", dev, AB_MAX_DEVICES);
+        std::lock_guard<std::mutex> lock(mu);
+        if (!done[dev]) {
+            int v = 0, m = 0;
+            AB_CUDA(cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev));
+            AB_CUDA(cudaDeviceGetAttribute(&m, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+            props[dev].n_sm = v;
+            props[dev].smem_optin = (size_t)m;
+            const int s = f(props[dev]);
+            if (s != OK) return s;
+            done[dev] = true;
+        }
+        if (out) *out = &props[dev];
+        return OK;
+    }
+};
+
 // Device-side status word: kernels OR a bit in when a bounded wait gives up.
 // The host reads it with ab_device_status().
 static __device__ unsigned int g_device_status = 0;
 constexpr unsigned int DEV_WAIT_GEMV = 1u;
 constexpr unsigned int DEV_WAIT_GEMM = 2u;
 constexpr unsigned int DEV_WAIT_HEAD = 4u;
+constexpr unsigned int DEV_BAD_TOKEN = 8u;   // a token id outside [0, vocab) reached a kernel (it was clamped, not followed)
 
 // ---------------------------------------------------------------------------------------------
 // PTX wrappers

@@ -182,27 +182,28 @@ size_t decode_program_bytes(int n_layer, int n_blocks) {
 }
 
 int decode_launch(const DecodeProgram* prog_dev, unsigned* barrier_dev, int Kn, int xq_bytes, cudaStream_t stream) {
-    static int n_sm = 0;
-    static size_t max_smem = 0;
-    if (!n_sm) {
-        int dev = 0, v = 0, m = 0, coop = 0;
-        AB_CUDA(cudaGetDevice(&dev));
-        AB_CUDA(cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev));
-        AB_CUDA(cudaDeviceGetAttribute(&m, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
-        AB_CUDA(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev));
-        AB_CHECK_ARG(coop, "decode: device does not support cooperative launch");
-        cudaFuncAttributes fa;
-        AB_CUDA(cudaFuncGetAttributes(&fa, decode_kernel));
-        max_smem = (size_t)m - fa.sharedSizeBytes;
-        n_sm = v;
+    static PerDeviceOnce once;
+    static size_t static_smem = 0;
+    const DeviceProps* dp = nullptr;
+    {
+        const int s = once.run(&dp, [](DeviceProps& d) -> int {
+            int dev = 0, coop = 0;
+            AB_CUDA(cudaGetDevice(&dev));
+            AB_CUDA(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev));
+            AB_CHECK_ARG(coop, "decode: device does not support cooperative launch");
+            cudaFuncAttributes fa;
+            AB_CUDA(cudaFuncGetAttributes(&fa, decode_kernel));
+            static_smem = fa.sharedSizeBytes;
+            // the largest dynamic size the device allows next to the kernel's static shared memory, set once
+            AB_CUDA(cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(d.smem_optin - fa.sharedSizeBytes)));
+            return (int)OK;
+        });
+        if (s != OK) return s;
     }
+    const int n_sm = dp->n_sm;
+    const size_t max_smem = dp->smem_optin - static_smem;
     const size_t smem = gemv_layout(Kn, 1, xq_bytes).total;
     AB_CHECK_ARG(smem <= max_smem, "decode: needs %zu bytes of shared memory (limit %zu)", smem, max_smem);
-    static size_t smem_set = 0;
-    if (smem > smem_set) {
-        AB_CUDA(cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        smem_set = smem;
-    }
     int per_sm = 0;
     AB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_kernel, GEMV_THREADS, smem));
     AB_CHECK_ARG(per_sm >= 1, "decode: kernel does not fit on an SM");

@@ -63,6 +63,7 @@ struct ab_model {
     int smem_prefetch = 0;
     int early_slice = 0;   // measured slower: any weight traffic in flight delays the loads of the input vector
     int barrier_prefetch = 0;   // measured slower: the polls of the barrier queue behind the prefetch traffic
+    int stage_gemv = 0;  // ab_forward_stage at B = T = 1 runs the batch-1 matrix-vector kernels instead of the row-wise program
     int merge_ups = 0;   // persistent decode kernel: block h computes the adapter up-projections of head h inside the head
                          // phase: one phase and barrier fewer per block and the same arithmetic as the per-phase
                          // launches (identical logits), but 3 % slower per token than the phase of matrix-vector rows
@@ -143,9 +144,21 @@ Workspace carve(const ab_model* m, int B, int T, unsigned char* base) {
         }                                                                                          \
     } while (0)
 
-int forward_one(ab_model* m, const int32_t* token, void* const* state, const Workspace& ws, __half* logits,
-                cudaStream_t st) {
+// Pipeline-stage view of a forward pass: where the hidden state comes from and where it goes.
+struct StageIO {
+    const __half* x_in;   // [M, D] hidden state from the previous stage (null: gather the embedding rows)
+    __half* v_first;      // [M, D] layer-0 value, produced by the first stage and read by every later block
+    __half* x_out;        // [M, D] hidden state for the next stage (null: final norm + vocabulary head)
+};
+
+int forward_one(ab_model* m, const int32_t* token, void* const* state, const Workspace& ws_in, __half* logits,
+                cudaStream_t st, const StageIO* io = nullptr) {
     const int D = m->d.n_embd, H = D / HEAD;
+    Workspace ws = ws_in;
+    if (io && io->v_first) ws.vfirst = io->v_first;
+    const bool from_x = io && io->x_in;
+    if (from_x) AB_CUDA(cudaMemcpyAsync(ws.x, io->x_in, (size_t)D * 2, cudaMemcpyDeviceToDevice, st));
+    const int g0 = m->layer_offset;   // index of this model's first block in the whole network
     for (int i = 0; i < m->d.n_layer; ++i) {
         const ab_layer& L = m->layers[i];
         __half* att_prev = (__half*)state[3 * i];
@@ -154,7 +167,7 @@ int forward_one(ab_model* m, const int32_t* token, void* const* state, const Wor
         {   // LN1 + shift-lerps + r/k/v + adapter-down rows
             GemvParams p = {};
             p.K = D; p.use_pdl = m->use_pdl;
-            if (i == 0) { p.emb = (const __half*)m->d.emb; p.token = token; p.x_copy = ws.x; }
+            if (i == 0 && !from_x) { p.emb = (const __half*)m->d.emb; p.token = token; p.emb_rows = m->d.vocab; p.x_copy = ws.x; }
             else p.x = ws.x;
             p.x_prev = att_prev; p.ln_w = (const __half*)L.ln1_w; p.ln_b = (const __half*)L.ln1_b; p.ln_out = ws.xn;
             int n = 0;
@@ -163,18 +176,18 @@ int forward_one(ab_model* m, const int32_t* token, void* const* state, const Wor
             p.seg[n++] = seg_of(L.value, L.x_v, EPI_NONE, ws.v);
             p.seg[n++] = seg_of(L.w1t, L.x_w, EPI_TANH, ws.hw);
             p.seg[n++] = seg_of(L.a1t, L.x_a, EPI_NONE, ws.ha);
-            if (i > 0) p.seg[n++] = seg_of(L.v1t, L.x_v, EPI_NONE, ws.hv);
+            if (g0 + i > 0) p.seg[n++] = seg_of(L.v1t, L.x_v, EPI_NONE, ws.hv);
             p.seg[n++] = seg_of(L.g1t, L.x_g, EPI_SIGMOID, ws.hg);
             p.nseg = n;
             AB_STEP(m, st, i, "rkv+adapter-down gemv", gemv_launch(p, st));
         }
         {   // per-head: adapter up-projections, glue, WKV state update, group norm, bonus, gate
             HeadParams h = {};
-            h.B = 1; h.T = 1; h.D = D; h.H = H; h.layer0 = (i == 0);
+            h.B = 1; h.T = 1; h.D = D; h.H = H; h.layer0 = (g0 + i == 0);
             h.state = kv; h.r = ws.r; h.k = ws.k; h.v = ws.v; h.v_first = ws.vfirst;
             h.hw = ws.hw; h.ha = ws.ha; h.hv = ws.hv; h.hg = ws.hg;
             h.w2 = (const __half*)L.w2; h.a2 = (const __half*)L.a2; h.v2 = (const __half*)L.v2; h.g2 = (const __half*)L.g2;
-            h.rw = L.w1t.n_out; h.ra = L.a1t.n_out; h.rv = (i == 0) ? 0 : L.v1t.n_out; h.rg = L.g1t.n_out;
+            h.rw = L.w1t.n_out; h.ra = L.a1t.n_out; h.rv = (g0 + i == 0) ? 0 : L.v1t.n_out; h.rg = L.g1t.n_out;
             h.w0 = (const __half*)L.w0; h.a0 = (const __half*)L.a0; h.v0 = (const __half*)L.v0;
             h.k_k = (const __half*)L.k_k; h.k_a = (const __half*)L.k_a; h.r_k = (const __half*)L.r_k;
             h.lnx_w = (const __half*)L.lnx_w; h.lnx_b = (const __half*)L.lnx_b;
@@ -201,6 +214,10 @@ int forward_one(ab_model* m, const int32_t* token, void* const* state, const Wor
             p.copy_src = ws.xn2; p.copy_dst = ffn_prev; p.copy_n = D;
             AB_STEP(m, st, i, "ffn value gemv", gemv_launch(p, st));
         }
+    }
+    if (io && io->x_out) {
+        AB_CUDA(cudaMemcpyAsync(io->x_out, ws.x, (size_t)D * 2, cudaMemcpyDeviceToDevice, st));
+        return OK;
     }
     GemvParams p = {};
     p.K = D; p.use_pdl = m->use_pdl; p.x = ws.x; p.nseg = 1;
@@ -252,7 +269,7 @@ int build_decode_program(ab_model* m, const int32_t* token, void* const* state, 
         {
             GemvParams p = {};
             p.K = D;
-            if (i == 0) { p.emb = (const __half*)m->d.emb; p.token = token; p.x_copy = ws.x; }
+            if (i == 0) { p.emb = (const __half*)m->d.emb; p.token = token; p.emb_rows = m->d.vocab; p.x_copy = ws.x; }
             else p.x = ws.x;
             p.x_prev = att_prev; p.ln_w = (const __half*)Ly.ln1_w; p.ln_b = (const __half*)Ly.ln1_b; p.ln_out = ws.xn;
             int k = 0;
@@ -371,20 +388,13 @@ int time_mix_up_ops(const ab_layer& L, int layer, const Workspace& ws, GemmOp* o
     return n;
 }
 
-// Pipeline-stage view of a forward pass: where the hidden state comes from and where it goes.
-struct StageIO {
-    const __half* x_in;   // [M, D] hidden state from the previous stage (null: gather the embedding rows)
-    __half* v_first;      // [M, D] layer-0 value, produced by the first stage and read by every later block
-    __half* x_out;        // [M, D] hidden state for the next stage (null: final norm + vocabulary head)
-};
-
 int forward_rows(ab_model* m, int B, int T, const int32_t* tokens, void* const* state, const Workspace& ws_in,
                  __half* logits, int full_output, cudaStream_t st, const StageIO* io = nullptr) {
     const int D = m->d.n_embd, H = D / HEAD, M = B * T;
     Workspace ws = ws_in;
     if (io && io->v_first) ws.vfirst = io->v_first;
     if (io && io->x_in) AB_CUDA(cudaMemcpyAsync(ws.x, io->x_in, (size_t)M * D * 2, cudaMemcpyDeviceToDevice, st));
-    else AB_TRY(gather_rows((const __half*)m->d.emb, tokens, M, D, ws.x, st));
+    else AB_TRY(gather_rows((const __half*)m->d.emb, tokens, M, D, m->d.vocab, ws.x, st));
     const int g0 = m->layer_offset;   // index of this model's first block in the whole network
     for (int li = 0; li < m->d.n_layer; ++li) {
         const int i = li;
@@ -460,6 +470,12 @@ int ab_device_status(uint32_t* status_host) {
     AB_CUDA(cudaMemcpyFromSymbol(&v, g_device_status, sizeof(v)));
     AB_CUDA(cudaMemcpyToSymbol(g_device_status, &zero, sizeof(zero)));
     *status_host = v;
+    if (v != 0) {
+        // a wait that gave up may have left split-K arrival counters behind: those of the built-in scratch area are
+        // put back to zero here (callers of ab_gemm / ab_forward must clear their own scratch / workspace)
+        AB_TRY(static_scratch_reset(nullptr));
+        AB_CUDA(cudaDeviceSynchronize());
+    }
     return OK;
 }
 
@@ -478,10 +494,15 @@ int ab_gemv(const ab_mat* m, const void* x, void* y, void* stream) {
     return gemv_launch(p, (cudaStream_t)stream);
 }
 
-size_t ab_gemm_scratch_bytes(const ab_mat* m, int rows) { return m ? gemm_scratch_bytes(*m, rows) : 0; }
+size_t ab_gemm_scratch_bytes(const ab_mat* m, int rows) {
+    if (!m || rows <= 0 || check_mat(*m, "ab_gemm_scratch_bytes") != OK) return 0;
+    return gemm_scratch_bytes(*m, rows);
+}
 
 int ab_gemm(const ab_mat* m, int rows, const void* x, void* y, int epi, const void* resid, void* scratch, void* stream) {
     AB_CHECK_ARG(m && x && y, "ab_gemm: null pointer");
+    AB_CHECK_ARG(rows > 0, "ab_gemm: rows must be positive");
+    AB_TRY(check_mat(*m, "ab_gemm"));
     AB_CHECK_ARG(epi >= EPI_NONE && epi <= EPI_RESID && (epi != EPI_RESID || resid), "ab_gemm: bad epilogue");
     return gemm_launch(*m, rows, (const __half*)x, (__half*)y, epi, (const __half*)resid, scratch, (cudaStream_t)stream);
 }
@@ -568,6 +589,7 @@ int ab_model_set_option(ab_model* m, const char* name, int value) {
     else if (!strcmp(name, "l2_prefetch_kb")) m->l2_prefetch_kb = value < 0 ? 0 : value;
     else if (!strcmp(name, "smem_prefetch")) m->smem_prefetch = value != 0;
     else if (!strcmp(name, "merge_ups")) m->merge_ups = value != 0;
+    else if (!strcmp(name, "stage_gemv")) m->stage_gemv = value != 0;
     else if (!strcmp(name, "early_slice")) m->early_slice = value != 0;
     else if (!strcmp(name, "barrier_prefetch")) m->barrier_prefetch = value != 0;
     else if (!strcmp(name, "layer_offset")) { AB_CHECK_ARG(value >= 0, "layer_offset must be >= 0"); m->layer_offset = value; }
@@ -600,7 +622,13 @@ int ab_forward_stage(ab_model* m, int B, int T, const int32_t* tokens, const voi
     for (int i = 0; i < 3 * m->d.n_layer; ++i) AB_CHECK_ARG(state[i], "ab_forward_stage: state[%d] is null", i);
     const Workspace ws = carve(m, B, T, (unsigned char*)workspace);
     StageIO io = {(const __half*)x_in, (__half*)v_first, (__half*)x_out};
-    // stages always take the row-wise (batched) program, also at B = T = 1
+    // stages take the row-wise (batched) program, also at B = T = 1, unless option "stage_gemv" asks for the
+    // batch-1 matrix-vector kernels
+    if (B == 1 && T == 1 && m->stage_gemv) {
+        for (const ab_layer& l : m->layers)
+            AB_CHECK_ARG(l.w2 && l.a2 && l.g2, "ab_forward_stage: adapter up-projections missing");
+        return forward_one(m, tokens, state, ws, (__half*)logits, (cudaStream_t)stream, &io);
+    }
     return forward_rows(m, B, T, tokens, state, ws, (__half*)logits, 0, (cudaStream_t)stream, &io);
 }
 

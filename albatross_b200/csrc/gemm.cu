@@ -761,7 +761,7 @@ int split_recv_slots(int n_tile, int ks) {
     return fit < own_max ? fit : own_max;
 }
 
-GroupShape group_shape(const GemmOp* ops, int n, int rows) {
+GroupShape group_shape(const GemmOp* ops, int n, int rows, int n_sm) {
     GroupShape gs = {};
     if (rows <= 256) { gs.n_tile = (rows + 15) & ~15; gs.n_first = gs.tma_rows = gs.n_tile; }
     else if (rows <= 320) { gs.n_tile = (rows + 31) & ~31; gs.n_first = 192; gs.tma_rows = gs.n_tile % 64 ? 32 : 64; }
@@ -779,15 +779,15 @@ GroupShape group_shape(const GemmOp* ops, int n, int rows) {
     for (int i = 0; i < n; ++i) {
         const int ksteps = (ops[i].w.k + G_BK - 1) / G_BK;
         int ks = 1;
-        if (base_ctas < 100 && ksteps >= 32) {   // too few tiles to fill the GPU: split the long K loops
-            ks = 148 / base_ctas;
+        if (base_ctas > 0 && base_ctas < (100 * n_sm) / 148 && ksteps >= 32) {   // too few tiles to fill the GPU: split the long K loops
+            ks = n_sm / base_ctas;
             if (ks > 8) ks = 8;
             if (ks > ksteps / 8) ks = ksteps / 8;
             if (ks < 1) ks = 1;
-        } else if (base_ctas < 148 && slow_ctas > 0 && ops[i].w.fmt == FMT_F16 && ksteps >= 32) {
+        } else if (base_ctas < n_sm && slow_ctas > 0 && ops[i].w.fmt == FMT_F16 && ksteps >= 32) {
             // A nearly full grid whose fp16 products (twice to four times the bytes per k-step of the quantised
             // ones, fetched only two k-steps ahead) would finish last: the idle SMs take slices of their K loops.
-            ks = 1 + (148 - base_ctas) / slow_ctas;
+            ks = 1 + (n_sm - base_ctas) / slow_ctas;
             if (ks > 8) ks = 8;
             if (ks > ksteps / 8) ks = ksteps / 8;
             if (ks < 1) ks = 1;
@@ -806,8 +806,19 @@ GroupShape group_shape(const GemmOp* ops, int n, int rows) {
 
 }  // namespace
 
+// SMs of the current device (148 on B200); the split-K decisions depend on it.
+int current_sm_count() {
+    static PerDeviceOnce once;
+    const DeviceProps* dp = nullptr;
+    if (once.run(&dp, [](DeviceProps&) -> int { return OK; }) != OK || !dp || dp->n_sm <= 0) return 148;
+    return dp->n_sm;
+}
+
 size_t gemm_group_scratch_bytes(const GemmOp* ops, int n, int rows) {
-    const GroupShape gs = group_shape(ops, n, rows);
+    if (!ops || n < 1 || n > G_MAX_OPS || rows <= 0) return 0;
+    for (int i = 0; i < n; ++i)
+        if (ops[i].w.n_out <= 0 || ops[i].w.k <= 0) return 0;
+    const GroupShape gs = group_shape(ops, n, rows, current_sm_count());
     return (size_t)G_COUNTERS * 4 + (size_t)gs.part_floats * 4 + 256;
 }
 size_t gemm_scratch_bytes(const ab_mat& m, int rows) {
@@ -818,18 +829,19 @@ size_t gemm_scratch_bytes(const ab_mat& m, int rows) {
 
 int gemm_group_launch(const GemmOp* ops, int n, int rows, void* scratch, cudaStream_t stream, bool pdl) {
     AB_CHECK_ARG(ops && n >= 1 && n <= G_MAX_OPS && rows > 0, "gemm: bad group (n=%d rows=%d)", n, rows);
-    const GroupShape gs = group_shape(ops, n, rows);
+    for (int i = 0; i < n; ++i) {   // shapes first: the grid arithmetic below divides by tile counts
+        const int s = check_mat(ops[i].w, "gemm");
+        if (s != OK) return s;
+    }
+    const int n_sm = current_sm_count();
+    GroupShape gs = group_shape(ops, n, rows, n_sm);
     AB_CHECK_ARG(gs.n_split_tiles <= G_COUNTERS, "gemm: too many split-K tiles");
-    if (gs.n_split_tiles > 0) {
-        // the blocks of a split tile wait for one another: all of them must be resident (one block per SM)
-        static int n_sm = 0;
-        if (!n_sm) {
-            int dev = 0, v = 0;
-            AB_CUDA(cudaGetDevice(&dev));
-            AB_CUDA(cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev));
-            n_sm = v;
-        }
-        AB_CHECK_ARG(gs.grid_x * gs.n_tiles_y <= n_sm, "gemm: a split-K grid of %d blocks does not fit %d SMs", gs.grid_x * gs.n_tiles_y, n_sm);
+    if (gs.n_split_tiles > 0 && gs.grid_x * gs.n_tiles_y > n_sm) {
+        // the blocks of a split tile wait for one another, so all of them must be resident (one block per SM); a
+        // split grid that would not be is launched without the split instead
+        GemmOp unsplit[G_MAX_OPS];
+        for (int i = 0; i < n; ++i) unsplit[i] = ops[i];
+        gs = group_shape(unsplit, n, rows, 0);   // no SMs to fill: every product keeps its whole K loop
     }
     AB_CHECK_ARG(gs.part_floats == 0 || (scratch && ((uintptr_t)scratch & 15) == 0), "gemm: split-K needs a 16-byte aligned scratch area");
     EncodeTiledFn encode;
@@ -901,11 +913,15 @@ int gemm_group_launch(const GemmOp* ops, int n, int rows, void* scratch, cudaStr
     for (int i = n; i < G_MAX_OPS; ++i) { maps.m[i] = maps.m[0]; maps.y[i] = maps.m[0]; maps.r[i] = maps.m[0]; }
 
     const size_t smem = 1024 + block_smem(gs.n_tile);
-    static size_t smem_set = 0;
-    if (smem > smem_set) {
-        AB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        AB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        smem_set = smem;
+    {
+        static PerDeviceOnce once;
+        const int s = once.run(nullptr, [](DeviceProps& d) -> int {
+            // the largest dynamic size the device allows (the kernels' static shared memory is under 1 KB)
+            AB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d.smem_optin - 1024));
+            AB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d.smem_optin - 1024));
+            return OK;
+        });
+        if (s != OK) return s;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(gs.grid_x, gs.n_tiles_y);
@@ -953,16 +969,19 @@ namespace {
 
 static __device__ __align__(256) unsigned char g_static_scratch[AB_GEMM_STATIC_SCRATCH_BYTES];
 
-constexpr int STATIC_MAX_DEVICES = 64;
+constexpr int STATIC_MAX_DEVICES = AB_MAX_DEVICES;
+std::mutex g_static_mu;
+void* g_static_ptrs[STATIC_MAX_DEVICES] = {};
 
-// Address of the array on the current device, looked up once per device; the counters are cleared on `stream`
-// when a device is first used (the kernels need them at zero and leave them at zero).
+// Address of the array on the current device, looked up once per device (under a lock: the first calls of two host
+// threads may coincide); the counters are cleared on `stream` when a device is first used (the kernels need them at
+// zero and leave them at zero).
 int static_scratch(void** out, cudaStream_t stream) {
-    static void* ptrs[STATIC_MAX_DEVICES] = {};
     int dev = 0;
     AB_CUDA(cudaGetDevice(&dev));
     AB_CHECK_ARG(dev >= 0 && dev < STATIC_MAX_DEVICES, "ab_gemm_static: device index %d not supported", dev);
-    if (!ptrs[dev]) {
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    if (!g_static_ptrs[dev]) {
         void* ptr = nullptr;
         const cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
         if (e != cudaSuccess || !ptr) {
@@ -970,12 +989,27 @@ int static_scratch(void** out, cudaStream_t stream) {
             return ERR_CUDA;
         }
         AB_CUDA(cudaMemsetAsync(ptr, 0, (size_t)G_COUNTERS * 4, stream));
-        ptrs[dev] = ptr;
+        g_static_ptrs[dev] = ptr;
     }
-    *out = ptrs[dev];
+    *out = g_static_ptrs[dev];
     return OK;
 }
 
+}  // namespace
+
+// Puts the arrival counters of the built-in scratch area of the current device back to zero (nothing to do if the
+// device has not used it yet). The kernels leave them at zero themselves, except when a bounded wait gave up or a
+// launch was aborted half-way; then every later split-K product through ab_gemm_static would read stale counts.
+int static_scratch_reset(cudaStream_t stream) {
+    int dev = 0;
+    AB_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= STATIC_MAX_DEVICES) return OK;
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    if (g_static_ptrs[dev]) AB_CUDA(cudaMemsetAsync(g_static_ptrs[dev], 0, (size_t)G_COUNTERS * 4, stream));
+    return OK;
+}
+
+namespace {
 }  // namespace
 }  // namespace ab
 
@@ -997,5 +1031,22 @@ extern "C" int ab_gemm_static(const ab_mat* m, int rows, const void* x, void* y,
     st = static_scratch(&scratch, (cudaStream_t)stream);
     if (st != OK) return st;
     return gemm_launch(*m, rows, (const __half*)x, (__half*)y, epi, (const __half*)resid, scratch, (cudaStream_t)stream);
+}
+
+extern "C" int ab_gemm_static_reset(void* stream) { return ab::static_scratch_reset((cudaStream_t)stream); }
+
+// Test hook: reads (write == 0) or overwrites (write != 0) arrival counter `index` of the built-in scratch area of the
+// current device, through `value_host`. Synchronises the device.
+extern "C" int ab_gemm_static_debug_counter(int index, int write, uint32_t* value_host) {
+    using namespace ab;
+    AB_CHECK_ARG(value_host && index >= 0 && index < G_COUNTERS, "ab_gemm_static_debug_counter: bad argument");
+    void* scratch = nullptr;
+    const int st = static_scratch(&scratch, nullptr);
+    if (st != OK) return st;
+    AB_CUDA(cudaDeviceSynchronize());
+    uint32_t* p = reinterpret_cast<uint32_t*>(scratch) + index;
+    if (write) AB_CUDA(cudaMemcpy(p, value_host, 4, cudaMemcpyHostToDevice));
+    else AB_CUDA(cudaMemcpy(value_host, p, 4, cudaMemcpyDeviceToHost));
+    return OK;
 }
 

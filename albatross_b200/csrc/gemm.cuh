@@ -20,6 +20,7 @@ size_t gemm_group_scratch_bytes(const GemmOp* ops, int n, int rows);
 // started its weight stream).
 int gemm_group_launch(const GemmOp* ops, int n, int rows, void* scratch, cudaStream_t stream, bool pdl = false);
 size_t gemm_scratch_bytes(const ab_mat& m, int rows);
+int static_scratch_reset(cudaStream_t stream);   // built-in scratch of ab_gemm_static: counters back to zero
 int gemm_launch(const ab_mat& m, int rows, const __half* x, __half* y, int epi, const __half* resid, void* scratch,
                 cudaStream_t stream, bool pdl = false);
 int dequant_launch(const ab_mat& m, float* out, cudaStream_t stream);

@@ -46,6 +46,7 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const int Kn, const int
 int gemv_check(GemvParams& p) {
     AB_CHECK_ARG(p.nseg >= 1 && p.nseg <= GEMV_MAX_SEG, "gemv: nseg %d out of range", p.nseg);
     const bool shared_in = p.emb || p.x;
+    AB_CHECK_ARG(!p.emb || (p.token && p.emb_rows > 0), "gemv: embedding input needs a token pointer and the table's row count");
     AB_CHECK_ARG(!shared_in || (p.K >= 16 && p.K % 16 == 0 && p.K <= 32768), "gemv: K=%d must be a multiple of 16 in [16, 32768]", p.K);
     for (int s = 0; s < p.nseg; ++s) {
         GemvSeg& g = p.seg[s];
@@ -97,20 +98,19 @@ int gemv_launch(const GemvParams& p_in, cudaStream_t stream) {
     GemvParams p = p_in;
     int st = gemv_check(p);
     if (st != OK) return st;
-    static int n_sm = 0;
-    static size_t max_smem = 0;
-    if (!n_sm) {
-        int dev = 0, v = 0;
-        AB_CUDA(cudaGetDevice(&dev));
-        AB_CUDA(cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev));
-        int m = 0;
-        AB_CUDA(cudaDeviceGetAttribute(&m, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+    static PerDeviceOnce once;
+    static size_t static_smem = 0;
+    const DeviceProps* dp = nullptr;
+    st = once.run(&dp, [](DeviceProps& d) -> int {
         cudaFuncAttributes fa;
         AB_CUDA(cudaFuncGetAttributes(&fa, gemv_stream_kernel));
-        max_smem = (size_t)m - fa.sharedSizeBytes;
-        AB_CUDA(cudaFuncSetAttribute(gemv_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)max_smem));
-        n_sm = v;
-    }
+        static_smem = fa.sharedSizeBytes;
+        AB_CUDA(cudaFuncSetAttribute(gemv_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(d.smem_optin - fa.sharedSizeBytes)));
+        return (int)OK;
+    });
+    if (st != OK) return st;
+    const int n_sm = dp->n_sm;
+    const size_t max_smem = dp->smem_optin - static_smem;
     const GemvLaunchShape sh = gemv_shape(p);
     const size_t smem = gemv_layout(sh.Kn, sh.with_dx, sh.xq_bytes).total;
     AB_CHECK_ARG(smem <= max_smem, "gemv: launch needs %zu bytes of shared memory (limit %zu)", smem, max_smem);

@@ -36,6 +36,7 @@ struct __align__(16) GemvParams {
     const __half* x;        // shared input vector [K] (ignored when emb != null)
     const __half* emb;      // optional embedding table [V,K]: x = emb[token[0]]
     const int* token;
+    int emb_rows;           // rows of the embedding table: a token id outside [0, emb_rows) is clamped and reported
     const __half* x_prev;   // token-shift state [K] (needed when any seg has mix)
     const __half* ln_w;     // layer-norm weight/bias [K], or null: no normalisation
     const __half* ln_b;

@@ -532,7 +532,15 @@ __device__ __forceinline__ void gemv_consume(const GemvParams& p, const BlockPla
     const bool shared_in = p.emb || p.x;
     if (shared_in) {
         const int K = p.K;
-        const __half* xin = p.emb ? p.emb + (size_t)__ldcg(p.token) * K : p.x;
+        const __half* xin = p.x;
+        if (p.emb) {
+            int tok = __ldcg(p.token);
+            if ((unsigned)tok >= (unsigned)p.emb_rows) {   // never index past the table: clamp and tell the host
+                tok = tok < 0 ? 0 : p.emb_rows - 1;
+                if (tid == 0 && bid == 0) atomicOr(&g_device_status, DEV_BAD_TOKEN);
+            }
+            xin = p.emb + (size_t)tok * K;
+        }
         bool any_mix = false;
         for (int s = 0; s < p.nseg; ++s) any_mix |= p.seg[s].mix != nullptr;
         // One pass when K / 8 <= threads (every thread keeps its 8 inputs, weights, bias and previous inputs in

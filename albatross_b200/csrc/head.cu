@@ -174,7 +174,12 @@ __global__ void __launch_bounds__(HB_THREADS, HB_BLOCKS) head_batch_kernel(const
             mbar_expect_tx(&full[s], HB_STATE_BYTES);
             bulk_g2s(dsm + s * HB_STATE_BYTES, p.state + (size_t)item_of(n) * 4096, HB_STATE_BYTES, &full[s]);
         };
-        // the state was last written by this kernel one token ago: it does not depend on the preceding kernel
+        // The state is requested BEFORE the wait for the preceding grid. That is safe because its last writer is this
+        // same kernel one decode step earlier, hundreds of launches back, and programmatic launch cannot stack that
+        // deep: a grid may start early only once EVERY block of its predecessor has started, and no block of any
+        // grid of the step exits before its own wait has passed, i.e. before the grid in front of it is complete.
+        // For this request to overtake that writer, all blocks of all launches in between would have to be resident
+        // at once; the products between two head launches alone are hundreds of blocks that each fill an SM.
         if (lane == 0)
             for (int n = 0; n < HB_STAGES && n < n_mine; ++n) load_state_of(n);
         if (p.use_pdl) {
@@ -359,14 +364,16 @@ int head_launch(const HeadParams& p, cudaStream_t stream) {
     AB_CHECK_ARG(!ups || (p.B == 1 && p.T == 1), "head: in-kernel adapter up-projection is the batch-1 path");
     if (!ups && p.T == 1 && p.B * p.H >= 512) {
         // many sequences, one step each: persistent blocks with the state staged by bulk copies
-        static int n_sm = 0;
-        if (!n_sm) {
-            int dev = 0, v = 0;
-            AB_CUDA(cudaGetDevice(&dev));
-            AB_CUDA(cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev));
-            AB_CUDA(cudaFuncSetAttribute(head_batch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, HB_STAGES * HB_STATE_BYTES));
-            n_sm = v;
+        static PerDeviceOnce once;
+        const DeviceProps* dp = nullptr;
+        {
+            const int s = once.run(&dp, [](DeviceProps&) -> int {
+                return check_cuda(cudaFuncSetAttribute(head_batch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, HB_STAGES * HB_STATE_BYTES),
+                                  "cudaFuncSetAttribute(head_batch_kernel)");
+            });
+            if (s != OK) return s;
         }
+        const int n_sm = dp->n_sm;
         AB_CHECK_ARG(((uintptr_t)p.state & 15) == 0, "head: state must be 16-byte aligned");
         const int n_items = p.B * p.H;
         cudaLaunchConfig_t cfg = {};
@@ -386,14 +393,16 @@ int head_launch(const HeadParams& p, cudaStream_t stream) {
     if (ups) {
         smem = head_ups_smem(p.rw + p.ra + p.rv + p.rg);
     }
-    static size_t max_smem = 0;
-    if (!max_smem) {
-        int dev = 0, m = 0;
-        AB_CUDA(cudaGetDevice(&dev));
-        AB_CUDA(cudaDeviceGetAttribute(&m, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
-        AB_CUDA(cudaFuncSetAttribute(head_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, m - 4096));
-        max_smem = (size_t)m - 4096;
+    static PerDeviceOnce once_fused;
+    const DeviceProps* dpf = nullptr;
+    {
+        const int s = once_fused.run(&dpf, [](DeviceProps& d) -> int {
+            return check_cuda(cudaFuncSetAttribute(head_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d.smem_optin - 4096),
+                              "cudaFuncSetAttribute(head_fused_kernel)");
+        });
+        if (s != OK) return s;
     }
+    const size_t max_smem = dpf->smem_optin - 4096;
     if (smem > max_smem) {
         set_error("head: adapter ranks need %zu bytes of shared memory (limit %zu)", smem, max_smem);
         return ERR_TOO_LARGE;

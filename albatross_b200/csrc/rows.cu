@@ -23,9 +23,14 @@ __device__ __forceinline__ float block_sum_rt(float v, float* red) {
 }
 
 __global__ void __launch_bounds__(RT) gather_rows_kernel(const __half* __restrict__ table, const int* __restrict__ idx,
-                                                         int D, __half* __restrict__ out) {
+                                                         int D, int vocab, __half* __restrict__ out) {
     const size_t m = blockIdx.x;
-    const uint4* src = reinterpret_cast<const uint4*>(table + (size_t)idx[m] * D);
+    int tok = idx[m];
+    if ((unsigned)tok >= (unsigned)vocab) {   // never index past the table: clamp and tell the host
+        tok = tok < 0 ? 0 : vocab - 1;
+        if (threadIdx.x == 0) atomicOr(&g_device_status, DEV_BAD_TOKEN);
+    }
+    const uint4* src = reinterpret_cast<const uint4*>(table + (size_t)tok * D);
     uint4* dst = reinterpret_cast<uint4*>(out + m * D);
     for (int i = threadIdx.x; i < D / 8; i += RT) dst[i] = src[i];
 }
@@ -221,9 +226,9 @@ __global__ void __launch_bounds__(RT) last_rows_kernel(const __half* __restrict_
 
 }  // namespace
 
-int gather_rows(const __half* table, const int* idx, int rows, int D, __half* out, cudaStream_t s) {
-    AB_CHECK_ARG(table && idx && out && rows > 0 && D % 8 == 0, "gather_rows: bad argument");
-    gather_rows_kernel<<<rows, RT, 0, s>>>(table, idx, D, out);
+int gather_rows(const __half* table, const int* idx, int rows, int D, int vocab, __half* out, cudaStream_t s) {
+    AB_CHECK_ARG(table && idx && out && rows > 0 && D % 8 == 0 && vocab > 0, "gather_rows: bad argument");
+    gather_rows_kernel<<<rows, RT, 0, s>>>(table, idx, D, vocab, out);
     AB_CUDA(cudaGetLastError());
     return OK;
 }

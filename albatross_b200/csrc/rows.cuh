@@ -12,7 +12,7 @@ struct MixParams {
     int n_mix, B, T, D;
 };
 
-int gather_rows(const __half* table, const int* idx, int rows, int D, __half* out, cudaStream_t s);
+int gather_rows(const __half* table, const int* idx, int rows, int D, int vocab, __half* out, cudaStream_t s);
 int ln_rows(const __half* x, const __half* w, const __half* b, int rows, int D, int stride, int offset, __half* out,
             cudaStream_t s);
 int mix_rows(const MixParams& p, cudaStream_t s);

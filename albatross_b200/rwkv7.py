@@ -262,6 +262,22 @@ class RWKV_x070:
         _lib.check(_lib.lib.ab_forward(self._handle, B, T, tokens_dev.data_ptr(), ptrs, base, logits.data_ptr(),
                                        int(full_output), torch.cuda.current_stream().cuda_stream), "ab_forward")
 
+    def _check_ids(self, ids) -> None:
+        """Token ids are validated on the host, where they still are Python numbers: an id outside the embedding
+        table raises IndexError as `z['emb.weight'][idx]` does in the reference (reference/rwkv7.py:132, :163,
+        :195). (The kernels clamp such an id and set a status bit all the same; they never read past the table.)"""
+        flat = ids if isinstance(ids, (list, tuple)) else [ids]
+        if flat and isinstance(flat[0], (list, tuple)):
+            lo = min(min(r) for r in flat)
+            hi = max(max(r) for r in flat)
+        else:
+            lo, hi = min(flat), max(flat)
+        if lo < -self.vocab or hi >= self.vocab:
+            raise IndexError(f"token id {lo if lo < -self.vocab else hi} is out of range for a vocabulary of {self.vocab}")
+
+    def _wrap_id(self, idx: int) -> int:
+        return int(idx) + self.vocab if idx < 0 else int(idx)     # torch indexing counts negative ids from the end
+
     # ---- the reference's public entry points ------------------------------------------------
     def forward(self, idx, state, full_output=False):
         if state is None:
@@ -282,6 +298,8 @@ class RWKV_x070:
     @torch.no_grad()
     def forward_one(self, idx: int, state: List[torch.Tensor]):
         self._check_state(state, None)
+        self._check_ids(idx)
+        idx = self._wrap_id(idx)
         if self.decode_mode == "persistent":
             return self._forward_one_persistent(idx, state)
         if self.decode_mode == "eager":
@@ -371,7 +389,8 @@ class RWKV_x070:
     def forward_seq(self, idx: List[int], state: List[torch.Tensor], full_output: bool = False):
         self._check_state(state, None)
         T = len(idx)
-        tok = torch.tensor(idx, dtype=torch.int32, device=self.device)
+        self._check_ids(idx)
+        tok = torch.tensor([self._wrap_id(t) for t in idx], dtype=torch.int32, device=self.device)
         logits = torch.empty((T, self.vocab) if full_output else (self.vocab,), dtype=DTYPE, device=self.device)
         self._run(1, T, tok, state, logits, full_output)
         return logits, list(state)
@@ -380,7 +399,9 @@ class RWKV_x070:
     def forward_seq_batch(self, idxs: List[List[int]], state: List[torch.Tensor], full_output: bool = False):
         B, T = len(idxs), len(idxs[0])
         self._check_state(state, B)
-        tok = torch.tensor(idxs, dtype=torch.int32, device=self.device)
+        self._check_ids(idxs)
+        tok = torch.tensor(idxs, dtype=torch.int32)
+        tok = torch.where(tok < 0, tok + self.vocab, tok).to(self.device)
         shape = (B, T, self.vocab) if full_output else (B, self.vocab)
         logits = torch.empty(shape, dtype=DTYPE, device=self.device)
         self._run(B, T, tok, state, logits, full_output)

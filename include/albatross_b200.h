@@ -69,8 +69,10 @@ typedef struct ab_model ab_model;
 /* ---- diagnostics ------------------------------------------------------------------------- */
 const char* ab_last_error(void);
 int ab_version(void);
-/* Reads and clears the device-side status word (non-zero: a bounded device wait gave up).
- * Synchronises the device. Host pointer. */
+/* Reads and clears the device-side status word. Bits: 1, 2, 4 = a bounded device wait gave up in the matrix-vector,
+ * tensor-core or WKV / persistent kernels; 8 = a token id outside [0, vocab) reached a kernel (it was clamped to the
+ * table, never followed). Synchronises the device. Host pointer. After a non-zero wait bit, split-K arrival counters
+ * may be stale: those of ab_gemm_static's built-in area are cleared here, a caller's own scratch / workspace is not. */
 int ab_device_status(uint32_t* status_host);
 
 /* ---- WKV-7 state update -------------------------------------------------------------------
@@ -119,9 +121,18 @@ int ab_gemm(const ab_mat* m, int rows, const void* x, void* y, int epi, const vo
  * a host-side call, not a stream operation) and clears its counters on `stream`: make that first call during
  * set-up, before any stream capture begins. There is ONE array per device: two ab_gemm_static calls that can
  * overlap in time (different streams, or different host threads on different streams) race on it; keep them
- * on one stream or order them with events. */
+ * on one stream or order them with events. The look-up itself is guarded by a lock, so the first calls of two host
+ * threads may coincide.
+ * Recovery: the kernels leave the arrival counters at zero, except when a bounded device wait gave up (a non-zero
+ * ab_device_status) or a launch was aborted half-way. ab_device_status clears the counters of this built-in area
+ * whenever it reports a non-zero status; ab_gemm_static_reset(stream) does the same on request. (The scratch a
+ * caller passes to ab_gemm, and the workspace of ab_forward, are the caller's to clear in that case.) */
 #define AB_GEMM_STATIC_SCRATCH_BYTES (8u * 1024u * 1024u)
 int ab_gemm_static(const ab_mat* m, int rows, const void* x, void* y, int epi, const void* resid, void* stream);
+int ab_gemm_static_reset(void* stream);
+/* Test hook (no counterpart in the reference): reads (write == 0) or overwrites (write != 0) arrival counter `index`
+ * of the built-in area of the current device through the HOST pointer `value_host`; synchronises the device. */
+int ab_gemm_static_debug_counter(int index, int write, uint32_t* value_host);
 
 /* ---- token sampling on the device -----------------------------------------------------------
  * Replaces sampler_simple_batch (reference/utils.py:43-45: uniform noise in [0, noise) added to the logits, then
@@ -171,6 +182,8 @@ int ab_decode_run(ab_model* m, void* program, void* stream);
  *   "debug_sync" (0)      synchronise and check after every launch
  *   "timeline" (0)        persistent kernel records per-phase timestamps (ab_decode_timeline_offset)
  *   "layer_offset" (0)    index of this model's first block in the whole network (pipeline stages)
+ *   "stage_gemv" (0)      ab_forward_stage with B = T = 1 runs the batch-1 matrix-vector kernels (the launches of
+ *                         ab_forward at B = T = 1) instead of the row-wise program
  *   "merge_ups" (0)       persistent kernel: adapter up-projections inside the per-head phase instead of a phase
  *                         of matrix-vector rows of their own (bit-identical to ab_forward at B = T = 1, 3 % slower;
  *                         switches "smem_prefetch" and "barrier_prefetch" off)

@@ -85,6 +85,22 @@ def main():
     out["kv_fp16_none"] = kv
     np.savez_compressed(os.path.join(HERE, "tiny_ref_onepath.npz"), **out)
 
+    # The 0.1B shapes (baseline config 2: L=12, D=768, vocab 65536), int8 big matrices, single-token path, fp32.
+    # The full logits would be 3 MB; the fixture keeps every 61st column, the arg-max, the five largest values and
+    # float64 checksums of each step's logits, and the kv state of the first and last block after the last token.
+    args = synth.make_args("0.1b")
+    toks = tokens_for(args.vocab_size, n=8, seed=0)
+    raw = synth.make_checkpoint("0.1b", seed=0)
+    rq = {k: (torch.from_numpy(qo.fake_quantize(v.numpy(), "int8")) if is_big(k) else v) for k, v in raw.items()}
+    logits, kv, xp = run_reference(ref_mod, rq, args, torch.float, toks)
+    top = np.argsort(-logits, axis=1)[:, :5]
+    np.savez_compressed(os.path.join(HERE, "ref_onepath_0.1b_int8.npz"), tokens=np.array(toks, dtype=np.int64),
+                        logits_strided=logits[:, ::61].astype(np.float32), argmax=logits.argmax(1),
+                        top5_idx=top, top5_val=np.take_along_axis(logits, top, axis=1).astype(np.float32),
+                        logits_sum=logits.astype(np.float64).sum(1), logits_sqsum=(logits.astype(np.float64) ** 2).sum(1),
+                        kv_first=kv[0].astype(np.float32)[::4, ::8, ::8], kv_last=kv[-1].astype(np.float32)[::4, ::8, ::8],
+                        kv_sum=kv.astype(np.float64).sum(axis=(1, 2, 3)), xprev_last=xp[-1].astype(np.float32))
+
     # Config 1 of the baseline: one int8 weight-only GEMV, x fp16 [1,4096] ~N(0,1), W ~N(0,0.02).
     torch.manual_seed(0)
     x = torch.randn(1, 4096).half()

@@ -32,6 +32,26 @@ def test_onepath_matches_reference_fixture(golden, fmt):
     assert np.abs(xp - golden[f"xprev_fp32_{fmt}"]).max() < 1e-5
 
 
+def test_onepath_matches_reference_fixture_at_the_0_1b_shapes():
+    """Baseline config 2's shapes (12 blocks, 768 wide, vocabulary 65536), int8 big matrices, against the fixture
+    tests/golden/make_golden.py wrote by running the unmodified reference module on the CPU."""
+    g = np.load(os.path.join(GOLDEN, "ref_onepath_0.1b_int8.npz"))
+    o, args = oracle_for("0.1b", "int8")
+    st = new_state(args.n_layer, args.n_embd)
+    for i, t in enumerate(g["tokens"].tolist()):
+        l, st = o.step(t, st)
+        l = l.numpy()
+        assert np.abs(l[::61] - g["logits_strided"][i]).max() < 2e-5
+        assert int(l.argmax()) == int(g["argmax"][i])
+        assert np.abs(l[g["top5_idx"][i]] - g["top5_val"][i]).max() < 2e-5
+        assert abs(float(l.astype(np.float64).sum()) - float(g["logits_sum"][i])) < 1e-2
+    kv = np.stack([st[3 * i + 1].numpy() for i in range(args.n_layer)])
+    assert np.abs(kv[0][::4, ::8, ::8] - g["kv_first"]).max() < 1e-5
+    assert np.abs(kv[-1][::4, ::8, ::8] - g["kv_last"]).max() < 1e-5
+    assert np.abs(kv.astype(np.float64).sum(axis=(1, 2, 3)) - g["kv_sum"]).max() < 1e-2
+    assert np.abs(st[3 * (args.n_layer - 1)].numpy() - g["xprev_last"]).max() < 1e-5
+
+
 def test_onepath_fp16_matches_reference_fixture(golden):
     args = synth.make_args("tiny")
     z = prepare(synth.make_checkpoint("tiny", 0), args.n_embd, torch.half)

@@ -64,3 +64,47 @@ def test_static_scratch_rejects_products_beyond_its_size():
     assert rc == AB_ERR_TOO_LARGE
     msg = _lib.lib.ab_last_error().decode()
     assert "ab_gemm_static" in msg and "scratch" in msg and "ab_gemm" in msg
+
+
+def test_static_scratch_counters_are_cleared_after_a_reported_device_wait():
+    """A stale arrival counter (what a wait that gave up, or an aborted launch, leaves behind) would make every later
+    split-K product through the built-in area wrong. No device fault is needed to show the recovery: the test
+    overwrites a counter word from the host, runs the documented reset and checks the next product."""
+    _lib, pm, cm, xs = _setup("int8", 1024, 4096, 64, seed=5)       # split-K: the counters are in use
+    st = torch.cuda.current_stream().cuda_stream
+    want, _ = _reference(_lib, cm, 64, xs[0], EPI_NONE, None)
+    got = torch.empty_like(want)
+    run = lambda: _lib.check(_lib.lib.ab_gemm_static(C.byref(cm), 64, xs[0].data_ptr(), got.data_ptr(), EPI_NONE, None, st))
+    run()
+    torch.cuda.synchronize()
+    assert torch.equal(got, want)
+    v = C.c_uint32(0)
+    _lib.check(_lib.lib.ab_gemm_static_debug_counter(0, 0, C.byref(v)))
+    assert v.value == 0                                              # the kernels leave the counters at zero
+    # a stale count on a tile this product uses; nothing is launched while it sits there
+    v = C.c_uint32(1)
+    _lib.check(_lib.lib.ab_gemm_static_debug_counter(0, 1, C.byref(v)))
+    _lib.check(_lib.lib.ab_gemm_static_reset(st))
+    v = C.c_uint32(99)
+    _lib.check(_lib.lib.ab_gemm_static_debug_counter(0, 0, C.byref(v)))
+    assert v.value == 0
+    run()
+    torch.cuda.synchronize()
+    assert torch.equal(got, want) and _lib.device_status() == 0
+    # the same through ab_device_status: any non-zero status clears the counters. The harmless way to raise one is a
+    # token id beyond the vocabulary handed straight to the kernels (it is clamped to the table and reported).
+    from albatross_b200 import RWKV_x070, synth
+    args = synth.make_args("tiny")
+    model = RWKV_x070(args, quant="int8", state_dict=synth.make_checkpoint("tiny", seed=0), decode_mode="eager", use_graph=False)
+    v = C.c_uint32(1)
+    _lib.check(_lib.lib.ab_gemm_static_debug_counter(0, 1, C.byref(v)))
+    tok = torch.tensor([args.vocab_size + 5], dtype=torch.int32, device="cuda")
+    logits = torch.empty(args.vocab_size, dtype=torch.float16, device="cuda")
+    model._run(1, 1, tok, model.new_state(), logits, False)
+    assert _lib.device_status() == 8 and torch.isfinite(logits.float()).all()
+    v = C.c_uint32(99)
+    _lib.check(_lib.lib.ab_gemm_static_debug_counter(0, 0, C.byref(v)))
+    assert v.value == 0
+    run()
+    torch.cuda.synchronize()
+    assert torch.equal(got, want) and _lib.device_status() == 0
