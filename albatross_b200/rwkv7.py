@@ -81,7 +81,7 @@ def sampler_simple_batch(logits: torch.Tensor, noise: float = 1.0, seed: int = 0
 class RWKV_x070:
     def __init__(self, args, quant: Optional[str] = "int8", state_dict: Optional[Iterable[Tuple[str, torch.Tensor]]] = None,
                  device: str = "cuda", use_graph: bool = True, decode_mode: Optional[str] = None,
-                 layer_range: Optional[Tuple[int, int]] = None):
+                 layer_range: Optional[Tuple[int, int]] = None, pack_cache=None):
         if not torch.cuda.is_available():
             raise RuntimeError("albatross_b200 needs a CUDA device (sm_100a); there is no CPU path")
         self.args = args
@@ -102,7 +102,20 @@ class RWKV_x070:
         assert self.decode_mode in ("persistent", "graph", "eager")
 
         items = state_dict
+        # pack_cache: path of the file that keeps the quantised matrices between runs (packcache.py). Loading from
+        # a `.pth` file uses `<MODEL_NAME>.<format>.abpack` next to it unless pack_cache=False (or the environment
+        # says ALBATROSS_PACK_CACHE=0); with an in-memory state dict a path must be given explicitly.
+        if pack_cache is None:
+            pack_cache = items is None and quant is not None and os.environ.get("ALBATROSS_PACK_CACHE", "1") != "0"
+        if pack_cache is True:
+            pack_cache = "%s.%s.abpack" % (args.MODEL_NAME, quant or "fp16") if items is None else None
+        self._cache = None
+        if pack_cache:
+            from .packcache import PackCache
+            self._cache = PackCache(str(pack_cache), quant, mode=os.environ.get("ALBATROSS_PACK_CACHE_MODE", "sample"))
         if items is None:
+            # memory-mapped: a tensor's pages are read when it is used, so the checkpoint streams through block by
+            # block and matrices served by the pack cache are never read beyond their fingerprint samples
             items = torch.load(args.MODEL_NAME + ".pth", map_location="cpu", mmap=True).items()
         elif isinstance(items, dict):
             items = items.items()
@@ -125,6 +138,13 @@ class RWKV_x070:
             elif not self.is_last:      # ln_out.*, head.weight
                 continue
             self._ingest(name, t)
+        if self._cache is not None:
+            self.pack_cache_stats = (self._cache.hits, self._cache.misses)
+            try:
+                self._cache.close()
+            except OSError:      # read-only model directory: run without writing the cache
+                pass
+            self._cache = None
         z = self.z
         self.n_head, self.head_size = self._r_k_shape
         assert HEAD_SIZE == self.head_size
@@ -152,6 +172,13 @@ class RWKV_x070:
         dev = self.device
         if _is_big(name):
             # storage is [out, in] row-major; the reference views it as [in, out]. Quantise per output row.
+            if self._cache is not None:
+                pm = self._cache.get(name, t, dev)
+                if pm is None:
+                    pm = quantize(t.to(dev, non_blocking=True), self.quant)
+                    self._cache.put(name, t, pm)
+                self.z[name] = pm
+                return
             w = t.to(dev, non_blocking=True)
             self.z[name] = quantize(w, self.quant)
             return

@@ -29,9 +29,15 @@ from oracle.rwkv7_oracle import Oracle, is_big
 
 pytestmark = pytest.mark.gpu
 
-BLOCK_REL_TOL = 1e-2     # max |ours - oracle| / max |oracle| of a block's output, teacher-forced (measured: see DESIGN.md)
-STATE_REL_TOL = 1e-2     # the same for the new kv state
+# Tolerances, all as max |ours - oracle| / max |oracle| over the tensor:
+BLOCK_REL_TOL = 2e-2     # a block's output and its token-shift states, worst of the 320 sequences (the stated tolerance)
+BLOCK_MEDIAN_TOL = 3e-3  # ... and the median sequence
+STATE_REL_TOL = 5e-3     # the new kv state
 LOGIT_REL_TOL = 2e-2     # the stated tolerance on fp16 logits
+# Why the worst sequence is ten times the median: where a head's read-out y = S r nearly cancels (first steps from a zero
+# state: y = v (k . r) with k . r close to 0), the group norm (eps 64e-5, reference/rwkv7.py:248, :298) turns the fp16
+# rounding of r and k into a large relative change of that head's 64 outputs. The fp16 reference has the same
+# sensitivity against an fp32 evaluation; it is a property of the input, identical in the batch-1 and batched kernels.
 B, STEPS = 320, 2
 CFG = "7.2b"
 
@@ -82,7 +88,7 @@ def test_every_block_of_the_7_2b_shapes_matches_the_oracle(fmt):
     vf_or = [torch.zeros(B, 1, D, device=dev) for _ in range(STEPS)]
     vf_free = [torch.zeros(B, D, dtype=torch.float16, device=dev) for _ in range(STEPS)]
     report = {"fmt": fmt, "blocks": []}
-    worst = {"x": 0.0, "kv": 0.0, "shift": 0.0, "x_gemv": 0.0, "kv_gemv": 0.0}
+    worst = {"x": 0.0, "x_median_row": 0.0, "kv": 0.0, "shift": 0.0, "x_gemv": 0.0, "kv_gemv": 0.0}
     logits_err = {}
 
     for i in range(L):
@@ -124,7 +130,8 @@ def test_every_block_of_the_7_2b_shapes_matches_the_oracle(fmt):
                               "argmax_agree_teacher_forced": float((logits.argmax(-1) == ref.argmax(-1)).float().mean()),
                               "argmax_agree_free_running": float((logits_f.argmax(-1) == ref.argmax(-1)).float().mean())}
             else:
-                e = {"x": _rel(out, want[:, 0]), "kv": _rel(st_tf[1], st_or[1]),
+                row_err = (out.float() - want[:, 0]).abs().amax(1) / want.abs().max()
+                e = {"x": _rel(out, want[:, 0]), "x_median_row": float(row_err.median()), "kv": _rel(st_tf[1], st_or[1]),
                      "shift": max(_rel(st_tf[0], st_or[0]), _rel(st_tf[2], st_or[2])),
                      "x_gemv": _rel(out1[0], want1), "kv_gemv": _rel(st_gv[1][0], st_one[1]),
                      "x_free": _rel(outf, want[:, 0])}
@@ -148,6 +155,7 @@ def test_every_block_of_the_7_2b_shapes_matches_the_oracle(fmt):
     print(fmt, "worst teacher-forced:", worst, "logits:", logits_err, "free-running by depth:",
           report["free_running_x_error_by_depth"])
     assert worst["x"] <= BLOCK_REL_TOL and worst["x_gemv"] <= BLOCK_REL_TOL, worst
+    assert worst["x_median_row"] <= BLOCK_MEDIAN_TOL, worst
     assert worst["kv"] <= STATE_REL_TOL and worst["kv_gemv"] <= STATE_REL_TOL, worst
     assert worst["shift"] <= BLOCK_REL_TOL, worst
     assert logits_err["teacher_forced"] <= LOGIT_REL_TOL and logits_err["batch1_kernels"] <= LOGIT_REL_TOL, logits_err
