@@ -2,7 +2,8 @@
 
     python -m albatross_b200.build [--force] [--verbose]
 
-Output: albatross_b200/_C/libalbatross_b200.so (git-ignored; it ships with the source tree).
+Output: albatross_b200/_C/libalbatross_b200.so (git-ignored; it ships with the source tree) and, next to it,
+librwkv7_state_fwd_fp16.so: the torch operator shim (g++, csrc/torch_op.cpp).
 """
 from __future__ import annotations
 
@@ -50,6 +51,31 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+TORCH_OP_LIB = os.path.join(OUT_DIR, "librwkv7_state_fwd_fp16.so")
+
+
+def build_torch_op(force: bool = False) -> str:
+    """Builds the operator shim csrc/torch_op.cpp (plain C++, g++): `torch.ops.rwkv7_state_fwd_fp16.forward` backed by
+    ab_wkv7_fwd. Links against the kernel library next to it (found at run time through $ORIGIN)."""
+    src = os.path.join(CSRC, "torch_op.cpp")
+    if not force and os.path.exists(TORCH_OP_LIB) and os.path.getmtime(TORCH_OP_LIB) >= max(os.path.getmtime(src), os.path.getmtime(LIB)):
+        return TORCH_OP_LIB
+    import torch
+    from torch.utils import cpp_extension as ce
+    cmd = [os.environ.get("CXX", "g++"), "-O2", "-std=c++17", "-fPIC", "-shared", src, "-o", TORCH_OP_LIB,
+           "-D_GLIBCXX_USE_CXX11_ABI=%d" % int(torch._C._GLIBCXX_USE_CXX11_ABI)]
+    cmd += ["-I" + p for p in ce.include_paths("cuda")] + ["-I/usr/local/cuda/include"]
+    cmd += ["-L" + p for p in ce.library_paths("cuda")] + ["-L" + OUT_DIR]
+    cmd += ["-lalbatross_b200", "-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch", "-Wl,-rpath,$ORIGIN"]
+    cmd += ["-Wl,-rpath," + p for p in ce.library_paths("cuda")]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    with open(os.path.join(OUT_DIR, "build_torch_op.log"), "w") as f:
+        f.write(" ".join(cmd) + "\n" + res.stdout + res.stderr)
+    if res.returncode != 0:
+        raise RuntimeError("building the torch operator shim failed; see " + os.path.join(OUT_DIR, "build_torch_op.log"))
+    return TORCH_OP_LIB
+
+
 def resource_usage(log_path: str = os.path.join(OUT_DIR, "build.log")) -> dict:
     """Per kernel: registers and spill bytes as ptxas reported them in the last build (kernel name -> dict).
 
@@ -74,3 +100,4 @@ def resource_usage(log_path: str = os.path.join(OUT_DIR, "build.log")) -> dict:
 
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build_torch_op(force="--force" in sys.argv))

@@ -93,6 +93,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) decode_kernel(const DecodePro
     }
     __syncthreads();
 
+    const uint32_t epoch = prog->epoch;   // tag base of this token (dataflow mode)
     bool failed = false;
     int pre_phase = -1;
     unsigned n_barriers = 0;
@@ -124,24 +125,56 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) decode_kernel(const DecodePro
             const bool pre = j >= 0 && prog->smem_prefetch;
             gemv_consume(ph.g, plans[i & 3], m, tid, bid, i, pre_phase, pre ? &phs[j & 3].g : nullptr,
                          pre ? &plans[j & 3] : nullptr, j,
-                         (prog->timeline && bid == 0) ? prog->timeline + 2 * n_phases + 4 * i : nullptr, prog->early_slice != 0);
+                         (prog->timeline && bid == 0) ? prog->timeline + 2 * n_phases + 4 * i : nullptr, prog->early_slice != 0,
+                         [&]() {
+                             if (ph.no_barrier == 2 && tid < HT && bid < 2 * phs[(i + 1) & 3].h.H && (bid & 1) == 0) {
+                                 // "fused heads": this block runs head bid / 2 right after the phase. Its slices of the
+                                 // four adapter up-projection matrices (weights: no dependency) move into the idle
+                                 // prefetch area while the phase's own weights stream; requested any earlier they would
+                                 // sit in front of the loads of the phase's input vector. The head's per-channel
+                                 // parameters and its state (last touched a token ago) are pulled towards the SM as well.
+                                 const HeadParams& nh = phs[(i + 1) & 3].h;
+                                 const int h = bid >> 1;
+                                 head_ups_stage(nh, h, tid, m.pref);
+                                 asm volatile("cp.async.commit_group;" ::: "memory");
+                                 if (tid < 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(nh.state + (size_t)h * 4096 + tid * 32));
+                                 if (tid < 8) {
+                                     const __half* v[8] = {nh.w0, nh.a0, nh.v0, nh.k_k, nh.k_a, nh.r_k, nh.lnx_w, nh.lnx_b};
+                                     const __half* q = v[0];
+#pragma unroll
+                                     for (int e = 1; e < 8; ++e)
+                                         if (tid == e) q = v[e];
+                                     if (q) asm volatile("prefetch.global.L1 [%0];" ::"l"(q + h * 64));
+                                 }
+                             }
+                         }, epoch);
         } else {
             const HeadParams& hp = ph.h;
             // adapter up-projections inside the phase: block h needs only the 64 channels of head h, so the
             // matrix-vector phase (and the grid barrier) that would produce them for everybody is not needed
             const bool ups = hp.w2 != nullptr;
-            for (int h = bid; h < hp.H; h += nb) {   // block-uniform
+            // Dataflow mode (pair_mode): no barrier among all blocks came before this phase. Block 2h runs head h; its
+            // inputs (the head's r / k / v rows, the adapter hidden vectors) are tagged words and the loads wait for
+            // them one by one. Everybody else goes straight on to the next phase.
+            const bool pair = hp.pair_mode != 0;
+            const bool mine = !pair || (bid < 2 * hp.H && (bid & 1) == 0);
+            for (int h = pair ? (bid >> 1) : bid; mine && h < hp.H; h += pair ? hp.H : nb) {   // block-uniform
                 if (tid < HT) {
-                    if (ups) head_ups_stage(hp, h, tid, smem);   // the matrix-vector buffers are idle in this phase
+                    unsigned char* dsm = pair ? m.pref : smem;   // pair mode: staged during the phase before
+                    if (ups && !pair) head_ups_stage(hp, h, tid, dsm);   // the matrix-vector buffers are idle in this phase
                     float* sbase = hp.state + (size_t)h * 4096;
                     StateRow st;
-                    load_state(st, sbase, tid >> 2, tid & 3);
-                    if (ups) head_ups_compute(hp, tid, smem, hsh, SyncNamed256());
-                    head_steps(hp, 0, h, tid, st, hsh, ups, SyncNamed256());
+                    load_state(st, sbase, tid >> 2, tid & 3);   // last written a token ago: in flight while the inputs arrive
+                    const HeadTags tg = {hp.tag_in != 0, tag_of(epoch, hp.tag_in), tag_of(epoch, hp.tag_out)};
+                    if (ups) head_ups_compute(hp, tid, dsm, hsh, SyncNamed256(), tg);
+                    head_steps(hp, 0, h, tid, st, hsh, ups, SyncNamed256(), tg);
                     store_state(st, sbase, tid >> 2, tid & 3);
-                    if (hp.copy_src && tid < 32)
+                    // token-shift state hand-over. Pair mode: the normalised input of the phase before is still in this
+                    // block's shared memory (every block prepared it), so no other block's global write is read here.
+                    if (hp.copy_dst && tid < 32)
                         reinterpret_cast<__half2*>(hp.copy_dst + h * 64)[tid] =
-                            __ldcg(reinterpret_cast<const __half2*>(hp.copy_src + h * 64) + tid);
+                            pair ? reinterpret_cast<const __half2*>(m.xn + h * 64)[tid]
+                                 : __ldcg(reinterpret_cast<const __half2*>(hp.copy_src + h * 64) + tid);
                     SyncNamed256()();
                 }
             }
@@ -149,7 +182,9 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) decode_kernel(const DecodePro
         if (prog->timeline && bid == 0 && tid == 0) prog->timeline[2 * i + 1] = global_ns();
         if (i + 1 < n_phases) {
             if (ph.no_barrier) {
-                cons_sync();   // same block produces and consumes: a block barrier orders the global writes
+                // a block barrier only: either the same block produces and consumes, or (dataflow mode) the phase's
+                // outputs are tagged words that their readers wait for; the block's shared memory is free for the next phase
+                cons_sync();
             } else {
                 const int j = ph.type == PHASE_GEMV ? ph.next_gemv : -1;
                 grid_barrier(prog->barrier, (unsigned)(++n_barriers) * nb, tid, failed, [&]() {
@@ -166,6 +201,8 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) decode_kernel(const DecodePro
             }
         }
     }
+    // Every block has read the tag base by now (block 0 could not have finished the last phase otherwise).
+    if (bid == 0 && tid == 0) const_cast<DecodeProgram*>(prog)->epoch = epoch + (uint32_t)n_phases;
 }
 
 }  // namespace

@@ -10,7 +10,9 @@ enum PhaseType : int { PHASE_GEMV = 0, PHASE_HEAD = 1 };
 struct __align__(16) DecodePhase {
     int type;
     int next_gemv;   // index of the next matrix-vector phase after this one, or -1
-    int no_barrier;  // the next phase only consumes what this block itself produced: no grid barrier in between
+    int no_barrier;  // what follows the phase: 0 = barrier among all blocks; 1 or 2 = a block barrier only (1: the next
+                     // phase consumes what this block itself produced; 2: dataflow mode, the phase's outputs are
+                     // tagged words and their readers wait on the words themselves)
     int rows_per_block;  // > 0: block b owns rows [b * rows_per_block, +rows_per_block) of every segment
     GemvParams g;
     HeadParams h;
@@ -29,7 +31,11 @@ struct DecodeProgram {
     const BlockPlan* plans;  // [n_phases][n_blocks], computed on the host (device copy follows the phases)
     unsigned* barrier;       // points at barrier_word of the device copy
     unsigned long long* timeline;  // optional: block 0 stores %globaltimer at [2i] phase start, [2i+1] phase end
-    unsigned barrier_word, pad[3];
+    unsigned barrier_word;
+    unsigned epoch;          // dataflow mode: tag base of the next token (tags are epoch + phase index + 1, 16 bits); the
+                             // kernel advances it by n_phases when a token is done, so no two writes of a word that
+                             // follow one another carry the same tag
+    unsigned pad[2];
     DecodePhase phases[1];   // n_phases entries
 };
 

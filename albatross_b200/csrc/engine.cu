@@ -64,6 +64,10 @@ struct ab_model {
     int early_slice = 0;   // measured slower: any weight traffic in flight delays the loads of the input vector
     int barrier_prefetch = 0;   // measured slower: the polls of the barrier queue behind the prefetch traffic
     int stage_gemv = 0;  // ab_forward_stage at B = T = 1 runs the batch-1 matrix-vector kernels instead of the row-wise program
+    int fuse_heads = 1;  // persistent decode kernel: r/k/v rows of head h on blocks 2h, 2h+1, the adapter down-projections on
+                         // the remaining blocks; block 2h runs the head (up-projections from pre-staged weights, WKV step)
+                         // as soon as those producers have signalled: two barriers among all blocks fewer per network block
+    int pair_split = 6;  // ... row groups (of 4 rows) of a head's 16 that go to block 2h (which also stages the up-projections)
     int merge_ups = 0;   // persistent decode kernel: block h computes the adapter up-projections of head h inside the head
                          // phase: one phase and barrier fewer per block and the same arithmetic as the per-phase
                          // launches (identical logits), but 3 % slower per token than the phase of matrix-vector rows
@@ -96,10 +100,13 @@ Workspace carve(const ab_model* m, int B, int T, unsigned char* base) {
     Workspace w;
     size_t off = 0;
     auto take = [&](size_t elems) { __half* p = (__half*)(base + off); off += al(elems * 2); return p; };
-    w.x = take(M * D); w.xn = take(M * D); w.xn2 = take(M * D);
-    w.r = take(M * D); w.k = take(M * D); w.v = take(M * D); w.vfirst = take(M * D); w.att = take(M * D);
-    w.kf = take(M * F);
-    w.hw = take(M * rmax[0]); w.ha = take(M * rmax[1]); w.hv = take(M * rmax[2]); w.hg = take(M * rmax[3]);
+    // At B = T = 1 the vectors that cross blocks of the persistent kernel may be arrays of tagged 32-bit words
+    // (dataflow mode) instead of fp16: twice the room.
+    const size_t tw = M == 1 ? 2 : 1;
+    w.x = take(tw * M * D); w.xn = take(M * D); w.xn2 = take(M * D);
+    w.r = take(tw * M * D); w.k = take(tw * M * D); w.v = take(tw * M * D); w.vfirst = take(M * D); w.att = take(tw * M * D);
+    w.kf = take(tw * M * F);
+    w.hw = take(tw * M * rmax[0]); w.ha = take(tw * M * rmax[1]); w.hv = take(tw * M * rmax[2]); w.hg = take(tw * M * rmax[3]);
     const bool batched = !(B == 1 && T == 1) || !m->d.emb || !m->d.head.w || m->layer_offset > 0;
     for (int j = 0; j < 6; ++j) w.mix[j] = batched ? take(M * D) : nullptr;
     w.w_raw = take(M * D); w.a_raw = take(M * D); w.vg_raw = take(M * D); w.g = take(M * D);
@@ -245,13 +252,17 @@ int build_decode_program(ab_model* m, const int32_t* token, void* const* state, 
     prog->first_gemv = 0;
     prog->l2_prefetch_bytes = m->l2_prefetch_kb * 1024;
     // the in-phase adapter up-projection stages its matrices where the prefetched slices would wait: one or the other
-    prog->smem_prefetch = m->merge_ups ? 0 : m->smem_prefetch;
-    prog->early_slice = m->early_slice;
-    prog->barrier_prefetch = m->merge_ups ? 0 : m->barrier_prefetch;
+    const bool stage_area_taken = m->merge_ups || m->fuse_heads;
+    prog->smem_prefetch = stage_area_taken ? 0 : m->smem_prefetch;
+    prog->early_slice = stage_area_taken ? 0 : m->early_slice;
+    prog->barrier_prefetch = stage_area_taken ? 0 : m->barrier_prefetch;
     prog->barrier = const_cast<unsigned*>(&dev_addr->barrier_word);
+    prog->epoch = 1;   // tags start above zero: freshly cleared words (tag 0) are "not written yet"
     prog->timeline = m->timeline ? (unsigned long long*)((unsigned char*)dev_addr +
                                                           decode_timeline_offset(n_phases, m->n_sm)) : nullptr;
     int n = 0;
+    // dataflow mode: 1 + index of the phase that wrote the hidden state `ws.x` last (0: plain fp16, barrier mode)
+    int x_tag = 0;
     auto gemv_phase = [&](const GemvParams& g) -> int {
         DecodePhase& ph = prog->phases[n++];
         ph.type = PHASE_GEMV;
@@ -284,7 +295,23 @@ int build_decode_program(ab_model* m, const int32_t* token, void* const* state, 
             AB_TRY(gemv_phase(p));
         }
         const int rtot = Ly.w1t.n_out + Ly.a1t.n_out + (i == 0 ? 0 : Ly.v1t.n_out) + Ly.g1t.n_out;
-        const bool ups_in_head = m->merge_ups && H <= m->n_sm && head_ups_smem(rtot) <= gemv_layout(D, 1, 0).total;
+        // dataflow mode ("fuse_heads") needs two blocks per head plus at least four for the adapter rows, whole heads of 16 row groups
+        // in the three matrices, and the head's up-projection slices in the idle prefetch area
+        const bool fused = m->fuse_heads && !m->merge_ups && 2 * H + 4 <= m->n_sm &&
+                           Ly.receptance.n_out == D && Ly.key.n_out == D && Ly.value.n_out == D &&
+                           head_ups_smem(rtot) <= (size_t)GEMV_WARPS * GEMV_ROWS * GEMV_SLICE_BYTES &&
+                           m->pair_split >= 1 && m->pair_split <= HEAD / GEMV_ROWS - 1;
+        AB_CHECK_ARG(i == 0 || fused == (x_tag != 0), "decode program: the blocks of the network must all take the same mode");
+        if (fused) {
+            DecodePhase& p1 = prog->phases[n - 1];
+            p1.no_barrier = 2;         // dataflow: tagged outputs, no barrier among all blocks
+            p1.rows_per_block = -1;    // marks the head-aligned plan
+            // layer 0 reads the embedding row (weights) and block 0 publishes it as the tagged hidden state
+            p1.g.tag_in = i == 0 ? n : x_tag;
+            if (i == 0) x_tag = n;
+            for (int s = 0; s < p1.g.nseg; ++s) p1.g.seg[s].tag_out = n;
+        }
+        const bool ups_in_head = fused || (m->merge_ups && H <= m->n_sm && head_ups_smem(rtot) <= gemv_layout(D, 1, 0).total);
         if (!ups_in_head) {   // adapter up-projections: rows of [n_embd, rank], each with its own short input
             GemvParams p = {};
             int k = 0;
@@ -311,6 +338,10 @@ int build_decode_program(ab_model* m, const int32_t* token, void* const* state, 
             h.k_k = (const __half*)Ly.k_k; h.k_a = (const __half*)Ly.k_a; h.r_k = (const __half*)Ly.r_k;
             h.lnx_w = (const __half*)Ly.lnx_w; h.lnx_b = (const __half*)Ly.lnx_b;
             h.out = ws.att; h.copy_src = ws.xn; h.copy_dst = att_prev;
+            if (fused) {
+                h.pair_mode = 1; h.tag_in = n - 1; h.tag_out = n;   // n - 1: the phase before (1-based), n: this one
+                ph.no_barrier = 2;
+            }
             if (ups_in_head) {   // block h computes the adapter outputs of head h itself (no phase, no barrier for them)
                 h.hw = ws.hw; h.ha = ws.ha; h.hv = ws.hv; h.hg = ws.hg;
                 h.w2 = (const __half*)Ly.w2; h.a2 = (const __half*)Ly.a2; h.v2 = (const __half*)Ly.v2; h.g2 = (const __half*)Ly.g2;
@@ -321,14 +352,18 @@ int build_decode_program(ab_model* m, const int32_t* token, void* const* state, 
             GemvParams p = {};
             p.K = D; p.x = ws.att; p.nseg = 1;
             p.seg[0] = seg_of(Ly.output, nullptr, EPI_RESID, ws.x, ws.x);
+            if (fused) { p.tag_in = n; p.seg[0].tag_resid = x_tag; p.seg[0].tag_out = n + 1; }   // n: the head phase before
             AB_TRY(gemv_phase(p));
+            if (fused) { prog->phases[n - 1].no_barrier = 2; x_tag = n; }
         }
         {
             GemvParams p = {};
             p.K = D; p.x = ws.x; p.nseg = 1;
             p.x_prev = ffn_prev; p.ln_w = (const __half*)Ly.ln2_w; p.ln_b = (const __half*)Ly.ln2_b; p.ln_out = ws.xn2;
             p.seg[0] = seg_of(Ly.ffn_key, Ly.ffn_x_k, EPI_RELU2, ws.kf);
+            if (fused) { p.tag_in = x_tag; p.seg[0].tag_out = n + 1; }
             AB_TRY(gemv_phase(p));
+            if (fused) prog->phases[n - 1].no_barrier = 2;
         }
         {
             GemvParams p = {};
@@ -336,13 +371,16 @@ int build_decode_program(ab_model* m, const int32_t* token, void* const* state, 
             p.seg[0] = seg_of(Ly.ffn_value, nullptr, EPI_RESID, ws.x, ws.x);
             p.seg[0].x = ws.kf;   // 4*n_embd inputs: read straight from global memory
             p.copy_src = ws.xn2; p.copy_dst = ffn_prev; p.copy_n = D;
+            if (fused) { p.seg[0].tag_x = n; p.seg[0].tag_resid = x_tag; p.seg[0].tag_out = n + 1; }   // n: the ffn-key phase before
             AB_TRY(gemv_phase(p));
+            if (fused) { prog->phases[n - 1].no_barrier = 2; x_tag = n; }
         }
     }
     GemvParams p = {};
     p.K = D; p.x = ws.x; p.nseg = 1;
     p.ln_w = (const __half*)m->d.lnout_w; p.ln_b = (const __half*)m->d.lnout_b;
     p.seg[0] = seg_of(m->d.head, nullptr, EPI_NONE, logits);
+    p.tag_in = x_tag;
     AB_TRY(gemv_phase(p));
     prog->n_phases = n;   // one phase fewer per block when the adapter up-projections run inside the head phase
     int nxt = -1;
@@ -358,6 +396,7 @@ int build_decode_program(ab_model* m, const int32_t* token, void* const* state, 
             for (int b = 0; b < m->n_sm; ++b) {
                 BlockPlan& bp = host_plans[(size_t)i * m->n_sm + b];
                 if (prog->phases[i].rows_per_block > 0) compute_plan_rows(prog->phases[i].g, b, prog->phases[i].rows_per_block, bp);
+                else if (prog->phases[i].rows_per_block < 0) compute_plan_heads(prog->phases[i].g, b, m->n_sm, H, m->pair_split, bp);
                 else compute_plan(prog->phases[i].g, b, m->n_sm, bp);
             }
     return OK;
@@ -569,6 +608,9 @@ int ab_decode_program_build(ab_model* m, const int32_t* token, void* const* stat
     const Workspace ws = carve(m, 1, 1, (unsigned char*)workspace);
     std::vector<unsigned char> buf;
     AB_TRY(build_decode_program(m, token, state, ws, (__half*)logits, buf, (const DecodeProgram*)program));
+    // dataflow mode reads "not written yet" from a zero tag: whatever an earlier program or another decode mode left in
+    // the workspace must not look like a tagged word
+    AB_CUDA(cudaMemsetAsync(workspace, 0, ws.total, (cudaStream_t)stream));
     AB_CUDA(cudaMemcpyAsync(program, buf.data(), buf.size(), cudaMemcpyHostToDevice, (cudaStream_t)stream));
     AB_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
     return OK;
@@ -589,6 +631,8 @@ int ab_model_set_option(ab_model* m, const char* name, int value) {
     else if (!strcmp(name, "l2_prefetch_kb")) m->l2_prefetch_kb = value < 0 ? 0 : value;
     else if (!strcmp(name, "smem_prefetch")) m->smem_prefetch = value != 0;
     else if (!strcmp(name, "merge_ups")) m->merge_ups = value != 0;
+    else if (!strcmp(name, "fuse_heads")) m->fuse_heads = value != 0;
+    else if (!strcmp(name, "pair_split")) m->pair_split = value;
     else if (!strcmp(name, "stage_gemv")) m->stage_gemv = value != 0;
     else if (!strcmp(name, "early_slice")) m->early_slice = value != 0;
     else if (!strcmp(name, "barrier_prefetch")) m->barrier_prefetch = value != 0;

@@ -28,6 +28,11 @@ struct GemvSeg {
     float tscale;            // NVFP4 per-tensor scale, 1 otherwise
     int fmt, epi, n_rows;
     int K;                   // input length of this matrix (== GemvParams::K when x is null)
+    // Persistent kernel, dataflow mode: a vector that crosses blocks is an array of 32-bit words, fp16 value in the low
+    // half and a 16-bit tag of the phase that wrote it in the high half, so that its readers can tell a word that has
+    // arrived from one that has not without any barrier. 0 = plain fp16 array; else 1 + index of the writing phase.
+    int tag_x, tag_resid, tag_out;
+    int pad_;
 };
 
 struct __align__(16) GemvParams {
@@ -36,6 +41,7 @@ struct __align__(16) GemvParams {
     const __half* x;        // shared input vector [K] (ignored when emb != null)
     const __half* emb;      // optional embedding table [V,K]: x = emb[token[0]]
     const int* token;
+    int tag_in;             // shared input `x` (and `x_copy`): 0 = plain fp16, else 1 + index of the phase that wrote it
     int emb_rows;           // rows of the embedding table: a token id outside [0, emb_rows) is clamped and reported
     const __half* x_prev;   // token-shift state [K] (needed when any seg has mix)
     const __half* ln_w;     // layer-norm weight/bias [K], or null: no normalisation

@@ -33,6 +33,71 @@ __device__ __forceinline__ float ld_early_act_f16(const __half* p) {
     asm volatile("ld.global.cg.u16 %0, [%1];" : "=h"(v) : "l"(p));
     return __half2float(__ushort_as_half(v));
 }
+// ---- tagged words (dataflow mode of the persistent kernel) -------------------------------------------------------
+// word = fp16 bits | tag << 16. A reader spins until the tag is the one it expects: the load itself is the
+// synchronisation (no barrier, no fence: every 32-bit word is written and read atomically and validates itself).
+constexpr uint32_t TAG_SPIN_LIMIT = 1u << 21;
+__device__ __forceinline__ uint32_t tag_of(uint32_t epoch, int stored) { return (epoch + (uint32_t)stored) & 0xffffu; }
+__device__ __forceinline__ uint4 ld_relaxed_v4(const uint32_t* p) {
+    uint4 v;
+    asm volatile("ld.relaxed.gpu.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint32_t ld_relaxed_u32(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_relaxed_u32(uint32_t* p, uint32_t v) {
+    asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void st_tagged(void* base, int idx, float v, uint32_t tag) {
+    st_relaxed_u32(reinterpret_cast<uint32_t*>(base) + idx, (uint32_t)__half_as_ushort(__float2half_rn(v)) | (tag << 16));
+}
+// One tagged value; gives up (status bit, returns what is there) after a bounded number of tries.
+__device__ __forceinline__ float ld_tagged1(const void* base, int idx, uint32_t tag) {
+    const uint32_t* p = reinterpret_cast<const uint32_t*>(base) + idx;
+    uint32_t w = ld_relaxed_u32(p), it = 0;
+    while ((w >> 16) != tag) {
+        if (++it > TAG_SPIN_LIMIT) {
+            atomicOr(&g_device_status, DEV_WAIT_GEMV);
+            break;
+        }
+        __nanosleep(it < 4 ? 100u : 400u);   // waiting blocks must not flood the L2 that the producers still need
+        w = ld_relaxed_u32(p);
+    }
+    return __half2float(__ushort_as_half((unsigned short)(w & 0xffffu)));
+}
+// Eight consecutive tagged values (32-byte aligned) -> eight fp16 packed as a uint4.
+__device__ __forceinline__ uint4 ld_tagged8(const void* base, int idx8, uint32_t tag) {
+    const uint32_t* p = reinterpret_cast<const uint32_t*>(base) + 8 * (size_t)idx8;
+    const uint32_t t = tag << 16;
+    uint4 a, b;
+    uint32_t it = 0;
+    while (true) {
+        a = ld_relaxed_v4(p);
+        b = ld_relaxed_v4(p + 4);
+        const uint32_t bad = ((a.x ^ t) | (a.y ^ t) | (a.z ^ t) | (a.w ^ t) | (b.x ^ t) | (b.y ^ t) | (b.z ^ t) | (b.w ^ t)) >> 16;
+        if (!bad) break;
+        if (++it > TAG_SPIN_LIMIT) {
+            atomicOr(&g_device_status, DEV_WAIT_GEMV);
+            break;
+        }
+        __nanosleep(it < 4 ? 100u : 400u);   // waiting blocks must not flood the L2 that the producers still need
+    }
+    return make_uint4(__byte_perm(a.x, a.y, 0x5410), __byte_perm(a.z, a.w, 0x5410), __byte_perm(b.x, b.y, 0x5410),
+                      __byte_perm(b.z, b.w, 0x5410));
+}
+__device__ __forceinline__ void st_tagged8(void* base, int idx8, uint4 v, uint32_t tag) {
+    uint32_t* p = reinterpret_cast<uint32_t*>(base) + 8 * (size_t)idx8;
+    const uint32_t t = tag << 16, w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        st_relaxed_u32(p + 2 * e, (w[e] & 0xffffu) | t);
+        st_relaxed_u32(p + 2 * e + 1, (w[e] >> 16) | t);
+    }
+}
+
 // Start pulling a run of weights into L2 (no registers, no shared memory, nobody waits).
 __device__ __forceinline__ void prefetch_l2(const void* p, uint32_t bytes) {
     asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
@@ -175,6 +240,63 @@ __host__ __device__ inline void compute_plan_rows(const GemvParams& p, int bid, 
         rows += q.n_groups * GEMV_ROWS;
         part += q.n_groups * GEMV_ROWS * q.npc;
         if (q.n_groups > 0) xq += gemv_xq_bytes(sg.K);
+    }
+    bp.n_items = items;
+    bp.n_rows = rows;
+    bp.nseg = p.nseg;
+    bp.valid = 1;
+}
+
+// Plan of the r/k/v + adapter phase of the persistent kernel in dataflow mode. Segments 0..2 are the r, k, v matrices,
+// the rest the adapter down-projections. Blocks 2h and 2h + 1 compute the 64 rows of head h of each of r, k, v (the
+// first `split` row groups of the head go to block 2h, which also runs the head afterwards and holds its
+// up-projection weights, the other 16 - split to block 2h + 1); blocks 2H .. nb - 1 share the adapter rows by cost.
+__host__ inline void compute_plan_heads(const GemvParams& p, int bid, int nb, int H, int split, BlockPlan& bp) {
+    int items = 0, rows = 0, part = 0, xq = 0;
+    auto fill = [&](int s, int lo, int n_groups) {
+        const GemvSeg& sg = p.seg[s];
+        SegPlan& q = bp.sp[s];
+        q.lo = lo;
+        q.n_groups = n_groups;
+        q.nks = gemv_slices(sg.fmt, sg.K);
+        q.row_bytes = gemv_row_bytes(sg.fmt, sg.K);
+        int chunk = 1;
+        while (chunk * 2 <= q.nks && q.nks % (chunk * 2) == 0 && q.n_groups * (q.nks / (chunk * 2)) >= 2 * GEMV_WARPS) chunk *= 2;
+        q.chunk = chunk;
+        q.npc = q.nks / chunk;
+        q.item_base = items;
+        q.n_items = q.n_groups * q.npc;
+        q.row_base = rows;
+        q.part_base = part;
+        q.xq_off = xq;
+        items += q.n_items;
+        rows += q.n_groups * GEMV_ROWS;
+        part += q.n_groups * GEMV_ROWS * q.npc;
+        if (q.n_groups > 0) xq += gemv_xq_bytes(sg.K);
+    };
+    const int gph = HEAD / GEMV_ROWS;   // row groups per head
+    if (bid < 2 * H) {
+        const int h = bid >> 1, odd = bid & 1;
+        const int lo = h * gph + (odd ? split : 0), n = odd ? gph - split : split;
+        for (int s = 0; s < p.nseg; ++s) fill(s, s < 3 ? lo : 0, s < 3 ? n : 0);
+    } else {
+        const int b = bid - 2 * H, nd = nb - 2 * H;
+        unsigned total = 0;
+        for (int s = 3; s < p.nseg; ++s)
+            total += (unsigned)gemv_groups_of(p.seg[s].n_rows) * (unsigned)gemv_group_cost(p.seg[s].fmt, p.seg[s].K);
+        const unsigned C0 = (unsigned)((unsigned long long)total * (unsigned)b / (unsigned)nd);
+        const unsigned C1 = (unsigned)((unsigned long long)total * (unsigned)(b + 1) / (unsigned)nd);
+        unsigned base = 0;
+        for (int s = 0; s < p.nseg; ++s) {
+            if (s < 3) { fill(s, 0, 0); continue; }
+            const unsigned n = (unsigned)gemv_groups_of(p.seg[s].n_rows), unit = (unsigned)gemv_group_cost(p.seg[s].fmt, p.seg[s].K);
+            unsigned l = C0 <= base ? 0u : (C0 - base + unit - 1) / unit;
+            unsigned hgh = C1 <= base ? 0u : (C1 - base + unit - 1) / unit;
+            if (l > n) l = n;
+            if (hgh > n) hgh = n;
+            fill(s, (int)l, (int)(hgh - l));
+            base += n * unit;
+        }
     }
     bp.n_items = items;
     bp.n_rows = rows;
@@ -392,7 +514,7 @@ __device__ __forceinline__ float2 cons_block_sum2(float a, float b, float* red, 
 }
 
 // Prepare one segment's input in shared memory in the form its rows consume (16 elements per thread per pass).
-__device__ __forceinline__ void prep_x(const GemvSeg& sg, const GemvSmem& m, int xq_off, int tid) {
+__device__ __forceinline__ void prep_x(const GemvSeg& sg, const GemvSmem& m, int xq_off, int tid, uint32_t epoch) {
     const int warp = tid >> 5, lane = tid & 31;
     const int K = sg.K, Kp = (K + 511) & ~511;
     unsigned char* xq = m.xq + xq_off;
@@ -403,7 +525,10 @@ __device__ __forceinline__ void prep_x(const GemvSeg& sg, const GemvSmem& m, int
         float v[16];
         if (in) {
             uint4 a0, a1;
-            if (sg.x) {
+            if (sg.x && sg.tag_x) {
+                a0 = ld_tagged8(sg.x, 2 * c, tag_of(epoch, sg.tag_x));
+                a1 = ld_tagged8(sg.x, 2 * c + 1, tag_of(epoch, sg.tag_x));
+            } else if (sg.x) {
                 a0 = ld_act16(reinterpret_cast<const uint4*>(sg.x) + 2 * c);
                 a1 = ld_act16(reinterpret_cast<const uint4*>(sg.x) + 2 * c + 1);
             } else {
@@ -483,10 +608,16 @@ __device__ __forceinline__ void prep_x(const GemvSeg& sg, const GemvSmem& m, int
 //   pre_phase : launch phase whose item `warp` sits in the warp's prefetch slot, or -1
 //   np, nbp : the next matrix-vector launch and this block's plan for it (or null): each warp copies its
 //             first item of that launch into its slot when it runs out of items here
+struct NoHook {
+    __device__ __forceinline__ void operator()() const {}
+};
+// after_prep: called by every thread once the block's inputs are prepared, right before the weight stream starts (work
+// that may share the memory pipe with the stream but must not sit in front of the input vector's loads).
+template <class AfterPrep = NoHook>
 __device__ __forceinline__ void gemv_consume(const GemvParams& p, const BlockPlan& bp, const GemvSmem& m, int tid,
                                              int bid, int phase_idx, int& pre_phase, const GemvParams* np,
                                              const BlockPlan* nbp, int next_phase_idx, unsigned long long* tl = nullptr,
-                                             bool early = false) {
+                                             bool early = false, AfterPrep after_prep = AfterPrep(), uint32_t epoch = 0) {
     auto stamp = [&](int k) {
         if (tl && tid == 0) {
             unsigned long long t;
@@ -524,7 +655,8 @@ __device__ __forceinline__ void gemv_consume(const GemvParams& p, const BlockPla
             e_seg = s;
             e_row = row;
             e_scale = sg.fmt == FMT_I8 ? ld_early_f32(reinterpret_cast<const float*>(sg.scale) + row) : sg.tscale;
-            if (sg.epi == EPI_RESID) e_resid = ld_early_act_f16(sg.resid + row);
+            if (sg.epi == EPI_RESID)
+                e_resid = sg.tag_resid ? ld_tagged1(sg.resid, row, tag_of(epoch, sg.tag_resid)) : ld_early_act_f16(sg.resid + row);
         }
     }
 
@@ -552,13 +684,16 @@ __device__ __forceinline__ void gemv_consume(const GemvParams& p, const BlockPla
             const bool in = i < K / 8;
             uint4 v = make_uint4(0, 0, 0, 0), wv = v, bv = v, pv = v;
             if (in) {
-                v = ld_act16(reinterpret_cast<const uint4*>(xin) + i);
+                v = (p.tag_in && !p.emb) ? ld_tagged8(xin, i, tag_of(epoch, p.tag_in)) : ld_act16(reinterpret_cast<const uint4*>(xin) + i);
                 if (ln) {
                     wv = reinterpret_cast<const uint4*>(p.ln_w)[i];
                     bv = reinterpret_cast<const uint4*>(p.ln_b)[i];
                 }
                 if (any_mix) pv = ld_act16(reinterpret_cast<const uint4*>(p.x_prev) + i);
-                if (p.x_copy && bid == 0) reinterpret_cast<uint4*>(p.x_copy)[i] = v;
+                if (p.x_copy && bid == 0) {
+                    if (p.tag_in) st_tagged8(p.x_copy, i, v, tag_of(epoch, p.tag_in));
+                    else reinterpret_cast<uint4*>(p.x_copy)[i] = v;
+                }
             }
             issue_early();
             const __half2* h = reinterpret_cast<const __half2*>(&v);
@@ -652,9 +787,10 @@ __device__ __forceinline__ void gemv_consume(const GemvParams& p, const BlockPla
 
     // ---- prepared inputs of every segment this block touches
     for (int s = 0; s < bp.nseg; ++s)
-        if (bp.sp[s].n_groups > 0) prep_x(p.seg[s], m, bp.sp[s].xq_off, tid);
+        if (bp.sp[s].n_groups > 0) prep_x(p.seg[s], m, bp.sp[s].xq_off, tid, epoch);
     cons_sync();
     stamp(1);
+    after_prep();
 
     // ---- stream the block's items: warp w takes items w, w + 32, ...
     if (warp < bp.n_items) {
@@ -731,7 +867,8 @@ __device__ __forceinline__ void gemv_consume(const GemvParams& p, const BlockPla
             case EPI_RESID: o = e_resid + o; break;
             default: break;
         }
-        sg.out[e_row] = __float2half_rn(o);
+        if (sg.tag_out) st_tagged(sg.out, e_row, o, tag_of(epoch, sg.tag_out));
+        else sg.out[e_row] = __float2half_rn(o);
     }
 }
 

@@ -21,6 +21,9 @@ struct HeadParams {
     const __half* copy_src;    // optional [D] -> copy_dst (token-shift state hand-over, batch-1 path)
     __half* copy_dst;
     int use_pdl;
+    // Persistent batch-1 kernel, dataflow mode: head h is run by block 2h (pair_mode); r, k, v, the adapter hidden
+    // vectors and `out` are arrays of tagged words (tag_in / tag_out: 1 + index of the writing phase, 0 = plain fp16).
+    int pair_mode, tag_in, tag_out, pad_;
 };
 
 int head_launch(const HeadParams& p, cudaStream_t stream);

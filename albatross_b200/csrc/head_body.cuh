@@ -20,6 +20,37 @@ struct SyncNamed256 {  // the first 256 threads of a larger block
 // activations may have been written by another SM earlier in the same kernel: bypass L1
 __device__ __forceinline__ float lda(const __half* p) { return __half2float(__ldcg(p)); }
 
+// Dataflow mode of the persistent kernel: the vectors that cross blocks (r, k, v, the adapter hidden vectors in; the
+// head output out) are arrays of tagged 32-bit words (fp16 value | phase tag << 16, see gemv_body.cuh); a reader spins
+// on the word itself until it carries the expected tag. `on == false`: plain fp16 arrays.
+struct HeadTags {
+    bool on;
+    uint32_t in, out;
+};
+__device__ __forceinline__ float head_ld(const __half* base, size_t idx, const HeadTags& tg) {
+    if (!tg.on) return lda(base + idx);
+    const uint32_t* p = reinterpret_cast<const uint32_t*>(base) + idx;
+    uint32_t w, it = 0;
+    while (true) {
+        asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(w) : "l"(p) : "memory");
+        if ((w >> 16) == tg.in) break;
+        if (++it > (1u << 21)) {
+            atomicOr(&g_device_status, DEV_WAIT_HEAD);
+            break;
+        }
+        __nanosleep(it < 4 ? 100u : 400u);
+    }
+    return __half2float(__ushort_as_half((unsigned short)(w & 0xffffu)));
+}
+__device__ __forceinline__ void head_st(__half* base, size_t idx, float v, const HeadTags& tg) {
+    if (!tg.on) {
+        base[idx] = __float2half_rn(v);
+        return;
+    }
+    const uint32_t w = (uint32_t)__half_as_ushort(__float2half_rn(v)) | (tg.out << 16);
+    asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(reinterpret_cast<uint32_t*>(base) + idx), "r"(w) : "memory");
+}
+
 struct StateRow {
     float s[16];
 };
@@ -67,7 +98,8 @@ __device__ __forceinline__ void head_ups_stage(const HeadParams& p, int h, int t
 }
 // Part 2: sh.up[m][c] = sum_j hidden_m[j] * W2_m[j, h*64 + c] for the four adapters m (w, a, v-gate, g).
 template <class Sync>
-__device__ __forceinline__ void head_ups_compute(const HeadParams& p, int tid, unsigned char* dsm, HeadShared& sh, Sync sync) {
+__device__ __forceinline__ void head_ups_compute(const HeadParams& p, int tid, unsigned char* dsm, HeadShared& sh, Sync sync,
+                                                 const HeadTags tg = HeadTags{false, 0u, 0u}) {
     const int rtot = p.rw + p.ra + p.rv + p.rg;
     const int lane = tid & 31, warp = tid >> 5;
     const __half* w2s = reinterpret_cast<const __half*>(dsm);
@@ -80,7 +112,7 @@ __device__ __forceinline__ void head_ups_compute(const HeadParams& p, int tid, u
         else if ((row -= p.rw) < p.ra) hv = p.ha;
         else if ((row -= p.ra) < p.rv) hv = p.hv;
         else { row -= p.rv; hv = p.hg; }
-        hvec[j] = lda(hv + row);
+        hvec[j] = head_ld(hv, (size_t)row, tg);
     }
     head_cp_async_wait_all();
     sync();
@@ -135,7 +167,7 @@ __device__ __forceinline__ float wkv_step(StateRow& st, const float* w, const fl
 // All T steps of one (sequence b, head h) for the 256 threads tid = 0..255.
 template <class Sync>
 __device__ __forceinline__ void head_steps(const HeadParams& p, int b, int h, int tid, StateRow& st, HeadShared& sh,
-                                           bool ups, Sync sync) {
+                                           bool ups, Sync sync, const HeadTags tg = HeadTags{false, 0u, 0u}) {
     const int i = tid >> 2, q = tid & 3, lane = tid & 31, warp = tid >> 5;
     const int D = p.D;
     float* sr = sh.r; float* sw = sh.w; float* sk = sh.k; float* sa_ = sh.a; float* sb = sh.b; float* sv = sh.v; float* sy = sh.y;
@@ -149,9 +181,9 @@ __device__ __forceinline__ void head_steps(const HeadParams& p, int b, int h, in
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int c = lane + 32 * e, gc = h * 64 + c;
-                const float rr = lda(p.r + off + c);
-                const float kr = lda(p.k + off + c);
-                float vv = lda(p.v + off + c);
+                const float rr = head_ld(p.r, off + c, tg);
+                const float kr = head_ld(p.k, off + c, tg);
+                float vv = head_ld(p.v, off + c, tg);
                 const float w_raw = ups ? up[0][c] : lda(p.w_raw + off + c);
                 const float a_raw = ups ? up[1][c] : lda(p.a_raw + off + c);
                 const float a = rh(sigmoidf_(rh(__half2float(p.a0[gc]) + a_raw)));
@@ -198,7 +230,7 @@ __device__ __forceinline__ void head_steps(const HeadParams& p, int b, int h, in
                 float o = rh((e ? d1 : d0) * rstd * __half2float(p.lnx_w[gc]) + __half2float(p.lnx_b[gc]));
                 o = rh(o + rh(rkr * sv[c]));
                 const float g = ups ? up[3][c] : lda(p.g + off + c);
-                p.out[off + c] = __float2half_rn(o * g);
+                head_st(p.out, off + c, o * g, tg);
             }
         } else {
             sync();

@@ -380,7 +380,9 @@ class RWKV_x070:
         """Per-phase (start, end) timestamps in ns of the last persistent decode step on `state`, as seen by
         block 0; needs set_option("timeline", 1) before the program for `state` was built."""
         prog, prog_ptr, _, _ = self._program_for(state)
-        per_block = 5 if self._options.get("merge_ups", 0) and self.n_head <= 148 else 6
+        merged = self._options.get("merge_ups", 0) and self.n_head <= 148
+        fused = self._options.get("fuse_heads", 1) and not self._options.get("merge_ups", 0) and 2 * self.n_head + 4 <= 148
+        per_block = 5 if (merged or fused) else 6
         n = per_block * self.n_layer + 1
         hdr = _lib.lib.ab_decode_timeline_offset(self._handle)
         off = (prog_ptr - prog.data_ptr()) + hdr

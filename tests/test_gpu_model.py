@@ -116,7 +116,7 @@ def test_pipeline_stages_chain_to_the_full_model():
     assert torch.equal(st[0][1], st_full[1]) and torch.equal(st[1][1], st_full[4]) and len(st[0]) == 3
 
 
-@pytest.mark.parametrize("option", ["merge_ups", "l2_prefetch_kb", "smem_prefetch", "early_slice", "barrier_prefetch"])
+@pytest.mark.parametrize("option", ["merge_ups", "fuse_heads", "pair_split", "l2_prefetch_kb", "smem_prefetch", "early_slice", "barrier_prefetch"])
 def test_persistent_kernel_options_do_not_change_results(option):
     """The scheduling options of the persistent kernel move work between phases; logits stay the same: bit for bit
     for the prefetch options. The merged adapter phase sums the up-projections in another order (fp32), which can
@@ -125,6 +125,8 @@ def test_persistent_kernel_options_do_not_change_results(option):
     toks = seeded_tokens(args.vocab_size, 6, seed=9)
 
     def run(value):
+        if option in ("smem_prefetch", "early_slice", "barrier_prefetch"):
+            model.set_option("fuse_heads", 0)      # these options use the shared-memory area the fused heads stage into
         model.set_option(option, value)
         st, outs = None, []
         for t in toks:
@@ -132,10 +134,11 @@ def test_persistent_kernel_options_do_not_change_results(option):
             outs.append(logits.float().clone())
         return torch.stack(outs)
 
-    base = run(0)
-    alt = run(64 if option == "l2_prefetch_kb" else 1)
-    model.set_option(option, 0)
-    if option == "merge_ups":
+    base = run(6 if option == "pair_split" else 0)
+    alt = run({"l2_prefetch_kb": 64, "pair_split": 9}.get(option, 1))
+    model.set_option(option, 6 if option == "pair_split" else (1 if option == "fuse_heads" else 0))
+    model.set_option("fuse_heads", 1)
+    if option in ("merge_ups", "fuse_heads"):
         err = rel_err(alt.cpu().numpy(), base.cpu().numpy())
         assert err <= LOGIT_REL_TOL, err
     else:
@@ -212,16 +215,16 @@ def test_batch1_modes_give_identical_logits():
     """CUDA-graph replay and per-phase launches are the same kernels; the persistent kernel runs the same arithmetic
     when its adapter up-projections are computed inside the head phase (option "merge_ups")."""
     outs = []
-    for mode in ("persistent", "graph", "eager"):
-        model, args = model_for("0.1b", "int8", decode_mode=mode, use_graph=(mode != "eager"))
-        if mode == "persistent":
-            model.set_option("merge_ups", 1)
+    for mode in ("persistent", "persistent-merged", "graph", "eager"):
+        model, args = model_for("0.1b", "int8", decode_mode=mode.split("-")[0], use_graph=(mode != "eager"))
+        if mode == "persistent-merged":
+            model.set_option("merge_ups", 1)     # (the default, "fuse_heads", computes the up-projections the same way)
         st, seq = None, []
         for t in seeded_tokens(args.vocab_size, 5, seed=4):
             logits, st = model.forward(t, st)
             seq.append(logits.clone())
         outs.append(torch.stack(seq))
-    assert torch.equal(outs[0], outs[2]) and torch.equal(outs[1], outs[2])
+    assert all(torch.equal(o, outs[-1]) for o in outs[:-1])
 
 
 def test_token_ids_are_range_checked_on_the_host_and_clamped_on_the_device():
