@@ -71,6 +71,42 @@ __device__ __forceinline__ void stage_phase(DecodePhase* dst, const DecodePhase*
         reinterpret_cast<uint4*>(dst)[j] = reinterpret_cast<const uint4*>(src)[j];
 }
 
+// The per-head phase of one network block. Its own function (not inlined) so that the register allocation of the
+// matrix-vector phases, which run at the kernel's register cap, does not have to make room for it.
+__device__ __noinline__ void head_phase(const HeadParams& hp, int bid, int nb, int tid, unsigned char* smem, unsigned char* pref,
+                                        const __half* xn, HeadShared& hsh, uint32_t epoch, unsigned long long* htl) {
+    // adapter up-projections inside the phase: block h needs only the 64 channels of head h, so the
+    // matrix-vector phase (and the grid barrier) that would produce them for everybody is not needed
+    const bool ups = hp.w2 != nullptr;
+    // Dataflow mode (pair_mode): no barrier among all blocks came before this phase. Block 2h runs head h; its
+    // inputs (the head's r / k / v rows, the adapter hidden vectors) are tagged words and the loads wait for
+    // them one by one. Everybody else goes straight on to the next phase.
+    const bool pair = hp.pair_mode != 0;
+    const bool mine = !pair || (bid < 2 * hp.H && (bid & 1) == 0);
+    for (int h = pair ? (bid >> 1) : bid; mine && h < hp.H; h += pair ? hp.H : nb) {   // block-uniform
+        if (tid < HT) {
+            unsigned char* dsm = pair ? pref : smem;   // pair mode: staged during the phase before
+            if (ups && !pair) head_ups_stage(hp, h, tid, dsm);   // the matrix-vector buffers are idle in this phase
+            float* sbase = hp.state + (size_t)h * 4096;
+            StateRow st;
+            load_state(st, sbase, tid >> 2, tid & 3);   // last written a token ago: in flight while the inputs arrive
+            const HeadTags tg = {hp.tag_in != 0, tag_of(epoch, hp.tag_in), tag_of(epoch, hp.tag_out)};
+            if (ups) head_ups_compute(hp, tid, dsm, hsh, SyncNamed256(), tg, htl);
+            if (htl) htl[2] = global_ns();
+            head_steps(hp, 0, h, tid, st, hsh, ups, SyncNamed256(), tg, (pair && ups) ? head_par_area(hp, dsm) : nullptr);
+            if (htl) htl[3] = global_ns();
+            store_state(st, sbase, tid >> 2, tid & 3);
+            // token-shift state hand-over. Pair mode: the normalised input of the phase before is still in this
+            // block's shared memory (every block prepared it), so no other block's global write is read here.
+            if (hp.copy_dst && tid < 32)
+                reinterpret_cast<__half2*>(hp.copy_dst + h * 64)[tid] =
+                    pair ? reinterpret_cast<const __half2*>(xn + h * 64)[tid]
+                         : __ldcg(reinterpret_cast<const __half2*>(hp.copy_src + h * 64) + tid);
+            SyncNamed256()();
+        }
+    }
+}
+
 __global__ void __launch_bounds__(GEMV_THREADS, 1) decode_kernel(const DecodeProgram* __restrict__ prog) {
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ HeadShared hsh;
@@ -98,12 +134,23 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) decode_kernel(const DecodePro
     int pre_phase = -1;
     unsigned n_barriers = 0;
     for (int i = 0; i < n_phases; ++i) {
+        // Descriptor and plan of phase i + 3 are copied asynchronously (a synchronous copy stalls every warp for a
+        // memory round trip at the top of every phase). This thread's copies of the earlier iterations are complete
+        // after the wait; the block barrier at the end of the iteration publishes them, two phases before their use.
+        asm volatile("cp.async.wait_all;" ::: "memory");
         if (i + 3 < n_phases) {
-            stage_phase(&phs[(i + 3) & 3], &prog->phases[i + 3], tid);
-            stage_plan(i + 3);
+            const unsigned char* src_ph = reinterpret_cast<const unsigned char*>(&prog->phases[i + 3]);
+            unsigned char* dst_ph = reinterpret_cast<unsigned char*>(&phs[(i + 3) & 3]);
+            for (int j = tid; j < (int)(sizeof(DecodePhase) / 16); j += NT_CONS)
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_ph + 16 * j)), "l"(src_ph + 16 * j) : "memory");
+            const unsigned char* src_pl = reinterpret_cast<const unsigned char*>(&my_plans[(size_t)(i + 3) * nb]);
+            unsigned char* dst_pl = reinterpret_cast<unsigned char*>(&plans[(i + 3) & 3]);
+            for (int j = tid; j < (int)(sizeof(BlockPlan) / 16); j += NT_CONS)
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_pl + 16 * j)), "l"(src_pl + 16 * j) : "memory");
+            asm volatile("cp.async.commit_group;" ::: "memory");
         }
         const DecodePhase& ph = phs[i & 3];
-        if (prog->timeline && bid == 0 && tid == 0) prog->timeline[2 * i] = global_ns();
+        if (prog->timeline && bid == prog->timeline_block && tid == 0) prog->timeline[2 * i] = global_ns();
         if (ph.type == PHASE_GEMV) {
             const int j = ph.next_gemv;
             // one thread plans the next matrix-vector phase while the others run this prologue
@@ -125,7 +172,9 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) decode_kernel(const DecodePro
             const bool pre = j >= 0 && prog->smem_prefetch;
             gemv_consume(ph.g, plans[i & 3], m, tid, bid, i, pre_phase, pre ? &phs[j & 3].g : nullptr,
                          pre ? &plans[j & 3] : nullptr, j,
-                         (prog->timeline && bid == 0) ? prog->timeline + 2 * n_phases + 4 * i : nullptr, prog->early_slice != 0,
+                         (prog->timeline && bid == prog->timeline_block) ? prog->timeline + 2 * n_phases + 4 * i : nullptr,
+                         // the first-slice prefetch uses the area that the phase before a paired head phase stages into
+                         prog->early_slice != 0 && !(i + 1 < n_phases && phs[(i + 1) & 3].type == PHASE_HEAD && phs[(i + 1) & 3].h.pair_mode),
                          [&]() {
                              if (ph.no_barrier == 2 && tid < HT && bid < 2 * phs[(i + 1) & 3].h.H && (bid & 1) == 0) {
                                  // "fused heads": this block runs head bid / 2 right after the phase. Its slices of the
@@ -136,50 +185,16 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) decode_kernel(const DecodePro
                                  const HeadParams& nh = phs[(i + 1) & 3].h;
                                  const int h = bid >> 1;
                                  head_ups_stage(nh, h, tid, m.pref);
+                                 head_par_stage(nh, h, tid, m.pref);
                                  asm volatile("cp.async.commit_group;" ::: "memory");
                                  if (tid < 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(nh.state + (size_t)h * 4096 + tid * 32));
-                                 if (tid < 8) {
-                                     const __half* v[8] = {nh.w0, nh.a0, nh.v0, nh.k_k, nh.k_a, nh.r_k, nh.lnx_w, nh.lnx_b};
-                                     const __half* q = v[0];
-#pragma unroll
-                                     for (int e = 1; e < 8; ++e)
-                                         if (tid == e) q = v[e];
-                                     if (q) asm volatile("prefetch.global.L1 [%0];" ::"l"(q + h * 64));
-                                 }
                              }
                          }, epoch);
         } else {
-            const HeadParams& hp = ph.h;
-            // adapter up-projections inside the phase: block h needs only the 64 channels of head h, so the
-            // matrix-vector phase (and the grid barrier) that would produce them for everybody is not needed
-            const bool ups = hp.w2 != nullptr;
-            // Dataflow mode (pair_mode): no barrier among all blocks came before this phase. Block 2h runs head h; its
-            // inputs (the head's r / k / v rows, the adapter hidden vectors) are tagged words and the loads wait for
-            // them one by one. Everybody else goes straight on to the next phase.
-            const bool pair = hp.pair_mode != 0;
-            const bool mine = !pair || (bid < 2 * hp.H && (bid & 1) == 0);
-            for (int h = pair ? (bid >> 1) : bid; mine && h < hp.H; h += pair ? hp.H : nb) {   // block-uniform
-                if (tid < HT) {
-                    unsigned char* dsm = pair ? m.pref : smem;   // pair mode: staged during the phase before
-                    if (ups && !pair) head_ups_stage(hp, h, tid, dsm);   // the matrix-vector buffers are idle in this phase
-                    float* sbase = hp.state + (size_t)h * 4096;
-                    StateRow st;
-                    load_state(st, sbase, tid >> 2, tid & 3);   // last written a token ago: in flight while the inputs arrive
-                    const HeadTags tg = {hp.tag_in != 0, tag_of(epoch, hp.tag_in), tag_of(epoch, hp.tag_out)};
-                    if (ups) head_ups_compute(hp, tid, dsm, hsh, SyncNamed256(), tg);
-                    head_steps(hp, 0, h, tid, st, hsh, ups, SyncNamed256(), tg);
-                    store_state(st, sbase, tid >> 2, tid & 3);
-                    // token-shift state hand-over. Pair mode: the normalised input of the phase before is still in this
-                    // block's shared memory (every block prepared it), so no other block's global write is read here.
-                    if (hp.copy_dst && tid < 32)
-                        reinterpret_cast<__half2*>(hp.copy_dst + h * 64)[tid] =
-                            pair ? reinterpret_cast<const __half2*>(m.xn + h * 64)[tid]
-                                 : __ldcg(reinterpret_cast<const __half2*>(hp.copy_src + h * 64) + tid);
-                    SyncNamed256()();
-                }
-            }
+            head_phase(ph.h, bid, nb, tid, smem, m.pref, m.xn, hsh, epoch,
+                       (prog->timeline && bid == prog->timeline_block && tid == 0) ? prog->timeline + 2 * n_phases + 4 * i : nullptr);
         }
-        if (prog->timeline && bid == 0 && tid == 0) prog->timeline[2 * i + 1] = global_ns();
+        if (prog->timeline && bid == prog->timeline_block && tid == 0) prog->timeline[2 * i + 1] = global_ns();
         if (i + 1 < n_phases) {
             if (ph.no_barrier) {
                 // a block barrier only: either the same block produces and consumes, or (dataflow mode) the phase's

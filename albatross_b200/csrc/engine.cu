@@ -59,15 +59,17 @@ struct ab_model {
     int prog_xq_bytes = 0;
     int debug_sync = 0;  // synchronise after every launch and name the one that failed
     int timeline = 0;    // persistent decode kernel records per-phase timestamps
+    int timeline_block = 0;   // ... as seen by this block
     int l2_prefetch_kb = 0;   // persistent decode kernel: L2 prefetch of the next phase, per block
     int smem_prefetch = 0;
-    int early_slice = 0;   // measured slower: any weight traffic in flight delays the loads of the input vector
+    int early_slice = -1;  // first weight slice requested ahead of the input vector: -1 = in dataflow mode only (there it travels
+                           // while the block waits for its input anyway; with barriers it delays the input loads and is slower)
     int barrier_prefetch = 0;   // measured slower: the polls of the barrier queue behind the prefetch traffic
     int stage_gemv = 0;  // ab_forward_stage at B = T = 1 runs the batch-1 matrix-vector kernels instead of the row-wise program
     int fuse_heads = 1;  // persistent decode kernel: r/k/v rows of head h on blocks 2h, 2h+1, the adapter down-projections on
                          // the remaining blocks; block 2h runs the head (up-projections from pre-staged weights, WKV step)
                          // as soon as those producers have signalled: two barriers among all blocks fewer per network block
-    int pair_split = 6;  // ... row groups (of 4 rows) of a head's 16 that go to block 2h (which also stages the up-projections)
+    int pair_split = 16; // ... row groups (of 4 rows) of a head's 48 (r, k, v) that go to block 2h (which also stages the up-projections)
     int merge_ups = 0;   // persistent decode kernel: block h computes the adapter up-projections of head h inside the head
                          // phase: one phase and barrier fewer per block and the same arithmetic as the per-phase
                          // launches (identical logits), but 3 % slower per token than the phase of matrix-vector rows
@@ -254,10 +256,12 @@ int build_decode_program(ab_model* m, const int32_t* token, void* const* state, 
     // the in-phase adapter up-projection stages its matrices where the prefetched slices would wait: one or the other
     const bool stage_area_taken = m->merge_ups || m->fuse_heads;
     prog->smem_prefetch = stage_area_taken ? 0 : m->smem_prefetch;
-    prog->early_slice = stage_area_taken ? 0 : m->early_slice;
+    // (dataflow mode: only in the phases that do not stage up-projections into the same area)
+    prog->early_slice = m->merge_ups ? 0 : (m->early_slice < 0 ? (m->fuse_heads ? 1 : 0) : m->early_slice);
     prog->barrier_prefetch = stage_area_taken ? 0 : m->barrier_prefetch;
     prog->barrier = const_cast<unsigned*>(&dev_addr->barrier_word);
     prog->epoch = 1;   // tags start above zero: freshly cleared words (tag 0) are "not written yet"
+    prog->timeline_block = m->timeline_block;
     prog->timeline = m->timeline ? (unsigned long long*)((unsigned char*)dev_addr +
                                                           decode_timeline_offset(n_phases, m->n_sm)) : nullptr;
     int n = 0;
@@ -299,8 +303,8 @@ int build_decode_program(ab_model* m, const int32_t* token, void* const* state, 
         // in the three matrices, and the head's up-projection slices in the idle prefetch area
         const bool fused = m->fuse_heads && !m->merge_ups && 2 * H + 4 <= m->n_sm &&
                            Ly.receptance.n_out == D && Ly.key.n_out == D && Ly.value.n_out == D &&
-                           head_ups_smem(rtot) <= (size_t)GEMV_WARPS * GEMV_ROWS * GEMV_SLICE_BYTES &&
-                           m->pair_split >= 1 && m->pair_split <= HEAD / GEMV_ROWS - 1;
+                           head_ups_smem(rtot) + 8 * 64 * 2 <= (size_t)GEMV_WARPS * GEMV_ROWS * GEMV_SLICE_BYTES &&
+                           m->pair_split >= 1 && m->pair_split <= 3 * (HEAD / GEMV_ROWS) - 1;
         AB_CHECK_ARG(i == 0 || fused == (x_tag != 0), "decode program: the blocks of the network must all take the same mode");
         if (fused) {
             DecodePhase& p1 = prog->phases[n - 1];
@@ -628,13 +632,14 @@ int ab_model_set_option(ab_model* m, const char* name, int value) {
     else if (!strcmp(name, "pdl")) m->use_pdl = value != 0;
     else if (!strcmp(name, "debug_sync")) m->debug_sync = value != 0;
     else if (!strcmp(name, "timeline")) m->timeline = value != 0;
+    else if (!strcmp(name, "timeline_block")) m->timeline_block = value < 0 ? 0 : value;
     else if (!strcmp(name, "l2_prefetch_kb")) m->l2_prefetch_kb = value < 0 ? 0 : value;
     else if (!strcmp(name, "smem_prefetch")) m->smem_prefetch = value != 0;
     else if (!strcmp(name, "merge_ups")) m->merge_ups = value != 0;
     else if (!strcmp(name, "fuse_heads")) m->fuse_heads = value != 0;
     else if (!strcmp(name, "pair_split")) m->pair_split = value;
     else if (!strcmp(name, "stage_gemv")) m->stage_gemv = value != 0;
-    else if (!strcmp(name, "early_slice")) m->early_slice = value != 0;
+    else if (!strcmp(name, "early_slice")) m->early_slice = value < 0 ? -1 : (value != 0);
     else if (!strcmp(name, "barrier_prefetch")) m->barrier_prefetch = value != 0;
     else if (!strcmp(name, "layer_offset")) { AB_CHECK_ARG(value >= 0, "layer_offset must be >= 0"); m->layer_offset = value; }
     else { set_error("unknown option %s", name); return ERR_BAD_ARG; }

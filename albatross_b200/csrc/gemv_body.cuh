@@ -88,6 +88,29 @@ __device__ __forceinline__ uint4 ld_tagged8(const void* base, int idx8, uint32_t
     return make_uint4(__byte_perm(a.x, a.y, 0x5410), __byte_perm(a.z, a.w, 0x5410), __byte_perm(b.x, b.y, 0x5410),
                       __byte_perm(b.z, b.w, 0x5410));
 }
+// Sixteen consecutive tagged values (64-byte aligned): all four loads in flight before the first is looked at.
+__device__ __forceinline__ void ld_tagged16(const void* base, int idx16, uint32_t tag, uint4& lo, uint4& hi) {
+    const uint32_t* p = reinterpret_cast<const uint32_t*>(base) + 16 * (size_t)idx16;
+    const uint32_t t = tag << 16;
+    uint4 a, b, c, d;
+    uint32_t it = 0;
+    while (true) {
+        a = ld_relaxed_v4(p);
+        b = ld_relaxed_v4(p + 4);
+        c = ld_relaxed_v4(p + 8);
+        d = ld_relaxed_v4(p + 12);
+        const uint32_t bad = ((a.x ^ t) | (a.y ^ t) | (a.z ^ t) | (a.w ^ t) | (b.x ^ t) | (b.y ^ t) | (b.z ^ t) | (b.w ^ t) |
+                              (c.x ^ t) | (c.y ^ t) | (c.z ^ t) | (c.w ^ t) | (d.x ^ t) | (d.y ^ t) | (d.z ^ t) | (d.w ^ t)) >> 16;
+        if (!bad) break;
+        if (++it > TAG_SPIN_LIMIT) {
+            atomicOr(&g_device_status, DEV_WAIT_GEMV);
+            break;
+        }
+        __nanosleep(it < 4 ? 100u : 400u);
+    }
+    lo = make_uint4(__byte_perm(a.x, a.y, 0x5410), __byte_perm(a.z, a.w, 0x5410), __byte_perm(b.x, b.y, 0x5410), __byte_perm(b.z, b.w, 0x5410));
+    hi = make_uint4(__byte_perm(c.x, c.y, 0x5410), __byte_perm(c.z, c.w, 0x5410), __byte_perm(d.x, d.y, 0x5410), __byte_perm(d.z, d.w, 0x5410));
+}
 __device__ __forceinline__ void st_tagged8(void* base, int idx8, uint4 v, uint32_t tag) {
     uint32_t* p = reinterpret_cast<uint32_t*>(base) + 8 * (size_t)idx8;
     const uint32_t t = tag << 16, w[4] = {v.x, v.y, v.z, v.w};
@@ -248,9 +271,9 @@ __host__ __device__ inline void compute_plan_rows(const GemvParams& p, int bid, 
 }
 
 // Plan of the r/k/v + adapter phase of the persistent kernel in dataflow mode. Segments 0..2 are the r, k, v matrices,
-// the rest the adapter down-projections. Blocks 2h and 2h + 1 compute the 64 rows of head h of each of r, k, v (the
-// first `split` row groups of the head go to block 2h, which also runs the head afterwards and holds its
-// up-projection weights, the other 16 - split to block 2h + 1); blocks 2H .. nb - 1 share the adapter rows by cost.
+// the rest the adapter down-projections. Blocks 2h and 2h + 1 compute the 64 rows of head h of each of r, k, v (48 row
+// groups in the order r, k, v: the first `split` go to block 2h, which also runs the head afterwards and holds its
+// up-projection weights, the others to block 2h + 1); blocks 2H .. nb - 1 share the adapter rows by cost.
 __host__ inline void compute_plan_heads(const GemvParams& p, int bid, int nb, int H, int split, BlockPlan& bp) {
     int items = 0, rows = 0, part = 0, xq = 0;
     auto fill = [&](int s, int lo, int n_groups) {
@@ -274,11 +297,20 @@ __host__ inline void compute_plan_heads(const GemvParams& p, int bid, int nb, in
         part += q.n_groups * GEMV_ROWS * q.npc;
         if (q.n_groups > 0) xq += gemv_xq_bytes(sg.K);
     };
-    const int gph = HEAD / GEMV_ROWS;   // row groups per head
+    const int gph = HEAD / GEMV_ROWS;   // row groups per head and matrix
     if (bid < 2 * H) {
+        // the head's 3 * gph row groups in the order r, k, v: block 2h takes the first `split`, block 2h + 1 the rest, so
+        // that each of them prepares the inputs of two matrices at most
         const int h = bid >> 1, odd = bid & 1;
-        const int lo = h * gph + (odd ? split : 0), n = odd ? gph - split : split;
-        for (int s = 0; s < p.nseg; ++s) fill(s, s < 3 ? lo : 0, s < 3 ? n : 0);
+        const int g0 = odd ? split : 0, g1 = odd ? 3 * gph : split;
+        for (int s = 0; s < p.nseg; ++s) {
+            int lo = 0, n = 0;
+            if (s < 3) {
+                const int a = g0 > s * gph ? g0 : s * gph, b = g1 < (s + 1) * gph ? g1 : (s + 1) * gph;
+                if (b > a) { lo = h * gph + a - s * gph; n = b - a; }
+            }
+            fill(s, lo, n);
+        }
     } else {
         const int b = bid - 2 * H, nd = nb - 2 * H;
         unsigned total = 0;
@@ -513,21 +545,21 @@ __device__ __forceinline__ float2 cons_block_sum2(float a, float b, float* red, 
     return make_float2(ta, tb);
 }
 
-// Prepare one segment's input in shared memory in the form its rows consume (16 elements per thread per pass).
-__device__ __forceinline__ void prep_x(const GemvSeg& sg, const GemvSmem& m, int xq_off, int tid, uint32_t epoch) {
-    const int warp = tid >> 5, lane = tid & 31;
+// Prepare 512 inputs (block `kb`) of one segment's input in shared memory in the form its rows consume: one warp, 16
+// elements per lane.
+__device__ __forceinline__ void prep_x_block(const GemvSeg& sg, const GemvSmem& m, int xq_off, int kb, int lane, uint32_t epoch) {
     const int K = sg.K, Kp = (K + 511) & ~511;
     unsigned char* xq = m.xq + xq_off;
     float* sx = m.sx + xq_off / 1024;
-    for (int c0 = warp * 32; c0 < Kp / 16; c0 += NT_CONS) {
+    {
+        const int c0 = kb * 32;
         const int c = c0 + lane;
         const bool in = c * 16 < K;
         float v[16];
         if (in) {
             uint4 a0, a1;
             if (sg.x && sg.tag_x) {
-                a0 = ld_tagged8(sg.x, 2 * c, tag_of(epoch, sg.tag_x));
-                a1 = ld_tagged8(sg.x, 2 * c + 1, tag_of(epoch, sg.tag_x));
+                ld_tagged16(sg.x, c, tag_of(epoch, sg.tag_x), a0, a1);
             } else if (sg.x) {
                 a0 = ld_act16(reinterpret_cast<const uint4*>(sg.x) + 2 * c);
                 a1 = ld_act16(reinterpret_cast<const uint4*>(sg.x) + 2 * c + 1);
@@ -638,6 +670,9 @@ __device__ __forceinline__ void gemv_consume(const GemvParams& p, const BlockPla
             early_issued = true;
         }
     };
+
+    // dataflow mode: the input is waited for below (tagged words); the first weight slice travels in the meantime
+    if (epoch) issue_early();
 
     if (p.copy_src && bid == 0)
         for (int i = tid; i < p.copy_n / 8; i += NT_CONS)
@@ -786,8 +821,15 @@ __device__ __forceinline__ void gemv_consume(const GemvParams& p, const BlockPla
     issue_early();
 
     // ---- prepared inputs of every segment this block touches
-    for (int s = 0; s < bp.nseg; ++s)
-        if (bp.sp[s].n_groups > 0) prep_x(p.seg[s], m, bp.sp[s].xq_off, tid, epoch);
+    {   // warp tasks = (segment the block touches, 512-input block of its input), dealt round-robin to all warps
+        int t = warp;   // this warp's next task, counted from the first block of the current segment
+        for (int s = 0; s < bp.nseg; ++s) {
+            if (bp.sp[s].n_groups <= 0) continue;
+            const int nb_k = (p.seg[s].K + 511) >> 9;
+            for (; t < nb_k; t += GEMV_WARPS) prep_x_block(p.seg[s], m, bp.sp[s].xq_off, t, lane, epoch);
+            t -= nb_k;
+        }
+    }
     cons_sync();
     stamp(1);
     after_prep();

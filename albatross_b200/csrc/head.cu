@@ -54,7 +54,7 @@ __global__ void __launch_bounds__(HT) wkv7_kernel(int T, int C, int H, float* __
 // ---------------------------------------------------------------------------------------------
 // Fused kernel
 // ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(HT) head_fused_kernel(const __grid_constant__ HeadParams p) {
+__global__ void __launch_bounds__(HT, 2) head_fused_kernel(const __grid_constant__ HeadParams p) {
     extern __shared__ __align__(128) unsigned char dsm[];
     __shared__ HeadShared sh;
     const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;

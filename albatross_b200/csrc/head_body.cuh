@@ -42,6 +42,42 @@ __device__ __forceinline__ float head_ld(const __half* base, size_t idx, const H
     }
     return __half2float(__ushort_as_half((unsigned short)(w & 0xffffu)));
 }
+// r, k, v of this lane's two channels (c = lane, lane + 32) in one go: six loads in flight, validated together (one
+// after the other, each with its own wait, they cost six memory round trips on the head's critical path).
+__device__ __forceinline__ void head_ld_rkv(const HeadParams& p, size_t off, int lane, const HeadTags& tg, float* rr, float* kr,
+                                            float* vv) {
+    if (!tg.on) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            rr[e] = lda(p.r + off + lane + 32 * e);
+            kr[e] = lda(p.k + off + lane + 32 * e);
+            vv[e] = lda(p.v + off + lane + 32 * e);
+        }
+        return;
+    }
+    const uint32_t* pr = reinterpret_cast<const uint32_t*>(p.r) + off + lane;
+    const uint32_t* pk = reinterpret_cast<const uint32_t*>(p.k) + off + lane;
+    const uint32_t* pv = reinterpret_cast<const uint32_t*>(p.v) + off + lane;
+    uint32_t w0, w1, w2, w3, w4, w5, it = 0;
+    while (true) {
+        asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(w0) : "l"(pr) : "memory");
+        asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(w1) : "l"(pr + 32) : "memory");
+        asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(w2) : "l"(pk) : "memory");
+        asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(w3) : "l"(pk + 32) : "memory");
+        asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(w4) : "l"(pv) : "memory");
+        asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(w5) : "l"(pv + 32) : "memory");
+        const uint32_t bad = ((w0 >> 16) ^ tg.in) | ((w1 >> 16) ^ tg.in) | ((w2 >> 16) ^ tg.in) | ((w3 >> 16) ^ tg.in) |
+                             ((w4 >> 16) ^ tg.in) | ((w5 >> 16) ^ tg.in);
+        if (!bad) break;
+        if (++it > (1u << 21)) {
+            atomicOr(&g_device_status, DEV_WAIT_HEAD);
+            break;
+        }
+        __nanosleep(it < 4 ? 100u : 400u);
+    }
+    auto val = [](uint32_t x) { return __half2float(__ushort_as_half((unsigned short)(x & 0xffffu))); };
+    rr[0] = val(w0); rr[1] = val(w1); kr[0] = val(w2); kr[1] = val(w3); vv[0] = val(w4); vv[1] = val(w5);
+}
 __device__ __forceinline__ void head_st(__half* base, size_t idx, float v, const HeadTags& tg) {
     if (!tg.on) {
         base[idx] = __float2half_rn(v);
@@ -96,26 +132,73 @@ __device__ __forceinline__ void head_ups_stage(const HeadParams& p, int h, int t
         head_cp_async16(w2s + (size_t)(pc >> 3) * 64 + seg8 * 8, m + (size_t)row * p.D + h * 64 + seg8 * 8);
     }
 }
+// The head's eight per-channel parameter vectors (64 fp16 each) behind the staged up-projection slices: [8][64] fp16.
+__device__ __forceinline__ __half* head_par_area(const HeadParams& p, unsigned char* dsm) {
+    return reinterpret_cast<__half*>(dsm + head_ups_smem(p.rw + p.ra + p.rv + p.rg));
+}
+__device__ __forceinline__ void head_par_stage(const HeadParams& p, int h, int tid, unsigned char* dsm) {
+    if (tid < 64) {
+        const int which = tid >> 3, chunk = tid & 7;
+        const __half* v[8] = {p.w0, p.a0, p.v0, p.k_k, p.k_a, p.r_k, p.lnx_w, p.lnx_b};
+        const __half* src = v[0];
+#pragma unroll
+        for (int e = 1; e < 8; ++e)
+            if (which == e) src = v[e];
+        if (src) head_cp_async16(head_par_area(p, dsm) + which * 64 + chunk * 8, src + h * 64 + chunk * 8);
+    }
+}
 // Part 2: sh.up[m][c] = sum_j hidden_m[j] * W2_m[j, h*64 + c] for the four adapters m (w, a, v-gate, g).
 template <class Sync>
 __device__ __forceinline__ void head_ups_compute(const HeadParams& p, int tid, unsigned char* dsm, HeadShared& sh, Sync sync,
-                                                 const HeadTags tg = HeadTags{false, 0u, 0u}) {
+                                                 const HeadTags tg = HeadTags{false, 0u, 0u}, unsigned long long* tl = nullptr) {
     const int rtot = p.rw + p.ra + p.rv + p.rg;
     const int lane = tid & 31, warp = tid >> 5;
     const __half* w2s = reinterpret_cast<const __half*>(dsm);
     float* hvec = reinterpret_cast<float*>(dsm + (size_t)rtot * 128);   // [rtot]
     float* part = hvec + ((rtot + 3) & ~3);                             // [8][4][64]
-    for (int j = tid; j < rtot; j += HT) {
+    // all of this thread's entries are requested before the first one is looked at (each is a tagged word that may
+    // have to be waited for: one after the other they would cost a memory round trip each)
+    constexpr int HV_MAX = 4;   // entries per thread: adapter ranks up to 4 * 256 in total (longer lists loop)
+    auto addr = [&](int j) -> const __half* {   // entry j of the concatenated hidden vectors (a word each when tagged)
         int row = j;
         const __half* hv;
         if (row < p.rw) hv = p.hw;
         else if ((row -= p.rw) < p.ra) hv = p.ha;
         else if ((row -= p.ra) < p.rv) hv = p.hv;
         else { row -= p.rv; hv = p.hg; }
-        hvec[j] = head_ld(hv, (size_t)row, tg);
+        return tg.on ? hv + 2 * (size_t)row : hv + row;
+    };
+    for (int j0 = tid; j0 < rtot; j0 += HV_MAX * HT) {
+        if (!tg.on) {
+#pragma unroll
+            for (int e = 0; e < HV_MAX; ++e)
+                if (j0 + e * HT < rtot) hvec[j0 + e * HT] = lda(addr(j0 + e * HT));
+            continue;
+        }
+        uint32_t w[HV_MAX], it = 0;
+        while (true) {
+            uint32_t bad = 0;
+#pragma unroll
+            for (int e = 0; e < HV_MAX; ++e)
+                if (j0 + e * HT < rtot) asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(w[e]) : "l"(addr(j0 + e * HT)) : "memory");
+#pragma unroll
+            for (int e = 0; e < HV_MAX; ++e)
+                if (j0 + e * HT < rtot) bad |= (w[e] >> 16) ^ tg.in;
+            if (!bad) break;
+            if (++it > (1u << 21)) {
+                atomicOr(&g_device_status, DEV_WAIT_HEAD);
+                break;
+            }
+            __nanosleep(it < 4 ? 100u : 400u);
+        }
+#pragma unroll
+        for (int e = 0; e < HV_MAX; ++e)
+            if (j0 + e * HT < rtot) hvec[j0 + e * HT] = __half2float(__ushort_as_half((unsigned short)(w[e] & 0xffffu)));
     }
+    if (tl) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tl[0]));   // this thread's hidden-vector entries are in
     head_cp_async_wait_all();
     sync();
+    if (tl) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tl[1]));   // everybody's are, and the staged weights
     // warp `warp` takes rows j = warp (mod 8); lane covers channels 2*lane, 2*lane+1
     const int bounds[5] = {0, p.rw, p.rw + p.ra, p.rw + p.ra + p.rv, rtot};
 #pragma unroll
@@ -165,9 +248,15 @@ __device__ __forceinline__ float wkv_step(StateRow& st, const float* w, const fl
 
 
 // All T steps of one (sequence b, head h) for the 256 threads tid = 0..255.
+// `par`: the head's per-channel parameters staged in shared memory as [8][64] fp16 in the order w0, a0, v0, k_k, k_a, r_k,
+// ln_x weight, ln_x bias (null: read them from global memory).
+__device__ __forceinline__ float head_par(const __half* par, int which, const __half* global_vec, int gc, int c) {
+    return __half2float(par ? par[which * 64 + c] : global_vec[gc]);
+}
 template <class Sync>
 __device__ __forceinline__ void head_steps(const HeadParams& p, int b, int h, int tid, StateRow& st, HeadShared& sh,
-                                           bool ups, Sync sync, const HeadTags tg = HeadTags{false, 0u, 0u}) {
+                                           bool ups, Sync sync, const HeadTags tg = HeadTags{false, 0u, 0u},
+                                           const __half* par = nullptr) {
     const int i = tid >> 2, q = tid & 3, lane = tid & 31, warp = tid >> 5;
     const int D = p.D;
     float* sr = sh.r; float* sw = sh.w; float* sk = sh.k; float* sa_ = sh.a; float* sb = sh.b; float* sv = sh.v; float* sy = sh.y;
@@ -178,30 +267,32 @@ __device__ __forceinline__ void head_steps(const HeadParams& p, int b, int h, in
             // per-channel glue on two channels per lane; head-wide sums are warp shuffles
             float kk0[2], av[2], rk[2];
             float ssq = 0.f, rkr = 0.f;
+            float rr2[2], kr2[2], vv2[2];
+            head_ld_rkv(p, off, lane, tg, rr2, kr2, vv2);
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int c = lane + 32 * e, gc = h * 64 + c;
-                const float rr = head_ld(p.r, off + c, tg);
-                const float kr = head_ld(p.k, off + c, tg);
-                float vv = head_ld(p.v, off + c, tg);
+                const float rr = rr2[e];
+                const float kr = kr2[e];
+                float vv = vv2[e];
                 const float w_raw = ups ? up[0][c] : lda(p.w_raw + off + c);
                 const float a_raw = ups ? up[1][c] : lda(p.a_raw + off + c);
-                const float a = rh(sigmoidf_(rh(__half2float(p.a0[gc]) + a_raw)));
-                kk0[e] = rh(kr * __half2float(p.k_k[gc]));
+                const float a = rh(sigmoidf_(rh(head_par(par, 1, p.a0, gc, c) + a_raw)));
+                kk0[e] = rh(kr * head_par(par, 3, p.k_k, gc, c));
                 ssq = fmaf(kk0[e], kk0[e], ssq);
-                const float k2 = rh(kr * rh(1.f + rh(rh(a - 1.f) * __half2float(p.k_a[gc]))));
+                const float k2 = rh(kr * rh(1.f + rh(rh(a - 1.f) * head_par(par, 4, p.k_a, gc, c))));
                 if (p.layer0) {
                     p.v_first[off + c] = __float2half_rn(vv);
                 } else {
                     const float vg_raw = ups ? up[2][c] : lda(p.vg_raw + off + c);
-                    const float vg = rh(sigmoidf_(rh(__half2float(p.v0[gc]) + vg_raw)));
+                    const float vg = rh(sigmoidf_(rh(head_par(par, 2, p.v0, gc, c) + vg_raw)));
                     vv = rh(vv + rh(rh(lda(p.v_first + off + c) - vv) * vg));
                 }
                 // decay in fp32 as on the reference's single-token path (reference/rwkv7.py:241)
-                const float wd = __expf(-0.606531f * sigmoidf_(rh(__half2float(p.w0[gc]) + w_raw)));
+                const float wd = __expf(-0.606531f * sigmoidf_(rh(head_par(par, 0, p.w0, gc, c) + w_raw)));
                 sr[c] = rr; sw[c] = wd; sk[c] = k2; sv[c] = vv;
                 av[e] = a;
-                rk[e] = rh(rh(rr * k2) * __half2float(p.r_k[gc]));
+                rk[e] = rh(rh(rr * k2) * head_par(par, 5, p.r_k, gc, c));
                 rkr += rk[e];
             }
             ssq = warp_sum(ssq);
@@ -227,7 +318,7 @@ __device__ __forceinline__ void head_steps(const HeadParams& p, int b, int h, in
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int c = lane + 32 * e, gc = h * 64 + c;
-                float o = rh((e ? d1 : d0) * rstd * __half2float(p.lnx_w[gc]) + __half2float(p.lnx_b[gc]));
+                float o = rh((e ? d1 : d0) * rstd * head_par(par, 6, p.lnx_w, gc, c) + head_par(par, 7, p.lnx_b, gc, c));
                 o = rh(o + rh(rkr * sv[c]));
                 const float g = ups ? up[3][c] : lda(p.g + off + c);
                 head_st(p.out, off + c, o * g, tg);

@@ -69,9 +69,14 @@ class PipelineDecoder:
     """Decode steps through S pipeline stages with M micro-batches in flight.
 
     stage_fn(mb, x_in, v_first) -> (x_out, v_first) for stages other than the last, where x_in is None on the
-    first stage (it embeds the micro-batch's current tokens itself, via `tokens_of(mb)`), and
+    first stage (it embeds the micro-batch's current tokens itself), and
     stage_fn(mb, x_in, v_first) -> next token ids [b] on the last stage.
-    Buffers are [b, D] tensors created by `make_buffer(mb)`; token ids travel as int64.
+    Buffers are [b, D] tensors created by `make_buffer(mb)`; token ids travel as int64 (`make_tokens(mb)`).
+
+    Transport: point-to-point over torch.distributed. The two tensors of a stage boundary go out as ONE batched
+    operation (`batch_isend_irecv`), and the token ids travel back from the last to the first stage on a process
+    group of their own, so that the return path never queues behind (or in front of) the forward traffic of the same
+    pair of ranks. Nothing waits for a send at the point where it is issued.
     """
 
     def __init__(self, stage_fn: Callable, n_micro: int, make_buffer: Callable[[int], torch.Tensor],
@@ -82,37 +87,65 @@ class PipelineDecoder:
         self.S = dist.get_world_size(group)
         self.s = dist.get_rank(group)
         self.first, self.last = self.s == 0, self.s == self.S - 1
+        # every rank of the group calls this (new_group is collective); ranks are the global ranks of `group`
+        self.back_group = None
+        if self.S > 1:
+            ranks = dist.get_process_group_ranks(group) if group is not None else list(range(self.S))
+            self.back_group = dist.new_group(ranks=ranks)
+        self._ranks = dist.get_process_group_ranks(group) if group is not None else list(range(self.S))
+
+    def _peer(self, stage: int) -> int:
+        return self._ranks[stage]
 
     def step(self, tokens: Optional[List[torch.Tensor]]) -> Optional[List[torch.Tensor]]:
-        """One decode step for every micro-batch. `tokens[mb]` (first stage only) are the current token ids.
-        Returns the next token ids per micro-batch on the first stage (received from the last), else None.
+        """One decode step for every micro-batch (see `run`)."""
+        return self.run(tokens, 1)
 
-        Order: every stage walks the micro-batches in order; a stage's receive for micro-batch mb matches the
-        previous stage's send for mb, so the stages overlap on different micro-batches."""
-        nxt = [None] * self.n_micro
-        pending = []   # token ids on their way back to the first stage (non-blocking: the first stage is still
-                       # busy sending later micro-batches forward and receives them after its own loop)
-        for mb in range(self.n_micro):
-            x_in = v_first = None
-            if not self.first:
-                x_in, v_first = self.make_buffer(mb), self.make_buffer(mb)
-                dist.recv(x_in, src=self.s - 1, group=self.group)
-                dist.recv(v_first, src=self.s - 1, group=self.group)
-            if self.last:
-                out = self.stage_fn(mb, x_in, v_first) if not self.first else self.stage_fn(mb, tokens[mb], None)
-                if self.S > 1:
-                    pending.append((dist.isend(out, dst=0, group=self.group), out))
+    def run(self, tokens: Optional[List[torch.Tensor]], n_steps: int) -> Optional[List[torch.Tensor]]:
+        """`n_steps` decode steps for every micro-batch, greedy / sampled inside `stage_fn` of the last stage.
+        `tokens[mb]` (first stage only) are the current token ids. Returns the token ids that follow the last step per
+        micro-batch on the first stage (received from the last stage), else None.
+
+        Every stage walks the items (step, micro-batch) in the same order; a stage's receive for an item matches the
+        previous stage's send for it. The first stage starts step t + 1 of a micro-batch as soon as that micro-batch's
+        token ids of step t have come back, so with at least as many micro-batches as stages no stage idles between
+        steps: there is no barrier per step."""
+        sends = []      # (work handles, tensors kept alive) of everything sent in this call
+        nxt: List[Optional[torch.Tensor]] = [None] * self.n_micro
+        for t in range(n_steps):
+            for mb in range(self.n_micro):
+                x_in = v_first = None
+                if self.first:
+                    if t == 0:
+                        cur = tokens[mb]
+                    elif self.S > 1:
+                        cur = self.make_tokens(mb)
+                        dist.recv(cur, src=self._peer(self.S - 1), group=self.back_group)
+                    else:
+                        cur = nxt[mb]
                 else:
-                    nxt[mb] = out
-            else:
-                x_out, v_first = self.stage_fn(mb, tokens[mb] if self.first else x_in, v_first)
-                dist.send(x_out, dst=self.s + 1, group=self.group)
-                dist.send(v_first, dst=self.s + 1, group=self.group)
-        for req, _keep in pending:
-            req.wait()
+                    x_in, v_first = self.make_buffer(mb), self.make_buffer(mb)
+                    ops = [dist.P2POp(dist.irecv, x_in, self._peer(self.s - 1), self.group),
+                           dist.P2POp(dist.irecv, v_first, self._peer(self.s - 1), self.group)]
+                    for w in dist.batch_isend_irecv(ops):
+                        w.wait()
+                if self.last:
+                    out = self.stage_fn(mb, x_in, v_first) if not self.first else self.stage_fn(mb, cur, None)
+                    if self.S > 1:
+                        sends.append((dist.isend(out, dst=self._peer(0), group=self.back_group), out))
+                    else:
+                        nxt[mb] = out
+                else:
+                    x_out, v_first = self.stage_fn(mb, cur if self.first else x_in, v_first)
+                    ops = [dist.P2POp(dist.isend, x_out, self._peer(self.s + 1), self.group),
+                           dist.P2POp(dist.isend, v_first, self._peer(self.s + 1), self.group)]
+                    sends.append((dist.batch_isend_irecv(ops), (x_out, v_first)))
         if self.first and self.S > 1:
             for mb in range(self.n_micro):
-                t = self.make_tokens(mb)
-                dist.recv(t, src=self.S - 1, group=self.group)
-                nxt[mb] = t
+                tk = self.make_tokens(mb)
+                dist.recv(tk, src=self._peer(self.S - 1), group=self.back_group)
+                nxt[mb] = tk
+        for work, _keep in sends:
+            for w in (work if isinstance(work, list) else [work]):
+                w.wait()
         return nxt if self.first else None

@@ -436,6 +436,54 @@ class RWKV_x070:
         self._run(B, T, tok, state, logits, full_output)
         return logits, list(state)
 
+    # ---- sequences of unequal length: prefill one by one, decode together -----------------------------------
+    # The reference cannot batch prompts of different lengths (reference/rwkv7.py:116-117 asserts equal lengths) nor
+    # move a sequence in or out of a running batch. Every sequence owns an independent recurrent state, so both are
+    # state bookkeeping: prefill each prompt on its own (`forward`, T = its length), copy its 3 * n_layer state tensors
+    # into a slot of the batched state, and step the batch with `forward_batch`.
+    @staticmethod
+    def insert_state(batch_state: List[torch.Tensor], slot: int, seq_state: List[torch.Tensor]) -> None:
+        """Copy a single-sequence state (tensors without batch dimension) into slot `slot` of a batched state, in place."""
+        assert len(batch_state) == len(seq_state)
+        for dst, src in zip(batch_state, seq_state):
+            assert dst.shape[1:] == src.shape and dst.dtype == src.dtype, "state layouts differ"
+            dst[slot].copy_(src)
+
+    @staticmethod
+    def extract_state(batch_state: List[torch.Tensor], slot: int) -> List[torch.Tensor]:
+        """The state of the sequence in slot `slot` as a single-sequence state (a copy)."""
+        return [t[slot].clone() for t in batch_state]
+
+    @torch.no_grad()
+    def prefill_batch(self, prompts: List[List[int]], state: Optional[List[torch.Tensor]] = None,
+                      slots: Optional[List[int]] = None):
+        """Prefill prompts of any lengths and return (logits [len(prompts), V], batched state).
+
+        With `state` / `slots` given, the sequences are written into those slots of an existing batched state (a
+        finished sequence's slot is reused by a new prompt while the others keep decoding); otherwise a new batched
+        state with one slot per prompt is made. Prompts of equal length are prefilled together."""
+        assert type(prompts) is list and all(type(p) is list and len(p) > 0 for p in prompts)
+        if state is None:
+            state = self.new_state(len(prompts))
+            slots = list(range(len(prompts)))
+        assert slots is not None and len(slots) == len(prompts)
+        logits = torch.empty(len(prompts), self.vocab, dtype=DTYPE, device=self.device)
+        by_len: Dict[int, List[int]] = {}
+        for i, p in enumerate(prompts):
+            by_len.setdefault(len(p), []).append(i)
+        for T, idxs in by_len.items():
+            if len(idxs) == 1 or T == 1:
+                for i in idxs:
+                    lg, st = self.forward(prompts[i] if T > 1 else prompts[i][0], None)
+                    logits[i] = lg
+                    self.insert_state(state, slots[i], st)
+            else:
+                lg, st = self.forward_batch([prompts[i] for i in idxs], None)
+                logits[idxs] = lg
+                for j, i in enumerate(idxs):
+                    self.insert_state(state, slots[i], [t[j] for t in st])
+        return logits, state
+
     @torch.no_grad()
     def forward_stage(self, state: List[torch.Tensor], v_first: torch.Tensor, tokens: Optional[torch.Tensor] = None,
                       x_in: Optional[torch.Tensor] = None, x_out: Optional[torch.Tensor] = None):

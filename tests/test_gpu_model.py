@@ -262,3 +262,40 @@ def test_token_ids_are_range_checked_on_the_host_and_clamped_on_the_device():
     assert _lib.device_status() == 8
     assert torch.equal(one, want)
     assert _lib.device_status() == 0        # reading the status clears it
+
+
+def test_prompts_of_unequal_length_are_prefilled_into_slots_and_decoded_together():
+    """Baseline config 4's continuous batching on the tiny shapes: prompts of different lengths (the reference asserts
+    equal lengths, reference/rwkv7.py:116-117) are prefilled one by one into the slots of a batched state, decoded
+    together, and a finished sequence's slot is taken over by a new prompt; every sequence's logits equal those of the
+    same sequence run alone."""
+    model, args = model_for("tiny", "int8")
+    V = args.vocab_size
+    prompts = [seeded_tokens(V, n, seed=20 + n) for n in (5, 9, 5, 1, 13)]
+    logits, state = model.prefill_batch(prompts)
+    alone = []
+    for p in prompts:
+        lg, st = model.forward(p if len(p) > 1 else p[0], None)
+        alone.append((lg, st))
+    for i in range(len(prompts)):
+        assert rel_err(logits[i].float().cpu().numpy(), alone[i][0].float().cpu().numpy()) <= 1e-2
+    nxt = [int(l.argmax()) for l, _ in alone]
+    for step in range(3):
+        lb, state = model.forward_batch([[t] for t in nxt], state)
+        for i in range(len(prompts)):
+            la, st = model.forward(nxt[i], alone[i][1])
+            alone[i] = (la, st)
+            assert rel_err(lb[i].float().cpu().numpy(), la.float().cpu().numpy()) <= 1e-2, (step, i)
+        nxt = [int(l.argmax()) for l, _ in alone]
+    # sequence 1 is done: a new prompt takes its slot, the others go on
+    fresh = seeded_tokens(V, 7, seed=99)
+    lg_new, state = model.prefill_batch([fresh], state=state, slots=[1])
+    alone[1] = model.forward(fresh, None)
+    assert rel_err(lg_new[0].float().cpu().numpy(), alone[1][0].float().cpu().numpy()) <= 1e-2
+    nxt[1] = int(alone[1][0].argmax())
+    lb, state = model.forward_batch([[t] for t in nxt], state)
+    for i in range(len(prompts)):
+        la, _ = model.forward(nxt[i], alone[i][1])
+        assert rel_err(lb[i].float().cpu().numpy(), la.float().cpu().numpy()) <= 1e-2, i
+    one = model.extract_state(state, 3)
+    assert all(torch.equal(a, b[3]) for a, b in zip(one, state))
