@@ -82,15 +82,21 @@ def resource_usage(log_path: str = os.path.join(OUT_DIR, "build.log")) -> dict:
     The streaming kernels sit at their register cap (128 registers x 512 threads); a spill in them costs tens of
     percent of decode throughput, so the tests keep an eye on this."""
     import re
-    out, name = {}, None
+    out, name, props_of = {}, None, None
     for line in open(log_path):
         m = re.search(r"Compiling entry function '(\S+)'", line)
         if m:
-            name = m.group(1)
+            name = props_of = m.group(1)
+            continue
+        m = re.search(r"Function properties for (\S+)", line)
+        if m:
+            props_of = m.group(1)     # the entry itself, or a device function it calls (not inlined)
             continue
         m = re.search(r"(\d+) bytes stack frame, (\d+) bytes spill stores, (\d+) bytes spill loads", line)
         if m and name:
-            out.setdefault(name, {})["spill_bytes"] = int(m.group(2)) + int(m.group(3))
+            # spills of the entry and of the functions it calls add up
+            out.setdefault(name, {}).setdefault("spill_bytes", 0)
+            out[name]["spill_bytes"] += int(m.group(2)) + int(m.group(3))
             continue
         m = re.search(r"Used (\d+) registers", line)
         if m and name:

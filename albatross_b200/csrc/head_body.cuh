@@ -203,14 +203,26 @@ __device__ __forceinline__ void head_ups_compute(const HeadParams& p, int tid, u
     const int bounds[5] = {0, p.rw, p.rw + p.ra, p.rw + p.ra + p.rv, rtot};
 #pragma unroll
     for (int m = 0; m < 4; ++m) {
-        float s0 = 0.f, s1 = 0.f;
-        for (int j = bounds[m] + warp; j < bounds[m + 1]; j += 8) {
-            const float2 wv = __half22float2(reinterpret_cast<const __half2*>(w2s + (size_t)j * 64)[lane]);
-            s0 = fmaf(hvec[j], wv.x, s0);
-            s1 = fmaf(hvec[j], wv.y, s1);
+        // four rows per step on separate accumulators: the shared-memory loads of the next rows are in flight while
+        // the products of these are added (one accumulator and one row at a time, every step waits for its own loads)
+        float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+        int j = bounds[m] + warp;
+        for (; j + 24 < bounds[m + 1]; j += 32) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const float2 wv = __half22float2(reinterpret_cast<const __half2*>(w2s + (size_t)(j + 8 * u) * 64)[lane]);
+                const float hx = hvec[j + 8 * u];
+                s0[u] = fmaf(hx, wv.x, s0[u]);
+                s1[u] = fmaf(hx, wv.y, s1[u]);
+            }
         }
-        part[(warp * 4 + m) * 64 + 2 * lane] = s0;
-        part[(warp * 4 + m) * 64 + 2 * lane + 1] = s1;
+        for (; j < bounds[m + 1]; j += 8) {
+            const float2 wv = __half22float2(reinterpret_cast<const __half2*>(w2s + (size_t)j * 64)[lane]);
+            s0[0] = fmaf(hvec[j], wv.x, s0[0]);
+            s1[0] = fmaf(hvec[j], wv.y, s1[0]);
+        }
+        part[(warp * 4 + m) * 64 + 2 * lane] = (s0[0] + s0[1]) + (s0[2] + s0[3]);
+        part[(warp * 4 + m) * 64 + 2 * lane + 1] = (s1[0] + s1[1]) + (s1[2] + s1[3]);
     }
     sync();
     {
