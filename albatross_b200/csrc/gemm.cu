@@ -42,7 +42,8 @@ namespace {
 #endif
 constexpr int G_NG = G_NG_;      // producer groups
 constexpr int G_PROD = 128 * G_NG;
-constexpr int GT = G_PROD + 64;  // threads per block
+constexpr int GT = G_PROD + 128; // threads per block: producers + a warpgroup holding the TMA warp, the MMA warp and two idle warps
+                                 // (register re-allocation works on whole, aligned warpgroups)
 #ifndef G_A_TMEM_
 #define G_A_TMEM_ 1
 #endif
@@ -57,6 +58,7 @@ constexpr int G_BK = 64;         // inputs per k-step (128 bytes of fp16 = one s
 constexpr int G_A_BYTES = G_BM * G_BK * 2;
 constexpr int G_RAW_BYTES = 56 * 1024;   // rings of raw (still quantised) weight k-steps filled by cp.async
 constexpr int G_RAW_GROUP = (G_RAW_BYTES / G_NG) & ~1023;   // one ring per producer group
+constexpr int G_REGS_PROD = 136, G_REGS_REST = 96;   // (136 - 128) * 384 producer threads <= (128 - 96) * 128 others
 constexpr int G_MAX_OPS = 8;
 constexpr int G_COUNTERS = 4096;         // split-K arrival counters at the start of the scratch area
 
@@ -317,6 +319,10 @@ __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ 
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_s;
+    // Registers go where the work is: the producers' de-quantisation needs more than an even share, the two single-thread
+    // warps and the idle ones far less. (Whole warpgroups execute these: warps 0-3, 4-7, 8-11 / 12-15.)
+    if (warp < 4 * G_NG) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(G_REGS_PROD));
+    else asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(G_REGS_REST));
     // Under programmatic stream serialisation the next grid may start now; like this one it begins with its weight
     // stream (weights are never written) and waits for its predecessor before it touches activations or outputs.
     if (tid == 0) pdl_launch_dependents();
@@ -628,7 +634,7 @@ __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ 
                     tma_load_2d(smB + s * b_bytes + r * 128, map, kstep_of(ks) * G_BK, n0 + r, &full[s]);
             }
         }
-    } else {
+    } else if (warp == 4 * G_NG + 1) {
         // ===== MMA issue =====
         if (lane == 0) {
             // One thread feeds the tensor core, so its instruction stream is kept short: descriptors are built

@@ -430,11 +430,43 @@ class RWKV_x070:
         self._check_state(state, B)
         self._check_ids(idxs)
         tok = torch.tensor(idxs, dtype=torch.int32)
-        tok = torch.where(tok < 0, tok + self.vocab, tok).to(self.device)
+        tok = torch.where(tok < 0, tok + self.vocab, tok)
+        if T == 1 and B > 1 and self.use_graph:
+            return self._forward_batch_graph(B, tok, state)
+        tok = tok.to(self.device)
         shape = (B, T, self.vocab) if full_output else (B, self.vocab)
         logits = torch.empty(shape, dtype=DTYPE, device=self.device)
         self._run(B, T, tok, state, logits, full_output)
         return logits, list(state)
+
+    def _forward_batch_graph(self, B: int, tok_host: torch.Tensor, state: List[torch.Tensor]):
+        """One batched decode step (T = 1) replayed from a CUDA graph: the ~260 launches of the step, and the tensor
+        maps the products encode on the host for every launch, are recorded once per (batch, state tensors)."""
+        key = (B,) + tuple(t.data_ptr() for t in state)
+        entry = self._graphs.get(key)
+        if entry is None:
+            tok_dev = torch.zeros(B, dtype=torch.int32, device=self.device)
+            logits_buf = torch.empty(B, self.vocab, dtype=DTYPE, device=self.device)
+            pinned = torch.empty(B, dtype=torch.int32).pin_memory()
+            scratch = [t.clone() for t in state]         # warm-up outside the capture (lazy one-time set-up in the library)
+            self._run(B, 1, tok_dev, scratch, logits_buf, False)
+            torch.cuda.synchronize()
+            del scratch
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                self._run(B, 1, tok_dev, state, logits_buf, False)
+            if len(self._graphs) >= 4:
+                self._graphs.pop(next(iter(self._graphs)))
+            # the entry keeps the workspace the launches were recorded with alive (the model may replace its own
+            # reference when another shape comes along)
+            entry = self._graphs[key] = (graph, tok_dev, logits_buf, pinned, torch.cuda.Event(), self._ws[(B, 1)])
+        graph, tok_dev, logits_buf, pinned, ev, _ws = entry
+        ev.synchronize()                                  # the copy that read the pinned ids last step has completed
+        pinned.copy_(tok_host.view(-1))
+        tok_dev.copy_(pinned, non_blocking=True)
+        ev.record()
+        graph.replay()
+        return logits_buf.clone(), list(state)
 
     # ---- sequences of unequal length: prefill one by one, decode together -----------------------------------
     # The reference cannot batch prompts of different lengths (reference/rwkv7.py:116-117 asserts equal lengths) nor

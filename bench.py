@@ -258,6 +258,10 @@ def run_ours(a, rank, world, dev, workload=None, batch=None):
         model.forward(0, state)                     # captures the graph for this state
         graph, tok_buf, logits_buf = model._graphs[tuple(t.data_ptr() for t in state)]
         step_fn = lambda i: (tok_buf.copy_(tok_dev[i]), graph.replay())
+    elif model.use_graph:
+        model.forward_batch([[0]] * B, state)       # records the graph of one batched step for this state
+        graph, tok_buf, logits_buf = model._graphs[(B,) + tuple(t.data_ptr() for t in state)][:3]
+        step_fn = lambda i: (tok_buf.copy_(tok_dev[i]), graph.replay())
     else:
         cur = torch.zeros(B, dtype=torch.int32, device=f"cuda:{dev}")
         logits_buf = torch.empty(B, V, dtype=torch.float16, device=f"cuda:{dev}")
