@@ -10,7 +10,9 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "_C", "libalbatross_b200.so")
+# AB_BOUNDS_CHECK=1 selects the range-checking build of the same library (python -m albatross_b200.build --bounds-check)
+LIB_PATH = os.path.join(_HERE, "_C", "libalbatross_b200_checked.so" if os.environ.get("AB_BOUNDS_CHECK") == "1"
+                        else "libalbatross_b200.so")
 
 FMT_F16, FMT_I8, FMT_FP4 = 0, 1, 2
 EPI_NONE, EPI_TANH, EPI_SIGMOID, EPI_RELU2, EPI_RESID = 0, 1, 2, 3, 4

@@ -15,6 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT_DIR = os.path.join(HERE, "_C")
 LIB = os.path.join(OUT_DIR, "libalbatross_b200.so")
+LIB_CHECKED = os.path.join(OUT_DIR, "libalbatross_b200_checked.so")   # -DAB_BOUNDS_CHECK build (see csrc/common.cuh)
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-shared", "-Xptxas", "-v"]
 
@@ -34,21 +35,24 @@ def needs_build() -> bool:
     return any(os.path.getmtime(s) > t for s in _sources())
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    if not force and not needs_build():
-        return LIB
+def build(force: bool = False, verbose: bool = False, bounds_check: bool = False) -> str:
+    """bounds_check: the debugging variant whose kernels range-check their computed indices and record a status bit
+    instead of making an out-of-range access (loaded by `_lib` when AB_BOUNDS_CHECK=1 is in the environment)."""
+    lib = LIB_CHECKED if bounds_check else LIB
+    if not force and os.path.exists(lib) and all(os.path.getmtime(s) <= os.path.getmtime(lib) for s in _sources()):
+        return lib
     os.makedirs(OUT_DIR, exist_ok=True)
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
-    cmd = [nvcc] + NVCC_FLAGS + [os.path.join(CSRC, "albatross_b200.cu"), "-o", LIB]
+    cmd = [nvcc] + NVCC_FLAGS + (["-DAB_BOUNDS_CHECK"] if bounds_check else []) + [os.path.join(CSRC, "albatross_b200.cu"), "-o", lib]
     res = subprocess.run(cmd, capture_output=True, text=True)
-    log = os.path.join(OUT_DIR, "build.log")
+    log = os.path.join(OUT_DIR, "build_checked.log" if bounds_check else "build.log")
     with open(log, "w") as f:
         f.write(" ".join(cmd) + "\n" + res.stdout + res.stderr)
     if verbose or res.returncode != 0:
         sys.stderr.write(res.stdout + res.stderr)
     if res.returncode != 0:
         raise RuntimeError(f"nvcc failed (exit {res.returncode}); see {log}")
-    return LIB
+    return lib
 
 
 TORCH_OP_LIB = os.path.join(OUT_DIR, "librwkv7_state_fwd_fp16.so")
@@ -106,4 +110,6 @@ def resource_usage(log_path: str = os.path.join(OUT_DIR, "build.log")) -> dict:
 
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    if "--bounds-check" in sys.argv:
+        print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, bounds_check=True))
     print(build_torch_op(force="--force" in sys.argv))

@@ -76,7 +76,18 @@ static __device__ unsigned int g_device_status = 0;
 constexpr unsigned int DEV_WAIT_GEMV = 1u;
 constexpr unsigned int DEV_WAIT_GEMM = 2u;
 constexpr unsigned int DEV_WAIT_HEAD = 4u;
+constexpr unsigned int DEV_BOUNDS = 16u;     // bounds-checked build only: a computed index fell outside its array (the access was skipped)
 constexpr unsigned int DEV_BAD_TOKEN = 8u;   // a token id outside [0, vocab) reached a kernel (it was clamped, not followed)
+
+// Bounds-checked build (-DAB_BOUNDS_CHECK, `python -m albatross_b200.build --bounds-check`): the stand-in for a memory
+// checker where none can be run. AB_BC(cond) is `true` in the normal build and costs nothing; in the checked build it
+// evaluates the range condition of the access it guards, and when the condition fails it records DEV_BOUNDS in the status
+// word and yields false, so that the access is skipped instead of made: `if (AB_BC(i < n)) a[i] = v;`.
+#ifdef AB_BOUNDS_CHECK
+#define AB_BC(cond) ((cond) ? true : (atomicOr(&ab::g_device_status, ab::DEV_BOUNDS), false))
+#else
+#define AB_BC(cond) true
+#endif
 
 // ---------------------------------------------------------------------------------------------
 // PTX wrappers

@@ -405,7 +405,8 @@ __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ 
                     const int k0 = ks_abs * G_BK;
 #pragma unroll
                     for (int q = 0; q < nq; ++q)
-                        cp_async_16(slot + q * 2048 + r_local * 16, wrow + (size_t)ks_abs * rb + q * 16, row_ok && k0 + q * epc < K);
+                        cp_async_16(slot + q * 2048 + r_local * 16, wrow + (size_t)ks_abs * rb + q * 16,
+                                    row_ok && k0 + q * epc < K && AB_BC(ks_abs >= 0 && (size_t)ks_abs * rb + q * 16 + 16 <= (size_t)K * rb / 64));
                     if (F == FMT_FP4) cp_async_4(slot + nq * 2048 + r_local * 4, srow + (size_t)ks_abs * 4, row_ok && k0 < K);
                 };
 #pragma unroll
@@ -464,7 +465,7 @@ __global__ void __launch_bounds__(GT, 1) gemm_tc_kernel(const __grid_constant__ 
             } else {
 #pragma unroll
                 for (int i = 0; i < 32; ++i)
-                    if (c0 + i < n_valid) yp[(size_t)i * n_out] = __float2half_rn(apply_epi(epi, rh(v[i] * scale)));
+                    if (c0 + i < n_valid && AB_BC(row < n_out && n0 + c0 + i < g.rows)) yp[(size_t)i * n_out] = __float2half_rn(apply_epi(epi, rh(v[i] * scale)));
             }
         };
 

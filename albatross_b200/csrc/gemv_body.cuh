@@ -383,7 +383,8 @@ __device__ __forceinline__ void load_item(const Item& t, int slice, int lane, It
         const unsigned char* pr = p0 + (size_t)r * t.row_bytes;
 #pragma unroll
         for (int u = 0; u < GEMV_SWEEPS; ++u) {
-            if (FULL || (o + u * 512 < t.row_bytes && r < t.rows)) b.w[u][r] = ld_w16(pr + u * 512);
+            if ((FULL || (o + u * 512 < t.row_bytes && r < t.rows)) && AB_BC(o + u * 512 + 16 <= t.row_bytes && r < t.rows))
+                b.w[u][r] = ld_w16(pr + u * 512);
             else b.w[u][r] = make_uint4(0, 0, 0, 0);
         }
     }
@@ -600,8 +601,10 @@ __device__ __forceinline__ void prep_x_block(const GemvSeg& sg, const GemvSmem& 
                 __half2 h[8];
 #pragma unroll
                 for (int e = 0; e < 8; ++e) h[e] = __floats2half2_rn(v[2 * e], v[2 * e + 1]);
-                reinterpret_cast<uint4*>(xq)[c * 2] = *reinterpret_cast<uint4*>(&h[0]);
-                reinterpret_cast<uint4*>(xq)[c * 2 + 1] = *reinterpret_cast<uint4*>(&h[4]);
+                if (AB_BC(c * 32 + 32 <= 2 * Kp)) {
+                    reinterpret_cast<uint4*>(xq)[c * 2] = *reinterpret_cast<uint4*>(&h[0]);
+                    reinterpret_cast<uint4*>(xq)[c * 2 + 1] = *reinterpret_cast<uint4*>(&h[4]);
+                }
             }
         } else {
             float amax = 0.f;
@@ -627,8 +630,10 @@ __device__ __forceinline__ void prep_x_block(const GemvSeg& sg, const GemvSmem& 
                 hw[q] = hh;
                 lw[q] = ll;
             }
-            reinterpret_cast<uint4*>(xq)[c] = make_uint4(hw[0], hw[1], hw[2], hw[3]);
-            reinterpret_cast<uint4*>(xq + Kp)[c] = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+            if (AB_BC(c * 16 + 16 <= Kp)) {
+                reinterpret_cast<uint4*>(xq)[c] = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+                reinterpret_cast<uint4*>(xq + Kp)[c] = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+            }
             if (lane == 0) sx[c0 / 32] = amax / 32639.0f;
         }
     }
@@ -878,7 +883,7 @@ __device__ __forceinline__ void gemv_consume(const GemvParams& p, const BlockPla
 #pragma unroll
                 for (int r = 0; r < GEMV_ROWS; ++r)
                     if (r == lane) val = acc[r];
-                m.part[pidx + lane * npc] = val;
+                if (AB_BC(pidx + lane * npc >= 0 && pidx + lane * npc < GEMV_PART_FLOATS)) m.part[pidx + lane * npc] = val;
             }
             if (!more) break;
         }
@@ -900,7 +905,8 @@ __device__ __forceinline__ void gemv_consume(const GemvParams& p, const BlockPla
         const SegPlan& q = bp.sp[e_seg];
         const int rl = tid - q.row_base;
         float val = 0.f;
-        for (int sl = 0; sl < q.npc; ++sl) val += m.part[q.part_base + rl * q.npc + sl];
+        for (int sl = 0; sl < q.npc; ++sl)
+            if (AB_BC(q.part_base + rl * q.npc + sl < GEMV_PART_FLOATS)) val += m.part[q.part_base + rl * q.npc + sl];
         float o = rh(val * e_scale);
         switch (sg.epi) {
             case EPI_TANH: o = tanhf(o); break;
@@ -909,8 +915,10 @@ __device__ __forceinline__ void gemv_consume(const GemvParams& p, const BlockPla
             case EPI_RESID: o = e_resid + o; break;
             default: break;
         }
-        if (sg.tag_out) st_tagged(sg.out, e_row, o, tag_of(epoch, sg.tag_out));
-        else sg.out[e_row] = __float2half_rn(o);
+        if (AB_BC(e_row >= 0 && e_row < sg.n_rows)) {
+            if (sg.tag_out) st_tagged(sg.out, e_row, o, tag_of(epoch, sg.tag_out));
+            else sg.out[e_row] = __float2half_rn(o);
+        }
     }
 }
 

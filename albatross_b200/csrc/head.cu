@@ -172,6 +172,7 @@ __global__ void __launch_bounds__(HB_THREADS, HB_BLOCKS) head_batch_kernel(const
         auto load_state_of = [&](int n) {
             const int s = n % HB_STAGES;
             mbar_expect_tx(&full[s], HB_STATE_BYTES);
+            (void)AB_BC(item_of(n) >= 0 && item_of(n) < n_items);   // checked build: recorded; the copy itself is not skipped (its barrier expects it)
             bulk_g2s(dsm + s * HB_STATE_BYTES, p.state + (size_t)item_of(n) * 4096, HB_STATE_BYTES, &full[s]);
         };
         // The state is requested BEFORE the wait for the preceding grid. That is safe because its last writer is this

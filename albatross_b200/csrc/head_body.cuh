@@ -92,6 +92,7 @@ struct StateRow {
 };
 
 __device__ __forceinline__ void load_state(StateRow& st, const float* base, int i, int q) {
+    if (!AB_BC(i >= 0 && i < 64 && q >= 0 && q < 4)) return;
     const float4* src = reinterpret_cast<const float4*>(base + i * 64 + q * 16);
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
@@ -100,6 +101,7 @@ __device__ __forceinline__ void load_state(StateRow& st, const float* base, int 
     }
 }
 __device__ __forceinline__ void store_state(const StateRow& st, float* base, int i, int q) {
+    if (!AB_BC(i >= 0 && i < 64 && q >= 0 && q < 4)) return;
     float4* dst = reinterpret_cast<float4*>(base + i * 64 + q * 16);
 #pragma unroll
     for (int e = 0; e < 4; ++e) dst[e] = make_float4(st.s[4 * e], st.s[4 * e + 1], st.s[4 * e + 2], st.s[4 * e + 3]);

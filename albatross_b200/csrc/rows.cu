@@ -32,7 +32,8 @@ __global__ void __launch_bounds__(RT) gather_rows_kernel(const __half* __restric
     }
     const uint4* src = reinterpret_cast<const uint4*>(table + (size_t)tok * D);
     uint4* dst = reinterpret_cast<uint4*>(out + m * D);
-    for (int i = threadIdx.x; i < D / 8; i += RT) dst[i] = src[i];
+    for (int i = threadIdx.x; i < D / 8; i += RT)
+        if (AB_BC(tok >= 0 && tok < vocab && (i + 1) * 8 <= D)) dst[i] = src[i];
 }
 
 // out[m] = LN(x[src_row(m)]) with src_row = m * stride + offset (stride/offset pick last tokens).

@@ -369,15 +369,15 @@ def run_pipeline(a, rank, world, dev):
     def sync_all():
         torch.cuda.synchronize(); td.barrier(); torch.cuda.synchronize()
 
-    for _ in range(a.warmup):
-        tokens = dec.step(tokens)
+    tokens = dec.run(tokens, a.warmup)
     sync_all()
     sampler = ClockSampler(dev)
     sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(a.steps):
-        tokens = dec.step(tokens)
+    # all steps in one call: a micro-batch starts its next step as soon as its token ids are back on the first stage,
+    # so with at least as many micro-batches as stages the stages do not idle between steps
+    tokens = dec.run(tokens, a.steps)
     e1.record()
     sync_all()
     clocks = sampler.stop()
