@@ -85,7 +85,7 @@ class PackCache:
             self._dirty = True              # another layout or format: nothing is reusable
             return
         self._entries = meta["entries"]
-        self._map = np.memmap(self.path, dtype=np.uint8, mode="r")
+        self._map = np.memmap(self.path, dtype=np.uint8, mode="c")   # private copy-on-write mapping: never written, but torch wants a writable buffer
 
     # ------------------------------------------------------------------------------------------
     def get(self, name: str, source: torch.Tensor, device) -> Optional[PackedMatrix]:

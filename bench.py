@@ -597,7 +597,11 @@ def main():
         if rank == 0:
             gv = run_gemv(a, local, workload="gemv_int8", n=4096, k=4096)
             out["also"]["gemv_int8_4096x4096"] = {k_: gv[k_] for k_ in ("metric", "value", "unit", "ms_per_step", "config", "roofline")}
-            out["gpu_launches"] += second["gpu_launches"] + gv["gpu_launches"]
+            # ... and the same kernel on the largest matrix of the model (the vocabulary head), where a launch is long
+            # enough to show the streaming rate itself
+            gh = run_gemv(a, local, workload="gemv_int8", n=65536, k=4096)
+            out["also"]["gemv_int8_65536x4096"] = {k_: gh[k_] for k_ in ("metric", "value", "unit", "ms_per_step", "config", "roofline")}
+            out["gpu_launches"] += second["gpu_launches"] + gv["gpu_launches"] + gh["gpu_launches"]
     if rank == 0:
         if world == 1 and not a.no_cpu_baseline and not a.workload.startswith("pipeline_"):
             out["cpu_baseline"] = run_cpu(a)
