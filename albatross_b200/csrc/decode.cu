@@ -153,28 +153,12 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) decode_kernel(const DecodePro
         if (prog->timeline && bid == prog->timeline_block && tid == 0) prog->timeline[2 * i] = global_ns();
         if (ph.type == PHASE_GEMV) {
             const int j = ph.next_gemv;
-            // one thread plans the next matrix-vector phase while the others run this prologue
-            if (tid == 32 && j >= 0) {
-                // the head of this block's share of the next phase starts moving HBM -> L2 now
-                const GemvParams& q = phs[j & 3].g;
-                const BlockPlan& np_ = plans[j & 3];
-                int budget = prog->l2_prefetch_bytes;
-                for (int s = 0; s < q.nseg && budget > 0; ++s) {
-                    const SegPlan& sp = np_.sp[s];
-                    if (sp.n_groups <= 0) continue;
-                    const int row0 = sp.lo * GEMV_ROWS;
-                    const int rows = min(sp.n_groups * GEMV_ROWS, q.seg[s].n_rows - row0);
-                    int bytes = min(rows * sp.row_bytes, budget) & ~15;
-                    if (bytes > 0) prefetch_l2((const unsigned char*)q.seg[s].w + (size_t)row0 * sp.row_bytes, (uint32_t)bytes);
-                    budget -= bytes;
-                }
-            }
             const bool pre = j >= 0 && prog->smem_prefetch;
             gemv_consume(ph.g, plans[i & 3], m, tid, bid, i, pre_phase, pre ? &phs[j & 3].g : nullptr,
                          pre ? &plans[j & 3] : nullptr, j,
                          (prog->timeline && bid == prog->timeline_block) ? prog->timeline + 2 * n_phases + 4 * i : nullptr,
                          // the first-slice prefetch uses the area that the phase before a paired head phase stages into
-                         prog->early_slice != 0 && !(i + 1 < n_phases && phs[(i + 1) & 3].type == PHASE_HEAD && phs[(i + 1) & 3].h.pair_mode),
+                         (i + 1 < n_phases && phs[(i + 1) & 3].type == PHASE_HEAD && phs[(i + 1) & 3].h.pair_mode) ? 0 : prog->early_slice,
                          [&]() {
                              if (ph.no_barrier == 2 && tid < HT && bid < 2 * phs[(i + 1) & 3].h.H && (bid & 1) == 0) {
                                  // "fused heads": this block runs head bid / 2 right after the phase. Its slices of the
@@ -189,7 +173,12 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) decode_kernel(const DecodePro
                                  asm volatile("cp.async.commit_group;" ::: "memory");
                                  if (tid < 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(nh.state + (size_t)h * 4096 + tid * 32));
                              }
-                         }, epoch);
+                         }, epoch, prog->l2_prefetch_bytes + (prog->early_slice ? GEMV_WARPS * GEMV_ROWS * GEMV_SLICE_BYTES : 0), prog->l2_prefetch2_bytes);
+            // The memory system idles from the moment the blocks run out of weights until the next phase's inputs have
+            // crossed the chip and been prepared. One thread asks for the head of this block's share of the next
+            // matrix-vector phase to be moved HBM -> L2 in that window (no data returns to the SM: the request does not
+            // sit in front of the loads that wait for the inputs).
+            if (tid == 32 && j >= 0 && prog->l2_prefetch_bytes > 0) prefetch_share(phs[j & 3].g, plans[j & 3], 0, prog->l2_prefetch_bytes);
         } else {
             head_phase(ph.h, bid, nb, tid, smem, m.pref, m.xn, hsh, epoch,
                        (prog->timeline && bid == prog->timeline_block && tid == 0) ? prog->timeline + 2 * n_phases + 4 * i : nullptr);

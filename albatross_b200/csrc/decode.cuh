@@ -27,7 +27,8 @@ struct DecodeProgram {
     int smem_prefetch;       // warps start the copy of their first slice of the next phase before the barrier
     int early_slice;         // warps request the first slice of their first item right behind the input loads
     int barrier_prefetch;    // ... or while the block waits at the grid barrier before that phase
-    int pad1[3];
+    int l2_prefetch2_bytes;  // ... and how much more once the phase's own inputs have arrived (dataflow mode)
+    int pad1[2];
     const BlockPlan* plans;  // [n_phases][n_blocks], computed on the host (device copy follows the phases)
     unsigned* barrier;       // points at barrier_word of the device copy
     unsigned long long* timeline;  // optional: block 0 stores %globaltimer at [2i] phase start, [2i+1] phase end

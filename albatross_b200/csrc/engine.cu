@@ -60,7 +60,11 @@ struct ab_model {
     int debug_sync = 0;  // synchronise after every launch and name the one that failed
     int timeline = 0;    // persistent decode kernel records per-phase timestamps
     int timeline_block = 0;   // ... as seen by this block
-    int l2_prefetch_kb = 0;   // persistent decode kernel: L2 prefetch of the next phase, per block
+    // persistent decode kernel, per block: KB of its share of the next matrix-vector phase asked into L2 when it has
+    // streamed its last weights of this one, and KB more once the next phase's inputs have arrived (-1: 64 and 128 in
+    // dataflow mode, else 0). More than that gets in the way of the blocks that are still streaming.
+    int l2_prefetch_kb = -1;
+    int l2_prefetch2_kb = -1;
     int smem_prefetch = 0;
     int early_slice = -1;  // first weight slice requested ahead of the input vector: -1 = in dataflow mode only (there it travels
                            // while the block waits for its input anyway; with barriers it delays the input loads and is slower)
@@ -252,7 +256,9 @@ int build_decode_program(ab_model* m, const int32_t* token, void* const* state, 
     prog->Kn = D;
     prog->xq_bytes = 0;
     prog->first_gemv = 0;
-    prog->l2_prefetch_bytes = m->l2_prefetch_kb * 1024;
+    const bool dataflow_opts = m->fuse_heads && !m->merge_ups;
+    prog->l2_prefetch_bytes = (m->l2_prefetch_kb < 0 ? (dataflow_opts ? 64 : 0) : m->l2_prefetch_kb) * 1024;
+    prog->l2_prefetch2_bytes = (m->l2_prefetch2_kb < 0 ? (dataflow_opts ? 128 : 0) : m->l2_prefetch2_kb) * 1024;
     // the in-phase adapter up-projection stages its matrices where the prefetched slices would wait: one or the other
     const bool stage_area_taken = m->merge_ups || m->fuse_heads;
     prog->smem_prefetch = stage_area_taken ? 0 : m->smem_prefetch;
@@ -633,13 +639,14 @@ int ab_model_set_option(ab_model* m, const char* name, int value) {
     else if (!strcmp(name, "debug_sync")) m->debug_sync = value != 0;
     else if (!strcmp(name, "timeline")) m->timeline = value != 0;
     else if (!strcmp(name, "timeline_block")) m->timeline_block = value < 0 ? 0 : value;
-    else if (!strcmp(name, "l2_prefetch_kb")) m->l2_prefetch_kb = value < 0 ? 0 : value;
+    else if (!strcmp(name, "l2_prefetch_kb")) m->l2_prefetch_kb = value < 0 ? -1 : value;
+    else if (!strcmp(name, "l2_prefetch2_kb")) m->l2_prefetch2_kb = value < 0 ? -1 : value;
     else if (!strcmp(name, "smem_prefetch")) m->smem_prefetch = value != 0;
     else if (!strcmp(name, "merge_ups")) m->merge_ups = value != 0;
     else if (!strcmp(name, "fuse_heads")) m->fuse_heads = value != 0;
     else if (!strcmp(name, "pair_split")) m->pair_split = value;
     else if (!strcmp(name, "stage_gemv")) m->stage_gemv = value != 0;
-    else if (!strcmp(name, "early_slice")) m->early_slice = value < 0 ? -1 : (value != 0);
+    else if (!strcmp(name, "early_slice")) m->early_slice = value < 0 ? -1 : (value > 2 ? 2 : value);
     else if (!strcmp(name, "barrier_prefetch")) m->barrier_prefetch = value != 0;
     else if (!strcmp(name, "layer_offset")) { AB_CHECK_ARG(value >= 0, "layer_offset must be >= 0"); m->layer_offset = value; }
     else { set_error("unknown option %s", name); return ERR_BAD_ARG; }

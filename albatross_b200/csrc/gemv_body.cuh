@@ -336,6 +336,25 @@ __host__ inline void compute_plan_heads(const GemvParams& p, int bid, int nb, in
     bp.valid = 1;
 }
 
+// Ask for bytes [skip, skip + bytes) of a block's share of a launch (its rows of each segment, in plan order: the order
+// its warps consume them in) to be moved HBM -> L2. Called by one thread.
+__device__ __forceinline__ void prefetch_share(const GemvParams& q, const BlockPlan& bp, int skip, int bytes) {
+    for (int s = 0; s < q.nseg && bytes > 0; ++s) {
+        const SegPlan& sp = bp.sp[s];
+        if (sp.n_groups <= 0) continue;
+        const int row0 = sp.lo * GEMV_ROWS;
+        const int total = min(sp.n_groups * GEMV_ROWS, q.seg[s].n_rows - row0) * sp.row_bytes;
+        if (skip >= total) {
+            skip -= total;
+            continue;
+        }
+        const int n = min(total - skip, bytes) & ~15;
+        if (n > 0) prefetch_l2((const unsigned char*)q.seg[s].w + (size_t)row0 * sp.row_bytes + skip, (uint32_t)n);
+        bytes -= n;
+        skip = 0;
+    }
+}
+
 // ---- work items ------------------------------------------------------------------------------------
 // In bytes every format looks the same: an item is GEMV_ROWS rows x 1024 bytes of each row starting at byte
 // `sb`; lane l reads bytes [sb + u*512 + l*16, +16) of each row for u = 0, 1.
@@ -654,7 +673,8 @@ template <class AfterPrep = NoHook>
 __device__ __forceinline__ void gemv_consume(const GemvParams& p, const BlockPlan& bp, const GemvSmem& m, int tid,
                                              int bid, int phase_idx, int& pre_phase, const GemvParams* np,
                                              const BlockPlan* nbp, int next_phase_idx, unsigned long long* tl = nullptr,
-                                             bool early = false, AfterPrep after_prep = AfterPrep(), uint32_t epoch = 0) {
+                                             int early = 0, AfterPrep after_prep = AfterPrep(), uint32_t epoch = 0,
+                                             int pf_skip = 0, int pf_bytes = 0) {
     auto stamp = [&](int k) {
         if (tl && tid == 0) {
             unsigned long long t;
@@ -677,7 +697,7 @@ __device__ __forceinline__ void gemv_consume(const GemvParams& p, const BlockPla
     };
 
     // dataflow mode: the input is waited for below (tagged words); the first weight slice travels in the meantime
-    if (epoch) issue_early();
+    if (epoch && early == 1) issue_early();
 
     if (p.copy_src && bid == 0)
         for (int i = tid; i < p.copy_n / 8; i += NT_CONS)
@@ -823,6 +843,9 @@ __device__ __forceinline__ void gemv_consume(const GemvParams& p, const BlockPla
         cons_sync();
     }
     stamp(0);
+    // every producer of the inputs is done, so no block streams weights any more: the memory system idles while the
+    // inputs are prepared. More of this block's share moves into L2 in that time.
+    if (pf_bytes > 0 && tid == 32) prefetch_share(p, bp, pf_skip, pf_bytes);
     issue_early();
 
     // ---- prepared inputs of every segment this block touches

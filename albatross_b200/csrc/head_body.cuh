@@ -121,7 +121,7 @@ __host__ __device__ inline size_t head_ups_smem(int rtot) {
 // Batch-1 adapter up-projections of head h, part 1: start copying this head's 64-channel slices of the four
 // up-projection matrices ([rank, D] each) into scratch shared memory. They are weights: no dependency on activations.
 __device__ __forceinline__ void head_ups_stage(const HeadParams& p, int h, int tid, unsigned char* dsm) {
-    __half* w2s = reinterpret_cast<__half*>(dsm);   // [rtot][64]
+    __half* w2s = reinterpret_cast<__half*>(dsm);   // [rtot][64], swizzled
     const int rtot = p.rw + p.ra + p.rv + p.rg;
     for (int pc = tid; pc < rtot * 8; pc += HT) {
         int row = pc >> 3;
@@ -131,7 +131,9 @@ __device__ __forceinline__ void head_ups_stage(const HeadParams& p, int h, int t
         else if ((row -= p.rw) < p.ra) m = p.a2;
         else if ((row -= p.ra) < p.rv) m = p.v2;
         else { row -= p.rv; m = p.g2; }
-        head_cp_async16(w2s + (size_t)(pc >> 3) * 64 + seg8 * 8, m + (size_t)row * p.D + h * 64 + seg8 * 8);
+        // 16-byte pieces of a row are stored at piece ^ (row & 7): the 8x8 tiles the tensor-core loads read (eight
+        // consecutive rows, the same piece) then touch eight different bank groups
+        head_cp_async16(w2s + (size_t)(pc >> 3) * 64 + (seg8 ^ ((pc >> 3) & 7)) * 8, m + (size_t)row * p.D + h * 64 + seg8 * 8);
     }
 }
 // The head's eight per-channel parameter vectors (64 fp16 each) behind the staged up-projection slices: [8][64] fp16.
@@ -156,8 +158,8 @@ __device__ __forceinline__ void head_ups_compute(const HeadParams& p, int tid, u
     const int rtot = p.rw + p.ra + p.rv + p.rg;
     const int lane = tid & 31, warp = tid >> 5;
     const __half* w2s = reinterpret_cast<const __half*>(dsm);
-    float* hvec = reinterpret_cast<float*>(dsm + (size_t)rtot * 128);   // [rtot]
-    float* part = hvec + ((rtot + 3) & ~3);                             // [8][4][64]
+    unsigned short* hv16 = reinterpret_cast<unsigned short*>(dsm + (size_t)rtot * 128);   // [rtot] fp16 bits
+    float* part = reinterpret_cast<float*>(hv16) + ((rtot + 3) & ~3);                    // [8][4][64]
     // all of this thread's entries are requested before the first one is looked at (each is a tagged word that may
     // have to be waited for: one after the other they would cost a memory round trip each)
     constexpr int HV_MAX = 4;   // entries per thread: adapter ranks up to 4 * 256 in total (longer lists loop)
@@ -174,7 +176,7 @@ __device__ __forceinline__ void head_ups_compute(const HeadParams& p, int tid, u
         if (!tg.on) {
 #pragma unroll
             for (int e = 0; e < HV_MAX; ++e)
-                if (j0 + e * HT < rtot) hvec[j0 + e * HT] = lda(addr(j0 + e * HT));
+                if (j0 + e * HT < rtot) hv16[j0 + e * HT] = __half_as_ushort(__ldcg(addr(j0 + e * HT)));
             continue;
         }
         uint32_t w[HV_MAX], it = 0;
@@ -195,36 +197,61 @@ __device__ __forceinline__ void head_ups_compute(const HeadParams& p, int tid, u
         }
 #pragma unroll
         for (int e = 0; e < HV_MAX; ++e)
-            if (j0 + e * HT < rtot) hvec[j0 + e * HT] = __half2float(__ushort_as_half((unsigned short)(w[e] & 0xffffu)));
+            if (j0 + e * HT < rtot) hv16[j0 + e * HT] = (unsigned short)(w[e] & 0xffffu);
     }
     if (tl) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tl[0]));   // this thread's hidden-vector entries are in
     head_cp_async_wait_all();
     sync();
     if (tl) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tl[1]));   // everybody's are, and the staged weights
-    // warp `warp` takes rows j = warp (mod 8); lane covers channels 2*lane, 2*lane+1
+    // On the tensor cores (mma.sync m16n8k16, fp16 in, fp32 accumulate): with scalar code the 53 k fp16 -> fp32
+    // conversions of the weights alone take longer than everything else in the head. Weights and hidden values are fp16 in
+    // memory, so nothing is rounded on the way in. A tile is 16 rows x 64 channels: four instructions with the weights
+    // as the 16 (channels) x 16 (rows) operand and the hidden values in column 0 of the 16 x 8 one. Warp w takes the
+    // tiles w, w + 8, ... of the concatenated tile list of the four matrices.
     const int bounds[5] = {0, p.rw, p.rw + p.ra, p.rw + p.ra + p.rv, rtot};
+    // lane's row address for the four 8x8 tiles of a 16 x 16 weight operand: tile (lane >> 3): bit 0 = channels 8-15,
+    // bit 1 = rows 8-15; row (lane & 7) of that tile
+    const int lrow = (lane & 7) + ((lane >> 4) << 3), lpiece = (lane >> 3) & 1;
+    const uint32_t w2s_u32 = (uint32_t)__cvta_generic_to_shared(w2s);
+    int tbase = 0;   // index of the matrix' first tile in the concatenated tile list
 #pragma unroll
     for (int m = 0; m < 4; ++m) {
-        // four rows per step on separate accumulators: the shared-memory loads of the next rows are in flight while
-        // the products of these are added (one accumulator and one row at a time, every step waits for its own loads)
-        float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
-        int j = bounds[m] + warp;
-        for (; j + 24 < bounds[m + 1]; j += 32) {
+        float acc[4][4];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const float2 wv = __half22float2(reinterpret_cast<const __half2*>(w2s + (size_t)(j + 8 * u) * 64)[lane]);
-                const float hx = hvec[j + 8 * u];
-                s0[u] = fmaf(hx, wv.x, s0[u]);
-                s1[u] = fmaf(hx, wv.y, s1[u]);
+        for (int ct = 0; ct < 4; ++ct) acc[ct][0] = acc[ct][1] = acc[ct][2] = acc[ct][3] = 0.f;
+        const int rows = bounds[m + 1] - bounds[m], nt = (rows + 15) >> 4;
+        for (int kt = (warp - tbase) & 7; kt < nt; kt += 8) {
+            // hidden values: column 0 of the 16 x 8 operand lives in lanes 0-3 (rows 2*lane, 2*lane+1 and those + 8);
+            // rows past the end of the matrix are zeros
+            uint32_t b0 = 0, b1 = 0;
+            if (lane < 4) {
+                const int r = kt * 16 + 2 * lane;
+                const unsigned short* hp = hv16 + bounds[m] + r;
+                b0 = (r < rows ? hp[0] : 0u) | ((r + 1 < rows ? hp[1] : 0u) << 16);
+                b1 = (r + 8 < rows ? hp[8] : 0u) | ((r + 9 < rows ? hp[9] : 0u) << 16);
+            }
+            // the address of a row past the end is clamped to the last row: only weights are multiplied by those zeros
+            const int krow = bounds[m] + min(kt * 16 + lrow, rows - 1);
+#pragma unroll
+            for (int ct = 0; ct < 4; ++ct) {
+                uint32_t a0, a1, a2, a3;
+                const uint32_t a_addr = w2s_u32 + (uint32_t)(krow * 128 + (((2 * ct + lpiece) ^ (krow & 7)) << 4));
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(a0), "=r"(a1), "=r"(a2), "=r"(a3) : "r"(a_addr));
+                asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                             : "+f"(acc[ct][0]), "+f"(acc[ct][1]), "+f"(acc[ct][2]), "+f"(acc[ct][3])
+                             : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
             }
         }
-        for (; j < bounds[m + 1]; j += 8) {
-            const float2 wv = __half22float2(reinterpret_cast<const __half2*>(w2s + (size_t)j * 64)[lane]);
-            s0[0] = fmaf(hvec[j], wv.x, s0[0]);
-            s1[0] = fmaf(hvec[j], wv.y, s1[0]);
+        // column 0 of the result: lanes 0, 4, .. 28 hold channels lane / 4 and lane / 4 + 8 of each 16-channel tile
+        if ((lane & 3) == 0) {
+#pragma unroll
+            for (int ct = 0; ct < 4; ++ct) {
+                part[(warp * 4 + m) * 64 + ct * 16 + (lane >> 2)] = acc[ct][0];
+                part[(warp * 4 + m) * 64 + ct * 16 + (lane >> 2) + 8] = acc[ct][2];
+            }
         }
-        part[(warp * 4 + m) * 64 + 2 * lane] = (s0[0] + s0[1]) + (s0[2] + s0[3]);
-        part[(warp * 4 + m) * 64 + 2 * lane + 1] = (s1[0] + s1[1]) + (s1[2] + s1[3]);
+        tbase += nt;
     }
     sync();
     {

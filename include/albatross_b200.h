@@ -187,9 +187,21 @@ int ab_decode_run(ab_model* m, void* program, void* stream);
  *   "merge_ups" (0)       persistent kernel: adapter up-projections inside the per-head phase instead of a phase
  *                         of matrix-vector rows of their own (bit-identical to ab_forward at B = T = 1, 3 % slower;
  *                         switches "smem_prefetch" and "barrier_prefetch" off)
- *   "l2_prefetch_kb" (0), "smem_prefetch" (0), "early_slice" (0), "barrier_prefetch" (0)
- *                         persistent kernel: ways of requesting the next phase's weights early; all measured
- *                         slower than not doing it (they delay the loads of the phase's input vector)
+ *   "fuse_heads" (1)      persistent kernel in dataflow mode: no barrier among all blocks; the vectors that cross
+ *                         blocks are tagged words their readers wait for, and block 2h runs head h right after its
+ *                         share of the r/k/v rows (needs 2 * heads + 4 blocks; else the barrier mode is used)
+ *   "pair_split" (16)     dataflow mode: how many of a head's 48 r/k/v row groups block 2h takes (block 2h+1: the rest)
+ *   "early_slice" (-1)    first weight slice of every warp requested into shared memory ahead of the phase's input
+ *                         vector: 1 = at the start of the phase, 2 = once the inputs have arrived, 0 = off,
+ *                         -1 = 1 in dataflow mode, 0 otherwise
+ *   "l2_prefetch_kb" (-1), "l2_prefetch2_kb" (-1)
+ *                         per block: KB of its share of the next matrix-vector phase asked into L2 when it has
+ *                         streamed its last weights of the current one, and KB more when that phase's inputs have
+ *                         arrived; -1 = 64 and 128 in dataflow mode, 0 otherwise
+ *   "timeline_block" (0)  block whose timestamps "timeline" records
+ *   "smem_prefetch" (0), "barrier_prefetch" (0)
+ *                         barrier mode only: earlier ways of requesting the next phase's weights early (measured
+ *                         slower than not doing it there: they delay the loads of the phase's input vector)
  *   "stages"              accepted and ignored */
 int ab_model_set_option(ab_model* m, const char* name, int value);
 
