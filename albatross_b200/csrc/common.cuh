@@ -79,6 +79,11 @@ constexpr unsigned int DEV_WAIT_HEAD = 4u;
 constexpr unsigned int DEV_BOUNDS = 16u;     // bounds-checked build only: a computed index fell outside its array (the access was skipped)
 constexpr unsigned int DEV_BAD_TOKEN = 8u;   // a token id outside [0, vocab) reached a kernel (it was clamped, not followed)
 
+#ifndef TAG_POLL_NS_VALUE
+#define TAG_POLL_NS_VALUE 100u
+#endif
+constexpr unsigned TAG_POLL_NS = TAG_POLL_NS_VALUE;   // pause between two looks at a tagged word that is not there yet
+
 // Bounds-checked build (-DAB_BOUNDS_CHECK, `python -m albatross_b200.build --bounds-check`): the stand-in for a memory
 // checker where none can be run. AB_BC(cond) is `true` in the normal build and costs nothing; in the checked build it
 // evaluates the range condition of the access it guards, and when the condition fails it records DEV_BOUNDS in the status

@@ -130,6 +130,13 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) decode_kernel(const DecodePro
     __syncthreads();
 
     const uint32_t epoch = prog->epoch;   // tag base of this token (dataflow mode)
+    // this block's time stamps: [2 * n] phase start / end, then [4 * n] inside the phase; timeline_block < 0: every block
+    // records, into consecutive areas of timeline_stride entries
+    auto tl_base = [&]() -> unsigned long long* {
+        if (!prog->timeline) return nullptr;
+        if (prog->timeline_block < 0) return prog->timeline + (size_t)bid * prog->timeline_stride;
+        return bid == prog->timeline_block ? prog->timeline : nullptr;
+    };
     bool failed = false;
     int pre_phase = -1;
     unsigned n_barriers = 0;
@@ -150,13 +157,13 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) decode_kernel(const DecodePro
             asm volatile("cp.async.commit_group;" ::: "memory");
         }
         const DecodePhase& ph = phs[i & 3];
-        if (prog->timeline && bid == prog->timeline_block && tid == 0) prog->timeline[2 * i] = global_ns();
+        if (tid == 0 && tl_base()) tl_base()[2 * i] = global_ns();
         if (ph.type == PHASE_GEMV) {
             const int j = ph.next_gemv;
             const bool pre = j >= 0 && prog->smem_prefetch;
             gemv_consume(ph.g, plans[i & 3], m, tid, bid, i, pre_phase, pre ? &phs[j & 3].g : nullptr,
                          pre ? &plans[j & 3] : nullptr, j,
-                         (prog->timeline && bid == prog->timeline_block) ? prog->timeline + 2 * n_phases + 4 * i : nullptr,
+                         tl_base() ? tl_base() + 2 * n_phases + 4 * i : nullptr,
                          // the first-slice prefetch uses the area that the phase before a paired head phase stages into
                          (i + 1 < n_phases && phs[(i + 1) & 3].type == PHASE_HEAD && phs[(i + 1) & 3].h.pair_mode) ? 0 : prog->early_slice,
                          [&]() {
@@ -181,9 +188,9 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) decode_kernel(const DecodePro
             if (tid == 32 && j >= 0 && prog->l2_prefetch_bytes > 0) prefetch_share(phs[j & 3].g, plans[j & 3], 0, prog->l2_prefetch_bytes);
         } else {
             head_phase(ph.h, bid, nb, tid, smem, m.pref, m.xn, hsh, epoch,
-                       (prog->timeline && bid == prog->timeline_block && tid == 0) ? prog->timeline + 2 * n_phases + 4 * i : nullptr);
+                       (tid == 0 && tl_base()) ? tl_base() + 2 * n_phases + 4 * i : nullptr);
         }
-        if (prog->timeline && bid == prog->timeline_block && tid == 0) prog->timeline[2 * i + 1] = global_ns();
+        if (tid == 0 && tl_base()) tl_base()[2 * i + 1] = global_ns();
         if (i + 1 < n_phases) {
             if (ph.no_barrier) {
                 // a block barrier only: either the same block produces and consumes, or (dataflow mode) the phase's
@@ -219,7 +226,7 @@ size_t decode_timeline_offset(int n_phases, int n_blocks) {
 }
 size_t decode_program_bytes(int n_layer, int n_blocks) {
     const int n_phases = 6 * n_layer + 1;
-    return decode_timeline_offset(n_phases, n_blocks) + 48 * (size_t)n_phases + 256;
+    return decode_timeline_offset(n_phases, n_blocks) + 48 * (size_t)n_phases * n_blocks + 256;
 }
 
 int decode_launch(const DecodeProgram* prog_dev, unsigned* barrier_dev, int Kn, int xq_bytes, cudaStream_t stream) {

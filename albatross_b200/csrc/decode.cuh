@@ -36,8 +36,8 @@ struct DecodeProgram {
     unsigned epoch;          // dataflow mode: tag base of the next token (tags are epoch + phase index + 1, 16 bits); the
                              // kernel advances it by n_phases when a token is done, so no two writes of a word that
                              // follow one another carry the same tag
-    int timeline_block;      // block that records the timeline
-    unsigned pad[1];
+    int timeline_block;      // block that records the timeline; < 0: all of them
+    unsigned timeline_stride;   // entries per block in that case
     DecodePhase phases[1];   // n_phases entries
 };
 

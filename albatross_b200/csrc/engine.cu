@@ -268,6 +268,7 @@ int build_decode_program(ab_model* m, const int32_t* token, void* const* state, 
     prog->barrier = const_cast<unsigned*>(&dev_addr->barrier_word);
     prog->epoch = 1;   // tags start above zero: freshly cleared words (tag 0) are "not written yet"
     prog->timeline_block = m->timeline_block;
+    prog->timeline_stride = 6u * (unsigned)n_phases;
     prog->timeline = m->timeline ? (unsigned long long*)((unsigned char*)dev_addr +
                                                           decode_timeline_offset(n_phases, m->n_sm)) : nullptr;
     int n = 0;
@@ -638,7 +639,7 @@ int ab_model_set_option(ab_model* m, const char* name, int value) {
     else if (!strcmp(name, "pdl")) m->use_pdl = value != 0;
     else if (!strcmp(name, "debug_sync")) m->debug_sync = value != 0;
     else if (!strcmp(name, "timeline")) m->timeline = value != 0;
-    else if (!strcmp(name, "timeline_block")) m->timeline_block = value < 0 ? 0 : value;
+    else if (!strcmp(name, "timeline_block")) m->timeline_block = value < 0 ? -1 : value;
     else if (!strcmp(name, "l2_prefetch_kb")) m->l2_prefetch_kb = value < 0 ? -1 : value;
     else if (!strcmp(name, "l2_prefetch2_kb")) m->l2_prefetch2_kb = value < 0 ? -1 : value;
     else if (!strcmp(name, "smem_prefetch")) m->smem_prefetch = value != 0;

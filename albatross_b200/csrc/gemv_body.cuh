@@ -63,7 +63,7 @@ __device__ __forceinline__ float ld_tagged1(const void* base, int idx, uint32_t 
             atomicOr(&g_device_status, DEV_WAIT_GEMV);
             break;
         }
-        __nanosleep(it < 4 ? 100u : 400u);   // waiting blocks must not flood the L2 that the producers still need
+        __nanosleep(TAG_POLL_NS);   // waiting blocks must not flood the L2 that the producers still need
         w = ld_relaxed_u32(p);
     }
     return __half2float(__ushort_as_half((unsigned short)(w & 0xffffu)));
@@ -83,7 +83,7 @@ __device__ __forceinline__ uint4 ld_tagged8(const void* base, int idx8, uint32_t
             atomicOr(&g_device_status, DEV_WAIT_GEMV);
             break;
         }
-        __nanosleep(it < 4 ? 100u : 400u);   // waiting blocks must not flood the L2 that the producers still need
+        __nanosleep(TAG_POLL_NS);   // waiting blocks must not flood the L2 that the producers still need
     }
     return make_uint4(__byte_perm(a.x, a.y, 0x5410), __byte_perm(a.z, a.w, 0x5410), __byte_perm(b.x, b.y, 0x5410),
                       __byte_perm(b.z, b.w, 0x5410));
@@ -106,7 +106,7 @@ __device__ __forceinline__ void ld_tagged16(const void* base, int idx16, uint32_
             atomicOr(&g_device_status, DEV_WAIT_GEMV);
             break;
         }
-        __nanosleep(it < 4 ? 100u : 400u);
+        __nanosleep(TAG_POLL_NS);
     }
     lo = make_uint4(__byte_perm(a.x, a.y, 0x5410), __byte_perm(a.z, a.w, 0x5410), __byte_perm(b.x, b.y, 0x5410), __byte_perm(b.z, b.w, 0x5410));
     hi = make_uint4(__byte_perm(c.x, c.y, 0x5410), __byte_perm(c.z, c.w, 0x5410), __byte_perm(d.x, d.y, 0x5410), __byte_perm(d.z, d.w, 0x5410));

@@ -38,7 +38,7 @@ __device__ __forceinline__ float head_ld(const __half* base, size_t idx, const H
             atomicOr(&g_device_status, DEV_WAIT_HEAD);
             break;
         }
-        __nanosleep(it < 4 ? 100u : 400u);
+        __nanosleep(TAG_POLL_NS);
     }
     return __half2float(__ushort_as_half((unsigned short)(w & 0xffffu)));
 }
@@ -73,7 +73,7 @@ __device__ __forceinline__ void head_ld_rkv(const HeadParams& p, size_t off, int
             atomicOr(&g_device_status, DEV_WAIT_HEAD);
             break;
         }
-        __nanosleep(it < 4 ? 100u : 400u);
+        __nanosleep(TAG_POLL_NS);
     }
     auto val = [](uint32_t x) { return __half2float(__ushort_as_half((unsigned short)(x & 0xffffu))); };
     rr[0] = val(w0); rr[1] = val(w1); kr[0] = val(w2); kr[1] = val(w3); vv[0] = val(w4); vv[1] = val(w5);
@@ -193,7 +193,7 @@ __device__ __forceinline__ void head_ups_compute(const HeadParams& p, int tid, u
                 atomicOr(&g_device_status, DEV_WAIT_HEAD);
                 break;
             }
-            __nanosleep(it < 4 ? 100u : 400u);
+            __nanosleep(TAG_POLL_NS);
         }
 #pragma unroll
         for (int e = 0; e < HV_MAX; ++e)

@@ -391,6 +391,21 @@ class RWKV_x070:
         self.last_timeline_detail = raw[2 * n:].reshape(n, 4)   # per phase: input ready, prepared, streamed, reduced
         return raw[:2 * n].reshape(n, 2)
 
+    def decode_timeline_all(self, state: List[torch.Tensor]):
+        """Timestamps of every block for the last persistent decode step on `state`: array [blocks, phases, 6] of ns
+        (phase start, phase end, inputs arrived, inputs prepared, weights streamed, partial sums reduced); needs
+        set_option("timeline", 1) and set_option("timeline_block", -1) before the program was built."""
+        prog, prog_ptr, _, _ = self._program_for(state)
+        fused = self._options.get("fuse_heads", 1) and not self._options.get("merge_ups", 0) and 2 * self.n_head + 4 <= 148
+        n = (5 if (fused or self._options.get("merge_ups", 0)) else 6) * self.n_layer + 1
+        stride = 6 * (6 * self.n_layer + 1)
+        off = (prog_ptr - prog.data_ptr()) + _lib.lib.ab_decode_timeline_offset(self._handle)
+        torch.cuda.synchronize()
+        n_blocks = torch.cuda.get_device_properties(self.device).multi_processor_count   # one block per SM
+        raw = prog[off:off + 8 * stride * n_blocks].view(torch.int64).cpu().numpy().reshape(n_blocks, stride)
+        import numpy as np
+        return np.concatenate([raw[:, :2 * n].reshape(n_blocks, n, 2), raw[:, 2 * n:6 * n].reshape(n_blocks, n, 4)], axis=2)
+
     def _forward_one_persistent(self, idx: int, state: List[torch.Tensor]):
         _, prog_ptr, tok_dev, logits_buf = self._program_for(state)
         self._send_token(idx, tok_dev)

@@ -198,7 +198,8 @@ int ab_decode_run(ab_model* m, void* program, void* stream);
  *                         per block: KB of its share of the next matrix-vector phase asked into L2 when it has
  *                         streamed its last weights of the current one, and KB more when that phase's inputs have
  *                         arrived; -1 = 64 and 128 in dataflow mode, 0 otherwise
- *   "timeline_block" (0)  block whose timestamps "timeline" records
+ *   "timeline_block" (0)  block whose timestamps "timeline" records; -1: every block, each into its own run of
+ *                         6 * (6 * n_layer + 1) entries behind ab_decode_timeline_offset
  *   "smem_prefetch" (0), "barrier_prefetch" (0)
  *                         barrier mode only: earlier ways of requesting the next phase's weights early (measured
  *                         slower than not doing it there: they delay the loads of the phase's input vector)

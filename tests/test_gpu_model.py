@@ -299,3 +299,25 @@ def test_prompts_of_unequal_length_are_prefilled_into_slots_and_decoded_together
         assert rel_err(lb[i].float().cpu().numpy(), la.float().cpu().numpy()) <= 1e-2, i
     one = model.extract_state(state, 3)
     assert all(torch.equal(a, b[3]) for a, b in zip(one, state))
+
+
+def test_persistent_kernel_timeline_of_every_block():
+    """The per-phase time stamps of the persistent kernel (set_option "timeline", "timeline_block" = -1): every block
+    records a start and an end per phase, in order, and the recording does not change the logits."""
+    import numpy as np
+    model, args = model_for("0.1b", "int8")
+    want, _ = model.forward(11, None)
+    model.set_option("timeline", 1)
+    model.set_option("timeline_block", -1)
+    st = model.new_state()
+    got, st = model.forward(11, st)
+    tl = model.decode_timeline_all(st)
+    model.set_option("timeline", 0)
+    model.set_option("timeline_block", 0)
+    assert torch.equal(got, want)
+    n_blocks, n_phases, _ = tl.shape
+    assert n_blocks == torch.cuda.get_device_properties(0).multi_processor_count and n_phases == 5 * args.n_layer + 1
+    start, end = tl[:, :, 0], tl[:, :, 1]
+    assert (start > 0).all() and (end >= start).all()
+    assert (start[:, 1:] >= end[:, :-1]).all()                 # a block runs its phases one after the other
+    assert np.ptp(start[:, 0]) < 1e6                           # all blocks start within a millisecond of one another
