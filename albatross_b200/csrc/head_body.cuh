@@ -308,6 +308,25 @@ __device__ __forceinline__ void head_steps(const HeadParams& p, int b, int h, in
             // per-channel glue on two channels per lane; head-wide sums are warp shuffles
             float kk0[2], av[2], rk[2];
             float ssq = 0.f, rkr = 0.f;
+            // what needs only the adapter outputs and the parameters comes first: in the persistent kernel r, k, v are
+            // the last inputs to arrive, and everything below the wait for them is on the token's critical path
+            float kfac[2], wd2[2], vg2[2], vf2[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int c = lane + 32 * e, gc = h * 64 + c;
+                const float w_raw = ups ? up[0][c] : lda(p.w_raw + off + c);
+                const float a_raw = ups ? up[1][c] : lda(p.a_raw + off + c);
+                av[e] = rh(sigmoidf_(rh(head_par(par, 1, p.a0, gc, c) + a_raw)));
+                kfac[e] = rh(1.f + rh(rh(av[e] - 1.f) * head_par(par, 4, p.k_a, gc, c)));
+                vg2[e] = vf2[e] = 0.f;
+                if (!p.layer0) {
+                    const float vg_raw = ups ? up[2][c] : lda(p.vg_raw + off + c);
+                    vg2[e] = rh(sigmoidf_(rh(head_par(par, 2, p.v0, gc, c) + vg_raw)));
+                    vf2[e] = lda(p.v_first + off + c);
+                }
+                // decay in fp32 as on the reference's single-token path (reference/rwkv7.py:241)
+                wd2[e] = __expf(-0.606531f * sigmoidf_(rh(head_par(par, 0, p.w0, gc, c) + w_raw)));
+            }
             float rr2[2], kr2[2], vv2[2];
             head_ld_rkv(p, off, lane, tg, rr2, kr2, vv2);
 #pragma unroll
@@ -316,23 +335,12 @@ __device__ __forceinline__ void head_steps(const HeadParams& p, int b, int h, in
                 const float rr = rr2[e];
                 const float kr = kr2[e];
                 float vv = vv2[e];
-                const float w_raw = ups ? up[0][c] : lda(p.w_raw + off + c);
-                const float a_raw = ups ? up[1][c] : lda(p.a_raw + off + c);
-                const float a = rh(sigmoidf_(rh(head_par(par, 1, p.a0, gc, c) + a_raw)));
                 kk0[e] = rh(kr * head_par(par, 3, p.k_k, gc, c));
                 ssq = fmaf(kk0[e], kk0[e], ssq);
-                const float k2 = rh(kr * rh(1.f + rh(rh(a - 1.f) * head_par(par, 4, p.k_a, gc, c))));
-                if (p.layer0) {
-                    p.v_first[off + c] = __float2half_rn(vv);
-                } else {
-                    const float vg_raw = ups ? up[2][c] : lda(p.vg_raw + off + c);
-                    const float vg = rh(sigmoidf_(rh(head_par(par, 2, p.v0, gc, c) + vg_raw)));
-                    vv = rh(vv + rh(rh(lda(p.v_first + off + c) - vv) * vg));
-                }
-                // decay in fp32 as on the reference's single-token path (reference/rwkv7.py:241)
-                const float wd = __expf(-0.606531f * sigmoidf_(rh(head_par(par, 0, p.w0, gc, c) + w_raw)));
-                sr[c] = rr; sw[c] = wd; sk[c] = k2; sv[c] = vv;
-                av[e] = a;
+                const float k2 = rh(kr * kfac[e]);
+                if (p.layer0) p.v_first[off + c] = __float2half_rn(vv);
+                else vv = rh(vv + rh(rh(vf2[e] - vv) * vg2[e]));
+                sr[c] = rr; sw[c] = wd2[e]; sk[c] = k2; sv[c] = vv;
                 rk[e] = rh(rh(rr * k2) * head_par(par, 5, p.r_k, gc, c));
                 rkr += rk[e];
             }
