@@ -67,6 +67,7 @@ def _load():
     lib.ab_dequant.argtypes = [C.POINTER(Mat), vp, vp]
     lib.ab_gemv_plan_selftest.argtypes = [vp, vp, vp, i32, i32, vp, vp]
     lib.ab_sample_rows.argtypes = [vp, i32, i32, C.c_float, C.c_uint32, vp, vp]
+    lib.ab_sample_rows_i64.argtypes = [vp, i32, i32, C.c_float, C.c_uint32, vp, vp]
     lib.ab_model_create.argtypes = [C.POINTER(ModelDesc), C.POINTER(vp)]
     lib.ab_model_destroy.argtypes = [vp]
     lib.ab_model_destroy.restype = None
@@ -87,7 +88,7 @@ def _load():
 lib = _load()
 
 EXPORTS = ["ab_last_error", "ab_version", "ab_device_status", "ab_wkv7_fwd", "ab_gemv", "ab_gemm_scratch_bytes",
-           "ab_gemm", "ab_gemm_static", "ab_gemm_static_reset", "ab_gemm_static_debug_counter", "ab_sample_rows", "ab_gemv_plan_selftest", "ab_dequant", "ab_model_create", "ab_model_destroy", "ab_workspace_bytes", "ab_forward", "ab_forward_stage",
+           "ab_gemm", "ab_gemm_static", "ab_gemm_static_reset", "ab_gemm_static_debug_counter", "ab_sample_rows", "ab_sample_rows_i64", "ab_gemv_plan_selftest", "ab_dequant", "ab_model_create", "ab_model_destroy", "ab_workspace_bytes", "ab_forward", "ab_forward_stage",
            "ab_model_set_option", "ab_decode_program_bytes", "ab_decode_timeline_offset", "ab_decode_program_build", "ab_decode_run"]
 
 

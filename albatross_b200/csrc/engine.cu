@@ -558,7 +558,11 @@ int ab_gemm(const ab_mat* m, int rows, const void* x, void* y, int epi, const vo
 }
 
 int ab_sample_rows(const void* logits, int rows, int vocab, float noise, uint32_t seed, int32_t* out, void* stream) {
-    return sample_rows((const __half*)logits, rows, vocab, noise, seed, out, (cudaStream_t)stream);
+    return sample_rows((const __half*)logits, rows, vocab, noise, seed, out, false, (cudaStream_t)stream);
+}
+
+int ab_sample_rows_i64(const void* logits, int rows, int vocab, float noise, uint32_t seed, int64_t* out, void* stream) {
+    return sample_rows((const __half*)logits, rows, vocab, noise, seed, out, true, (cudaStream_t)stream);
 }
 
 int ab_dequant(const ab_mat* m, float* out, void* stream) {

@@ -178,8 +178,9 @@ __device__ __forceinline__ float sample_noise(uint32_t seed, uint32_t row, uint3
     x ^= x >> 16; x *= 0x7FEB352Du; x ^= x >> 15; x *= 0x846CA68Bu; x ^= x >> 16;
     return (float)(x >> 8) * (1.0f / 16777216.0f);   // [0, 1)
 }
+template <class OutT>
 __global__ void __launch_bounds__(RT) sample_rows_kernel(const __half* __restrict__ logits, int V, float noise, uint32_t seed,
-                                                         int* __restrict__ out) {
+                                                         OutT* __restrict__ out) {
     __shared__ float bv[RT / 32];
     __shared__ int bi[RT / 32];
     const size_t row = blockIdx.x;
@@ -213,7 +214,7 @@ __global__ void __launch_bounds__(RT) sample_rows_kernel(const __half* __restric
     if (threadIdx.x == 0) {
         for (int w = 1; w < RT / 32; ++w)
             if (bv[w] > best || (bv[w] == best && bi[w] < idx)) { best = bv[w]; idx = bi[w]; }
-        out[row] = idx;
+        out[row] = (OutT)idx;
     }
 }
 
@@ -255,9 +256,10 @@ int ln_mix_rows(const __half* x, const __half* w, const __half* b, const MixPara
     AB_CUDA(cudaLaunchKernelEx(&cfg, ln_mix_rows_kernel, x, w, b, p, pdl ? 1 : 0));
     return OK;
 }
-int sample_rows(const __half* logits, int rows, int V, float noise, uint32_t seed, int* out, cudaStream_t s) {
+int sample_rows(const __half* logits, int rows, int V, float noise, uint32_t seed, void* out, bool out_i64, cudaStream_t s) {
     AB_CHECK_ARG(logits && out && rows > 0 && V > 0 && noise >= 0.f, "sample_rows: bad argument");
-    sample_rows_kernel<<<rows, RT, 0, s>>>(logits, V, noise, seed, out);
+    if (out_i64) sample_rows_kernel<long long><<<rows, RT, 0, s>>>(logits, V, noise, seed, (long long*)out);
+    else sample_rows_kernel<int><<<rows, RT, 0, s>>>(logits, V, noise, seed, (int*)out);
     AB_CUDA(cudaGetLastError());
     return OK;
 }

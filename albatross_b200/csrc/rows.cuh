@@ -16,7 +16,7 @@ int gather_rows(const __half* table, const int* idx, int rows, int D, int vocab,
 int ln_rows(const __half* x, const __half* w, const __half* b, int rows, int D, int stride, int offset, __half* out,
             cudaStream_t s);
 int mix_rows(const MixParams& p, cudaStream_t s);
-int sample_rows(const __half* logits, int rows, int V, float noise, uint32_t seed, int* out, cudaStream_t s);
+int sample_rows(const __half* logits, int rows, int V, float noise, uint32_t seed, void* out, bool out_i64, cudaStream_t s);
 // Layer norm of x (weights w, b) fused with the lerps, for T == 1 (p.xn is not used).
 bool ln_mix_rows_ok(const MixParams& p);
 int ln_mix_rows(const __half* x, const __half* w, const __half* b, const MixParams& p, cudaStream_t s, bool pdl = false);

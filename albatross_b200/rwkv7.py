@@ -65,14 +65,41 @@ def RWKV7_BATCH_OP(state, r, w, k, v, a, b):
     return _wkv(B, T, C_, state, r, w, k, v, a, b)
 
 
-def sampler_simple_batch(logits: torch.Tensor, noise: float = 1.0, seed: int = 0) -> torch.Tensor:
+def sampler_simple_batch(logits: torch.Tensor, noise: float = 1.0, seed: int = 0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Next-token ids [B, 1] (int64) from fp16 logits [B, V] on the device: argmax of logits + U(0, noise), as
-    reference/utils.py:43-45 computes with an argsort. `seed` selects the noise (vary it per step)."""
+    reference/utils.py:43-45 computes with an argsort. `seed` selects the noise (vary it per step). `out`: an int64
+    tensor of B elements to write the ids into, on the device or in pinned host memory (the kernel then stores them
+    straight to the host: read them after synchronising the stream)."""
     assert logits.dim() == 2 and logits.dtype == DTYPE and logits.is_cuda and logits.is_contiguous()
-    out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
-    _lib.check(_lib.lib.ab_sample_rows(logits.data_ptr(), logits.shape[0], logits.shape[1], float(noise), int(seed) & 0xFFFFFFFF,
-                                       out.data_ptr(), torch.cuda.current_stream().cuda_stream), "ab_sample_rows")
-    return out.to(torch.int64).unsqueeze(1)
+    if out is None:
+        out = torch.empty((logits.shape[0], 1), dtype=torch.int64, device=logits.device)
+    assert out.dtype == torch.int64 and out.numel() == logits.shape[0] and out.is_contiguous() and (out.is_cuda or out.is_pinned())
+    _lib.check(_lib.lib.ab_sample_rows_i64(logits.data_ptr(), logits.shape[0], logits.shape[1], float(noise), int(seed) & 0xFFFFFFFF,
+                                           out.data_ptr(), torch.cuda.current_stream().cuda_stream), "ab_sample_rows_i64")
+    return out.view(logits.shape[0], 1)
+
+
+class _State(list):
+    """The state list forward() hands back. It remembers which model has validated it and which decode program
+    belongs to its tensors, so that the next forward() with it skips both look-ups (96 tensors at 32 blocks: 40 us of
+    Python per token otherwise); any in-place change of the list forgets that."""
+    __slots__ = ("_ab",)
+
+    def __init__(self, items=(), ab=None):
+        super().__init__(items)
+        self._ab = ab
+
+    def _changed(name):
+        def f(self, *a, **k):
+            self._ab = None
+            return getattr(list, name)(self, *a, **k)
+        f.__name__ = name
+        return f
+
+    for _n in ("__setitem__", "__delitem__", "__iadd__", "__imul__", "append", "extend", "insert", "pop", "remove", "clear",
+               "sort", "reverse"):
+        locals()[_n] = _changed(_n)
+    del _n, _changed
 
 
 # --------------------------------------------------------------------------------------------
@@ -262,6 +289,9 @@ class RWKV_x070:
         return st
 
     def _check_state(self, state: List[torch.Tensor], batch: Optional[int]) -> None:
+        ab = getattr(state, "_ab", None)
+        if ab is not None and ab[0] is self and ab[1] == batch:
+            return                                  # validated when this model handed the list out, unchanged since
         D, H = self.n_embd, self.n_embd // HEAD_SIZE
         lead = () if batch is None else (batch,)
         assert len(state) == 3 * self.n_layer, "state must hold 3 tensors per layer"
@@ -333,8 +363,8 @@ class RWKV_x070:
             tok = torch.tensor([int(idx)], dtype=torch.int32, device=self.device)
             logits = torch.empty(self.vocab, dtype=DTYPE, device=self.device)
             self._run(1, 1, tok, state, logits, False)
-            return logits, list(state)
-        key = tuple(t.data_ptr() for t in state)
+            return logits, self._hand_back(state, None)
+        key = self._state_key(state)
         entry = self._graphs.get(key)
         if entry is None:
             entry = self._capture(state)
@@ -344,7 +374,7 @@ class RWKV_x070:
         graph, tok_dev, logits_buf = entry
         self._send_token(idx, tok_dev)
         graph.replay()
-        return logits_buf.clone(), list(state)
+        return logits_buf.clone(), _State(state, (self, None, key))
 
     def _send_token(self, idx: int, tok_dev: torch.Tensor) -> None:
         slot = self._tok_n % 64
@@ -358,8 +388,18 @@ class RWKV_x070:
             ev = self._tok_events[slot] = torch.cuda.Event()
         ev.record()
 
+    def _hand_back(self, state: List[torch.Tensor], batch: Optional[int]):
+        """The caller's next state: the same tensors (updated in place) in a list that remembers this model's checks."""
+        return _State(state, (self, batch, self._state_key(state)))
+
+    def _state_key(self, state: List[torch.Tensor]):
+        ab = getattr(state, "_ab", None)
+        if ab is not None and ab[0] is self:
+            return ab[2]
+        return tuple(t.data_ptr() for t in state)
+
     def _program_for(self, state: List[torch.Tensor]):
-        key = tuple(t.data_ptr() for t in state)
+        key = self._state_key(state)
         entry = self._programs.get(key)
         if entry is None:
             tok_dev = torch.zeros(1, dtype=torch.int32, device=self.device)
@@ -407,10 +447,11 @@ class RWKV_x070:
         return np.concatenate([raw[:, :2 * n].reshape(n_blocks, n, 2), raw[:, 2 * n:6 * n].reshape(n_blocks, n, 4)], axis=2)
 
     def _forward_one_persistent(self, idx: int, state: List[torch.Tensor]):
+        key = self._state_key(state)
         _, prog_ptr, tok_dev, logits_buf = self._program_for(state)
         self._send_token(idx, tok_dev)
         _lib.check(_lib.lib.ab_decode_run(self._handle, prog_ptr, torch.cuda.current_stream().cuda_stream), "ab_decode_run")
-        return logits_buf.clone(), list(state)
+        return logits_buf.clone(), _State(state, (self, None, key))
 
     def _capture(self, state: List[torch.Tensor]):
         """Record one decode step (all launches of ab_forward at B=T=1) into a CUDA graph.
@@ -437,7 +478,7 @@ class RWKV_x070:
         tok = torch.tensor([self._wrap_id(t) for t in idx], dtype=torch.int32, device=self.device)
         logits = torch.empty((T, self.vocab) if full_output else (self.vocab,), dtype=DTYPE, device=self.device)
         self._run(1, T, tok, state, logits, full_output)
-        return logits, list(state)
+        return logits, self._hand_back(state, None)
 
     @torch.no_grad()
     def forward_seq_batch(self, idxs: List[List[int]], state: List[torch.Tensor], full_output: bool = False):
@@ -452,12 +493,13 @@ class RWKV_x070:
         shape = (B, T, self.vocab) if full_output else (B, self.vocab)
         logits = torch.empty(shape, dtype=DTYPE, device=self.device)
         self._run(B, T, tok, state, logits, full_output)
-        return logits, list(state)
+        return logits, self._hand_back(state, B)
 
     def _forward_batch_graph(self, B: int, tok_host: torch.Tensor, state: List[torch.Tensor]):
         """One batched decode step (T = 1) replayed from a CUDA graph: the ~260 launches of the step, and the tensor
         maps the products encode on the host for every launch, are recorded once per (batch, state tensors)."""
-        key = (B,) + tuple(t.data_ptr() for t in state)
+        skey = self._state_key(state)
+        key = (B,) + skey
         entry = self._graphs.get(key)
         if entry is None:
             tok_dev = torch.zeros(B, dtype=torch.int32, device=self.device)
@@ -481,7 +523,7 @@ class RWKV_x070:
         tok_dev.copy_(pinned, non_blocking=True)
         ev.record()
         graph.replay()
-        return logits_buf.clone(), list(state)
+        return logits_buf.clone(), _State(state, (self, B, skey))
 
     # ---- sequences of unequal length: prefill one by one, decode together -----------------------------------
     # The reference cannot batch prompts of different lengths (reference/rwkv7.py:116-117 asserts equal lengths) nor

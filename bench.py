@@ -225,7 +225,7 @@ def run_ours(a, rank, world, dev, workload=None, batch=None):
             logits = logits.unsqueeze(0)
         else:
             logits, state = model.forward_batch([[int(t)] for t in toks[i]], state)
-        pinned_ids.copy_(sampler_simple_batch(logits, noise=0.0), non_blocking=True)
+        sampler_simple_batch(logits, noise=0.0, out=pinned_ids)     # the kernel stores the ids to pinned host memory
         torch.cuda.current_stream().synchronize()
 
     for i in range(a.warmup):

@@ -140,6 +140,9 @@ int ab_gemm_static_debug_counter(int index, int write, uint32_t* value_host);
  * the row of logits[r, :] + U(0, noise), ties to the lowest index. logits fp16 [rows, vocab], out int32 [rows].
  * noise == 0 is plain greedy decoding. The noise is a hash of (seed, row, column), not torch's generator. */
 int ab_sample_rows(const void* logits, int rows, int vocab, float noise, uint32_t seed, int32_t* out, void* stream);
+/* The same with 64-bit ids (the dtype the reference's sampler returns). `out` may be device memory or pinned host
+ * memory that the device can address: the ids then need no copy of their own on the way to the host. */
+int ab_sample_rows_i64(const void* logits, int rows, int vocab, float noise, uint32_t seed, int64_t* out, void* stream);
 
 /* ---- de-quantisation dump (parity checks) ---------------------------------------------------
  * Writes the kernels' in-register de-quantised weights as fp32 [n_out,k] (tensor/row/column scales applied). */

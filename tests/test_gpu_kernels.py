@@ -223,3 +223,9 @@ def test_device_sampler_matches_argsort():
             assert not torch.equal(a, c)
     ties = torch.zeros(2, 64, device="cuda").half()
     assert sampler_simple_batch(ties, noise=0.0).flatten().tolist() == [0, 0]  # ties go to the lowest index
+    # ids written by the kernel straight into pinned host memory (no copy of their own)
+    pinned = torch.full((3, 1), -1, dtype=torch.int64).pin_memory()
+    logits = torch.randn(3, 1000, device="cuda").half()
+    ret = sampler_simple_batch(logits, noise=0.0, out=pinned)
+    torch.cuda.current_stream().synchronize()
+    assert ret.data_ptr() == pinned.data_ptr() and pinned.flatten().tolist() == logits.float().argmax(-1).tolist()

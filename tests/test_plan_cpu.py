@@ -46,3 +46,21 @@ def test_random_segment_lists_are_covered_exactly_once(segs, n_blocks):
     rows = [s[1] for s in segs]
     k = [s[2] * 32 for s in segs]          # NVFP4 rows need k % 32 == 0
     _check(fmt, rows, k, n_blocks)
+
+
+def test_state_list_forgets_its_checks_when_changed():
+    """The list forward() hands back carries the model's validation and program key; any in-place change of the list
+    drops them, so a changed list is checked from scratch (it is still a plain list to its user)."""
+    from albatross_b200.rwkv7 import _State
+    owner = object()
+    mark = (owner, None, (1, 2, 3))
+    for change in (lambda s: s.__setitem__(0, "x"), lambda s: s.append("x"), lambda s: s.pop(), lambda s: s.extend(["y"]),
+                   lambda s: s.insert(0, "z"), lambda s: s.clear(), lambda s: s.reverse(), lambda s: s.__delitem__(0),
+                   lambda s: s.__iadd__(["w"])):
+        st = _State(["a", "b", "c"], mark)
+        assert st._ab is mark and isinstance(st, list) and list(st) == ["a", "b", "c"]
+        change(st)
+        assert st._ab is None
+    st = _State(["a", "b"], mark)
+    assert st[1] == "b" and len(st) == 2 and st._ab is mark          # reading keeps them
+    assert not hasattr(list(st), "_ab") and _State(st)._ab is None   # a copy starts unchecked
