@@ -484,9 +484,11 @@ class RWKV_x070:
     def forward_seq_batch(self, idxs: List[List[int]], state: List[torch.Tensor], full_output: bool = False):
         B, T = len(idxs), len(idxs[0])
         self._check_state(state, B)
-        self._check_ids(idxs)
-        tok = torch.tensor(idxs, dtype=torch.int32)
-        tok = torch.where(tok < 0, tok + self.vocab, tok)
+        tok = torch.tensor(idxs, dtype=torch.int64)
+        lo, hi = torch.aminmax(tok)                  # the range check of _check_ids, on the tensor (B * T ids)
+        if int(lo) < -self.vocab or int(hi) >= self.vocab:
+            self._check_ids(idxs)                    # raises the IndexError with the offending id
+        tok = torch.where(tok < 0, tok + self.vocab, tok).to(torch.int32)
         if T == 1 and B > 1 and self.use_graph:
             return self._forward_batch_graph(B, tok, state)
         tok = tok.to(self.device)

@@ -218,13 +218,15 @@ def run_ours(a, rank, world, dev, workload=None, batch=None):
     pinned_ids = torch.empty((B, 1), dtype=torch.int64).pin_memory()
     state = model.new_state(B if B > 1 else None)
 
+    tok_lists = toks.tolist()       # host token ids as the Python lists the reference's API takes
+
     def e2e_step(i):
         nonlocal state
         if B == 1:
-            logits, state = model.forward(int(toks[i, 0]), state)
+            logits, state = model.forward(tok_lists[i][0], state)
             logits = logits.unsqueeze(0)
         else:
-            logits, state = model.forward_batch([[int(t)] for t in toks[i]], state)
+            logits, state = model.forward_batch([[t] for t in tok_lists[i]], state)
         sampler_simple_batch(logits, noise=0.0, out=pinned_ids)     # the kernel stores the ids to pinned host memory
         torch.cuda.current_stream().synchronize()
 
