@@ -231,7 +231,8 @@ __device__ __forceinline__ void head_ups_compute(const HeadParams& p, int tid, u
                 b1 = (r + 8 < rows ? hp[8] : 0u) | ((r + 9 < rows ? hp[9] : 0u) << 16);
             }
             // the address of a row past the end is clamped to the last row: only weights are multiplied by those zeros
-            const int krow = bounds[m] + min(kt * 16 + lrow, rows - 1);
+            int krow = bounds[m] + min(kt * 16 + lrow, rows - 1);
+            if (!AB_BC(krow >= 0 && krow < rtot)) krow = 0;
 #pragma unroll
             for (int ct = 0; ct < 4; ++ct) {
                 uint32_t a0, a1, a2, a3;
@@ -247,8 +248,10 @@ __device__ __forceinline__ void head_ups_compute(const HeadParams& p, int tid, u
         if ((lane & 3) == 0) {
 #pragma unroll
             for (int ct = 0; ct < 4; ++ct) {
-                part[(warp * 4 + m) * 64 + ct * 16 + (lane >> 2)] = acc[ct][0];
-                part[(warp * 4 + m) * 64 + ct * 16 + (lane >> 2) + 8] = acc[ct][2];
+                if (AB_BC((warp * 4 + m) * 64 + ct * 16 + (lane >> 2) + 8 < 8 * 4 * 64)) {
+                    part[(warp * 4 + m) * 64 + ct * 16 + (lane >> 2)] = acc[ct][0];
+                    part[(warp * 4 + m) * 64 + ct * 16 + (lane >> 2) + 8] = acc[ct][2];
+                }
             }
         }
         tbase += nt;
