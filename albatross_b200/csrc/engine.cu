@@ -540,6 +540,7 @@ int ab_gemv(const ab_mat* m, const void* x, void* y, void* stream) {
     AB_TRY(check_mat(*m, "ab_gemv"));
     GemvParams p = {};
     p.nseg = 1; p.K = m->k; p.x = (const __half*)x;
+    p.use_pdl = 1;   // the kernel reads x and writes y only after its predecessor in the stream has completed
     p.seg[0] = seg_of(*m, nullptr, EPI_NONE, y);
     return gemv_launch(p, (cudaStream_t)stream);
 }

@@ -32,12 +32,20 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const int Kn, const int
     __shared__ BlockPlan bp;
     const GemvSmem m = gemv_smem(smem, gemv_layout(Kn, with_dx, xq_bytes));
     if (threadIdx.x == 0) compute_plan(p, blockIdx.x, gridDim.x, bp);
+    __syncthreads();
+    int pre_phase = -1;
     if (p.use_pdl) {
+        // Launched with programmatic stream serialisation the block may run before its predecessor has finished.
+        // Weights are never written, so every warp's first slice starts its way into shared memory now; inputs and
+        // outputs are touched only behind the wait.
+        const int warp = threadIdx.x >> 5;
+        if (warp < bp.n_items) {
+            prefetch_item(make_item(p, bp, warp), threadIdx.x & 31, m.pref + warp * (GEMV_ROWS * GEMV_SLICE_BYTES));
+            pre_phase = 0;
+        }
         pdl_wait();
         pdl_launch_dependents();
     }
-    __syncthreads();
-    int pre_phase = -1;
     gemv_consume(p, bp, m, threadIdx.x, blockIdx.x, 0, pre_phase, nullptr, nullptr, -1);
 }
 
