@@ -16,12 +16,16 @@ CSRC = os.path.join(HERE, "csrc")
 OUT_DIR = os.path.join(HERE, "_C")
 LIB = os.path.join(OUT_DIR, "libalbatross_b200.so")
 LIB_CHECKED = os.path.join(OUT_DIR, "libalbatross_b200_checked.so")   # -DAB_BOUNDS_CHECK build (see csrc/common.cuh)
-NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+# -fmad=false: a*b+c is fused only where the source says fmaf(). The same device functions are compiled into several
+# kernels (the persistent decode kernel and the per-phase launches share their matrix-vector and head code); left to
+# the compiler, which products get fused depends on the code around them, and two kernels that should agree bit for
+# bit differ in a last fp16 digit once in a few hundred tokens.
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-fmad=false",
               "-Xcompiler", "-fPIC", "-shared", "-Xptxas", "-v"]
 
 
 def _sources():
-    out = [os.path.join(HERE, "..", "include", "albatross_b200.h")]
+    out = [os.path.join(HERE, "..", "include", "albatross_b200.h"), os.path.abspath(__file__)]   # (this file holds the flags)
     for f in sorted(os.listdir(CSRC)):
         if f.endswith((".cu", ".cuh", ".h")):
             out.append(os.path.join(CSRC, f))

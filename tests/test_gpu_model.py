@@ -220,7 +220,7 @@ def test_batch1_modes_give_identical_logits():
         if mode == "persistent-merged":
             model.set_option("merge_ups", 1)     # (the default, "fuse_heads", computes the up-projections the same way)
         st, seq = None, []
-        for t in seeded_tokens(args.vocab_size, 5, seed=4):
+        for t in seeded_tokens(args.vocab_size, 300, seed=21):     # long enough for a last-digit difference to surface
             logits, st = model.forward(t, st)
             seq.append(logits.clone())
         outs.append(torch.stack(seq))
@@ -321,3 +321,20 @@ def test_persistent_kernel_timeline_of_every_block():
     assert (start > 0).all() and (end >= start).all()
     assert (start[:, 1:] >= end[:, :-1]).all()                 # a block runs its phases one after the other
     assert np.ptp(start[:, 0]) < 1e6                           # all blocks start within a millisecond of one another
+
+
+def test_persistent_kernel_tags_wrap_around():
+    """The tagged words of the dataflow mode carry 16-bit tags that advance by the number of phases per token: at 61
+    phases (0.1B) they wrap after 1074 tokens. A decode of 2300 tokens crosses the wrap twice; every logit vector must
+    still equal the one of the per-phase launches (which use no tags), and no wait may have run out."""
+    from albatross_b200 import _lib
+    pers, args = model_for("0.1b", "int8")
+    eager, _ = model_for("0.1b", "int8", decode_mode="graph")
+    toks = seeded_tokens(args.vocab_size, 2300, seed=21)
+    sp = se = None
+    for i, t in enumerate(toks):
+        lp, sp = pers.forward(t, sp)
+        le, se = eager.forward(t, se)
+        if i % 100 == 99 or i >= 2290 or 1070 <= i <= 1080 or 2145 <= i <= 2155:
+            assert torch.equal(lp, le), f"token {i}"
+    assert _lib.device_status() == 0
