@@ -182,8 +182,8 @@ def test_config2_int8_decode_teacher_forced():
             raw += same
             agree += same or (w.max() - w[int(g.argmax())] <= 2 * err)
         tok = int(w.argmax())
-    out_dir = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "gpurun_out")
-    if os.path.isdir(out_dir):   # the raw figures, for the record
+    out_dir = os.environ.get("AB_TEST_REPORT_DIR", "")    # where to leave the figures as a file, if anywhere
+    if out_dir and os.path.isdir(out_dir):   # the raw figures, for the record
         with open(os.path.join(out_dir, "config2_argmax.json"), "w") as f:
             json.dump({"decode_steps": n_decode, "raw_agreement": raw / (n_decode + 1),
                        "margin_adjusted_agreement": agree / (n_decode + 1), "worst_logit_rel_err": worst}, f)

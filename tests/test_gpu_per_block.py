@@ -148,8 +148,8 @@ def test_every_block_of_the_7_2b_shapes_matches_the_oracle(fmt):
     report["logits"] = logits_err
     report["free_running_x_error_by_depth"] = {str(d): report["blocks"][d - 1][f"step{STEPS - 1}"]["x_free"]
                                                for d in (1, 2, 4, 8, 16, 31)}
-    out_dir = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "gpurun_out")
-    if os.path.isdir(out_dir):
+    out_dir = os.environ.get("AB_TEST_REPORT_DIR", "")    # where to leave the figures as a file, if anywhere
+    if out_dir and os.path.isdir(out_dir):
         with open(os.path.join(out_dir, f"per_block_parity_{fmt}.json"), "w") as f:
             json.dump(report, f, indent=1)
     print(fmt, "worst teacher-forced:", worst, "logits:", logits_err, "free-running by depth:",
