@@ -178,11 +178,13 @@ __device__ __forceinline__ float sample_noise(uint32_t seed, uint32_t row, uint3
     x ^= x >> 16; x *= 0x7FEB352Du; x ^= x >> 15; x *= 0x846CA68Bu; x ^= x >> 16;
     return (float)(x >> 8) * (1.0f / 16777216.0f);   // [0, 1)
 }
-template <class OutT>
-__global__ void __launch_bounds__(RT) sample_rows_kernel(const __half* __restrict__ logits, int V, float noise, uint32_t seed,
+// NT threads per row: 1024 when there are only a few rows (a single row of 65536 logits is otherwise read by 256 threads,
+// 32 loads one after the other: 16 us), 256 otherwise.
+template <class OutT, int NT>
+__global__ void __launch_bounds__(NT) sample_rows_kernel(const __half* __restrict__ logits, int V, float noise, uint32_t seed,
                                                          OutT* __restrict__ out) {
-    __shared__ float bv[RT / 32];
-    __shared__ int bi[RT / 32];
+    __shared__ float bv[NT / 32];
+    __shared__ int bi[NT / 32];
     const size_t row = blockIdx.x;
     const __half* lr = logits + row * V;
     float best = -INFINITY;
@@ -192,7 +194,8 @@ __global__ void __launch_bounds__(RT) sample_rows_kernel(const __half* __restric
         if (v > best || (v == best && i < idx)) { best = v; idx = i; }
     };
     const int nv = (V % 8 == 0 && ((uintptr_t)lr & 15) == 0) ? V / 8 : 0;
-    for (int c = threadIdx.x; c < nv; c += RT) {
+#pragma unroll 4
+    for (int c = threadIdx.x; c < nv; c += NT) {
         const uint4 q = reinterpret_cast<const uint4*>(lr)[c];
         const __half2* h = reinterpret_cast<const __half2*>(&q);
 #pragma unroll
@@ -202,7 +205,7 @@ __global__ void __launch_bounds__(RT) sample_rows_kernel(const __half* __restric
             take(f.y, c * 8 + 2 * e + 1);
         }
     }
-    for (int i = nv * 8 + threadIdx.x; i < V; i += RT) take(__half2float(lr[i]), i);
+    for (int i = nv * 8 + threadIdx.x; i < V; i += NT) take(__half2float(lr[i]), i);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         const float ov = __shfl_xor_sync(0xffffffffu, best, o);
@@ -212,7 +215,7 @@ __global__ void __launch_bounds__(RT) sample_rows_kernel(const __half* __restric
     if ((threadIdx.x & 31) == 0) { bv[threadIdx.x >> 5] = best; bi[threadIdx.x >> 5] = idx; }
     __syncthreads();
     if (threadIdx.x == 0) {
-        for (int w = 1; w < RT / 32; ++w)
+        for (int w = 1; w < NT / 32; ++w)
             if (bv[w] > best || (bv[w] == best && bi[w] < idx)) { best = bv[w]; idx = bi[w]; }
         out[row] = (OutT)idx;
     }
@@ -258,8 +261,13 @@ int ln_mix_rows(const __half* x, const __half* w, const __half* b, const MixPara
 }
 int sample_rows(const __half* logits, int rows, int V, float noise, uint32_t seed, void* out, bool out_i64, cudaStream_t s) {
     AB_CHECK_ARG(logits && out && rows > 0 && V > 0 && noise >= 0.f, "sample_rows: bad argument");
-    if (out_i64) sample_rows_kernel<long long><<<rows, RT, 0, s>>>(logits, V, noise, seed, (long long*)out);
-    else sample_rows_kernel<int><<<rows, RT, 0, s>>>(logits, V, noise, seed, (int*)out);
+    if (rows <= 16) {
+        if (out_i64) sample_rows_kernel<long long, 1024><<<rows, 1024, 0, s>>>(logits, V, noise, seed, (long long*)out);
+        else sample_rows_kernel<int, 1024><<<rows, 1024, 0, s>>>(logits, V, noise, seed, (int*)out);
+    } else {
+        if (out_i64) sample_rows_kernel<long long, RT><<<rows, RT, 0, s>>>(logits, V, noise, seed, (long long*)out);
+        else sample_rows_kernel<int, RT><<<rows, RT, 0, s>>>(logits, V, noise, seed, (int*)out);
+    }
     AB_CUDA(cudaGetLastError());
     return OK;
 }
